@@ -1,0 +1,229 @@
+"""chunk_gated_delta_rule with the reference's signature (fla/ops/gated_delta_rule/chunk.py:395-593),
+computed by the sm_100a kernels of libb200gdn.so through a torch.autograd.Function.
+
+PyTorch is used for device memory, the current stream and autograd bookkeeping only; every stage of
+the reference's pipeline (chunk.py:33-250) runs inside the library.
+"""
+from __future__ import annotations
+
+import warnings
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+from .index import tables_for
+
+_SUPPORTED_HEAD_DIMS = ((64, 64), (128, 128))
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _l2norm(x: torch.Tensor) -> torch.Tensor:
+    """x * rsqrt(sum x^2 + 1e-6) in fp32, result in x.dtype (fla/modules/l2norm.py:84-109)."""
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.square().sum(-1, keepdim=True) + 1e-6)).to(x.dtype)
+
+
+def _gate(g: torch.Tensor, A_log: torch.Tensor, dt_bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """-exp(A_log) * softplus(g + dt_bias) in fp32 (fla/ops/gated_delta_rule/gate.py:21-46)."""
+    g = g.float()
+    if dt_bias is not None:
+        g = g + dt_bias.float()
+    return -A_log.float().exp() * F.softplus(g)
+
+
+def new_chunk_args(q, k, v, scale, tables) -> _lib.ChunkArgs:
+    chunk_meta, seq_meta, (n_chunks, n_seq) = tables
+    a = _lib.ChunkArgs()
+    a.rows = q.shape[0] * q.shape[1]
+    a.H, a.HV, a.K, a.V = q.shape[2], v.shape[2], q.shape[3], v.shape[3]
+    a.n_seq, a.n_chunks = n_seq, n_chunks
+    a.scale = float(scale)
+    a.stage_mask = 0
+    a.chunk_meta, a.seq_meta = chunk_meta.data_ptr(), seq_meta.data_ptr()
+    a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    return a
+
+
+class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
+    """Autograd node around b200gdn_chunk_fwd / b200gdn_chunk_bwd
+    (the role of fla/ops/gated_delta_rule/chunk.py:253-392)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, cu_seqlens_cpu):
+        in_dtypes = (q.dtype, k.dtype, v.dtype, g.dtype, beta.dtype)
+        dev = q.device
+        with torch.cuda.device(dev):
+            qb, kb, vb = (x.to(torch.bfloat16).contiguous() for x in (q, k, v))
+            gf, bf = g.float().contiguous(), beta.float().contiguous()
+            h0 = None if initial_state is None else initial_state.float().contiguous()
+            B, T, H, K = qb.shape
+            HV, V = vb.shape[2], vb.shape[3]
+            tables = tables_for(B, T, cu_seqlens, cu_seqlens_cpu, dev)
+            n_chunks, n_seq = tables[2]
+            rows = B * T
+            a = new_chunk_args(qb, kb, vb, scale, tables)
+            bf16 = dict(dtype=torch.bfloat16, device=dev)
+            f32 = dict(dtype=torch.float32, device=dev)
+            o = torch.empty(B, T, HV, V, **bf16)
+            ht = torch.empty(n_seq, HV, K, V, **f32) if output_final_state else None
+            gamma = torch.empty(rows, HV, **f32)
+            A = torch.empty(rows, HV, 64, **bf16)
+            w = torch.empty(rows, HV, K, **bf16)
+            u = torch.empty(rows, HV, V, **bf16)
+            h = torch.empty(n_chunks, HV, K, V, **bf16)
+            v_new = torch.empty(rows, HV, V, **bf16)
+            a.g, a.beta, a.h0 = gf.data_ptr(), bf.data_ptr(), _lib.ptr(h0)
+            a.o, a.ht = o.data_ptr(), _lib.ptr(ht)
+            a.gamma, a.A, a.w, a.u, a.h, a.v_new = (x.data_ptr() for x in (gamma, A, w, u, h, v_new))
+            _lib.call('b200gdn_chunk_fwd', a, _stream(qb))
+        ctx.save_for_backward(qb, kb, vb, bf, gamma, A, w, h, v_new, tables[0], tables[1])
+        ctx.meta = (scale, n_chunks, n_seq, initial_state is not None, in_dtypes)
+        return o.to(q.dtype), ht
+
+    @staticmethod
+    def backward(ctx, do, dht):
+        qb, kb, vb, bf, gamma, A, w, h, v_new, chunk_meta, seq_meta = ctx.saved_tensors
+        scale, n_chunks, n_seq, has_h0, in_dtypes = ctx.meta
+        dev = qb.device
+        with torch.cuda.device(dev):
+            B, T, H, K = qb.shape
+            HV, V = vb.shape[2], vb.shape[3]
+            rows = B * T
+            dob = do.to(torch.bfloat16).contiguous()
+            dhtf = None if dht is None else dht.float().contiguous()
+            a = new_chunk_args(qb, kb, vb, scale, (chunk_meta, seq_meta, (n_chunks, n_seq)))
+            bf16 = dict(dtype=torch.bfloat16, device=dev)
+            f32 = dict(dtype=torch.float32, device=dev)
+            dq = torch.empty(B, T, H, K, **bf16)
+            dk = torch.empty(B, T, H, K, **bf16)
+            dv = torch.empty(B, T, HV, V, **bf16)
+            dg = torch.empty(B, T, HV, **f32)
+            dbeta = torch.empty(B, T, HV, **f32)
+            dh0 = torch.empty(n_seq, HV, K, V, **f32) if has_h0 else None
+            dh = torch.empty(n_chunks, HV, K, V, **bf16)
+            dv2 = torch.empty(rows, HV, V, **bf16)
+            dw = torch.empty(rows, HV, K, **bf16)
+            dk_part = torch.empty(rows, H, K, **f32)
+            dG = torch.empty(rows, HV, **f32)
+            dq_acc = torch.empty(rows, H, K, **f32) if HV > H else None
+            a.beta, a.gamma, a.A, a.w, a.h, a.v_new = (x.data_ptr() for x in (bf, gamma, A, w, h, v_new))
+            a.d_o, a.dht = dob.data_ptr(), _lib.ptr(dhtf)
+            a.dq, a.dk, a.dv, a.dg, a.dbeta, a.dh0 = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dg.data_ptr(), \
+                dbeta.data_ptr(), _lib.ptr(dh0)
+            a.dh, a.dv2, a.dw, a.dk_part, a.dG, a.dq_acc = dh.data_ptr(), dv2.data_ptr(), dw.data_ptr(), \
+                dk_part.data_ptr(), dG.data_ptr(), _lib.ptr(dq_acc)
+            _lib.call('b200gdn_chunk_bwd', a, _stream(qb))
+        qd, kd, vd, gd, bd = in_dtypes
+        return dq.to(qd), dk.to(kd), dv.to(vd), dg.to(gd), dbeta.to(bd), None, dh0, None, None, None
+
+
+def chunk_gated_delta_rule(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    g: torch.Tensor,
+    beta: torch.Tensor,
+    scale: Optional[float] = None,
+    initial_state: Optional[torch.Tensor] = None,
+    output_final_state: bool = False,
+    use_qk_l2norm_in_kernel: bool = False,
+    use_beta_sigmoid_in_kernel: bool = False,
+    allow_neg_eigval: bool = False,
+    state_v_first: bool = False,
+    cu_seqlens: Optional[torch.Tensor] = None,
+    cu_seqlens_cpu: Optional[torch.Tensor] = None,
+    chunk_indices: Optional[torch.Tensor] = None,
+    cp_context=None,
+    **kwargs,
+):
+    r"""Chunked gated delta rule, same contract as the reference's ``chunk_gated_delta_rule``
+    (fla/ops/gated_delta_rule/chunk.py:395-593).
+
+    q, k ``[B,T,H,K]``; v ``[B,T,HV,V]`` (``HV % H == 0``: each q/k head serves ``HV/H`` value heads);
+    g, beta ``[B,T,HV]``; ``initial_state [N,HV,K,V]`` (``[N,HV,V,K]`` with ``state_v_first``);
+    ``cu_seqlens [N+1]`` for packed sequences (then ``B == 1``).  Returns ``(o [B,T,HV,V] in q.dtype,
+    final_state fp32 or None)``.  Keyword options ``use_gate_in_kernel``, ``A_log``, ``dt_bias``,
+    ``chunk_size`` (16/32/64 accepted; the result does not depend on it and 64 is always used) and the
+    deprecated ``transpose_state_layout`` are honoured; ``head_first`` raises as in the reference.
+    ``chunk_indices`` is accepted and ignored (the chunk tables are rebuilt from ``cu_seqlens``).
+    """
+    if 'transpose_state_layout' in kwargs:
+        if state_v_first:
+            raise ValueError("Cannot pass both `state_v_first` and the deprecated `transpose_state_layout`.")
+        warnings.warn("`transpose_state_layout` is deprecated and renamed to `state_v_first`.",
+                      DeprecationWarning, stacklevel=2)
+        state_v_first = kwargs.pop('transpose_state_layout')
+    if q.shape[2] != k.shape[2]:
+        raise ValueError(
+            f"q and k must have the same number of heads, "
+            f"but got q.shape[2]={q.shape[2]} and k.shape[2]={k.shape[2]}")
+    H, HV = q.shape[2], v.shape[2]
+    if HV % H != 0:
+        raise ValueError(
+            f"For GVA, num_v_heads (HV={HV}) must be evenly divisible by "
+            f"num_heads (H={H}), but got HV % H = {HV % H}")
+    if 'head_first' in kwargs:
+        raise DeprecationWarning("head_first has been removed. Inputs must be in `[B, T, H, ...]` format.")
+    chunk_size = kwargs.pop('chunk_size', 64)
+    if chunk_size not in (16, 32, 64):
+        raise ValueError(f"`chunk_size` must be 16, 32, or 64 for Gated Delta Rule, got {chunk_size}.")
+    if cp_context is not None:
+        assert initial_state is None, "Initial state is not supported for CP"
+        assert output_final_state is False, "Output final state is not supported for CP"
+        assert cp_context.cu_seqlens is not None, "cu_seqlens is required for CP"
+        cu_seqlens = cp_context.cu_seqlens
+        if cp_context.cu_seqlens_cpu is not None:
+            cu_seqlens_cpu = cp_context.cu_seqlens_cpu
+    if cu_seqlens is not None:
+        if q.shape[0] != 1:
+            raise ValueError(
+                f"The batch size is expected to be 1 rather than {q.shape[0]} when using `cu_seqlens`."
+                f"Please flatten variable-length inputs before processing.")
+        if initial_state is not None and initial_state.shape[0] != len(cu_seqlens) - 1:
+            raise ValueError(
+                f"The number of initial states is expected to be equal to the number of input sequences, "
+                f"i.e., {len(cu_seqlens) - 1} rather than {initial_state.shape[0]}.")
+    use_gate_in_kernel = kwargs.get('use_gate_in_kernel', False)
+    A_log = kwargs.get('A_log')
+    dt_bias = kwargs.get('dt_bias')
+    if use_gate_in_kernel:
+        assert A_log is not None, "A_log must be provided when use_gate_in_kernel=True."
+    if allow_neg_eigval and not use_beta_sigmoid_in_kernel:
+        raise ValueError("`allow_neg_eigval=True` requires `use_beta_sigmoid_in_kernel=True`.")
+    if scale is None:
+        scale = k.shape[-1] ** -0.5
+    if not q.is_cuda:
+        raise _lib.B200GDNError('chunk_gated_delta_rule runs on a CUDA device only (no CPU path)')
+    if (q.shape[-1], v.shape[-1]) not in _SUPPORTED_HEAD_DIMS:
+        raise _lib.B200GDNError(f'head dimensions K={q.shape[-1]}, V={v.shape[-1]} are not built; '
+                                f'supported: {_SUPPORTED_HEAD_DIMS}')
+
+    # The three options the layer turns on (fla/layers/gated_deltanet.py:309-325).  They are cheap
+    # element-wise pre-processing; torch autograd differentiates them.
+    if use_qk_l2norm_in_kernel:
+        q, k = _l2norm(q), _l2norm(k)
+    if use_beta_sigmoid_in_kernel:
+        beta = torch.sigmoid(beta.float()) * (2.0 if allow_neg_eigval else 1.0)
+    if use_gate_in_kernel:
+        g = _gate(g, A_log, dt_bias)
+    if state_v_first and initial_state is not None:
+        initial_state = initial_state.transpose(-1, -2)
+
+    if cp_context is not None and getattr(cp_context, 'group', None) is not None:
+        from .cp import chunk_gated_delta_rule_cp
+        o = chunk_gated_delta_rule_cp(q, k, v, g, beta, scale, cp_context)
+        return o, None
+
+    o, final_state = ChunkGatedDeltaRuleFunction.apply(
+        q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, cu_seqlens_cpu)
+    if final_state is not None and state_v_first:
+        final_state = final_state.transpose(-1, -2).contiguous()
+    return o, final_state
+
+
+chunk_gdn = chunk_gated_delta_rule

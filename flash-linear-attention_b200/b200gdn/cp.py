@@ -1,0 +1,307 @@
+"""Context parallelism for the chunked gated delta rule: one long packed batch split into equal
+contiguous token shards, one per rank (the semantics of fla/ops/cp/context.py and
+fla/ops/cp/chunk_delta_h.py).
+
+The state transition of a whole shard is affine, S_end = M S_start + h_ext with
+M = prod_c (2^gamma_last,c I - K~_c^T W_c).  Every rank computes (M, h_ext) of the part of its LAST local
+sequence with a zero start state, the pairs are exchanged, and each rank folds the pairs of the ranks that
+hold the earlier parts of its FIRST local sequence into that sequence's start state.  The backward pass
+mirrors this with (M^T, dh_ext) of each rank's first local sequence flowing towards lower ranks.
+All ranks therefore scan concurrently; the exchange is K*(K+V) fp32 per head and rank, independent of T.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .index import tables_for
+
+
+@dataclass
+class FLACPContext:
+    """Per-rank partition metadata; same fields as fla/ops/cp/context.py:22-57."""
+    group: Optional[object] = None
+    cu_seqlens: Optional[torch.Tensor] = None
+    cu_seqlens_cpu: Optional[torch.Tensor] = None
+    is_last_rank: Optional[bool] = None
+    pre_num_ranks: Optional[int] = None
+    is_first_rank: Optional[bool] = None
+    post_num_ranks: Optional[int] = None
+    conv1d_kernel_size: Optional[int] = None
+    pre_num_conv_tokens: Optional[int] = None
+
+    def copy_for_backward(self) -> 'FLACPContext':
+        return FLACPContext(
+            group=self.group,
+            cu_seqlens=None if self.cu_seqlens is None else self.cu_seqlens.clone(),
+            cu_seqlens_cpu=None if self.cu_seqlens_cpu is None else self.cu_seqlens_cpu.clone(),
+            is_last_rank=self.is_last_rank, pre_num_ranks=self.pre_num_ranks, is_first_rank=self.is_first_rank,
+            post_num_ranks=self.post_num_ranks, conv1d_kernel_size=self.conv1d_kernel_size,
+            pre_num_conv_tokens=self.pre_num_conv_tokens)
+
+    @property
+    def num_seqs(self) -> int:
+        return 0 if self.cu_seqlens is None else len(self.cu_seqlens) - 1
+
+    @property
+    def is_cp_enabled(self) -> bool:
+        return self.group is not None
+
+
+def get_cp_cu_seqlens(
+    cu_seqlens: torch.Tensor,
+    cu_seqlens_cpu: Optional[torch.Tensor] = None,
+    world_size: Optional[int] = None,
+    rank: Optional[int] = None,
+    group=None,
+    conv1d_kernel_size: Optional[int] = None,
+) -> FLACPContext:
+    """Partition a packed batch over ``world_size`` ranks (fla/ops/cp/context.py:60-160).
+
+    Rank r owns tokens [r*P, (r+1)*P), P = total/world_size (must divide).  Returns the rank's local
+    ``cu_seqlens`` (int32; global boundaries clipped to the interval) and how many lower / higher ranks
+    hold the earlier / later parts of its first / last local sequence.
+    """
+    if world_size is None:
+        assert group is not None
+        world_size = dist.get_world_size(group=group)
+        rank = dist.get_rank(group=group)
+    cpu = cu_seqlens_cpu if cu_seqlens_cpu is not None else cu_seqlens.cpu()
+    cu = [int(x) for x in cpu.tolist()]
+    total = cu[-1]
+    if total < world_size:
+        raise ValueError(
+            f"`total_tokens` ({total}) must be at least `world_size` ({world_size}) for context parallelism.")
+    if total % world_size != 0:
+        raise ValueError(
+            f"`total_tokens` ({total}) must be divisible by `world_size` ({world_size}) for context parallelism.")
+    part = total // world_size
+    lo, hi = part * rank, part * (rank + 1)
+    # sequences that overlap [lo, hi): end > lo and start < hi
+    seqs = [i for i in range(len(cu) - 1) if cu[i + 1] > lo and cu[i] < hi and cu[i + 1] > cu[i]]
+    first, last = seqs[0], seqs[-1]
+    local: List[int] = []
+    for b in cu[first:last + 2]:
+        x = min(max(b, lo), hi) - lo
+        if not local or local[-1] != x:
+            local.append(x)
+    first_start, last_end = cu[first], cu[last + 1]
+    first_rank_of_first = first_start // part
+    last_rank_of_last = (last_end - 1) // part
+    local_cpu = torch.tensor(local, dtype=torch.int32)
+    return FLACPContext(
+        group=group,
+        cu_seqlens=local_cpu.to(cu_seqlens.device, non_blocking=True),
+        cu_seqlens_cpu=local_cpu,
+        is_last_rank=rank == last_rank_of_last,
+        pre_num_ranks=rank - first_rank_of_first,
+        is_first_rank=rank == first_rank_of_first,
+        post_num_ranks=last_rank_of_last - rank,
+        conv1d_kernel_size=conv1d_kernel_size,
+        pre_num_conv_tokens=max(0, lo - first_start),
+    )
+
+
+def build_cp_context(cu_seqlens: torch.Tensor, group, conv1d_kernel_size: Optional[int] = None,
+                     cu_seqlens_cpu: Optional[torch.Tensor] = None) -> FLACPContext:
+    """fla/ops/cp/context.py:163-180."""
+    return get_cp_cu_seqlens(cu_seqlens, cu_seqlens_cpu=cu_seqlens_cpu, group=group,
+                             conv1d_kernel_size=conv1d_kernel_size)
+
+
+# ------------------------------------------------------------------------------ exchange and fold
+def exchange(local: torch.Tensor, group) -> torch.Tensor:
+    """All ranks contribute their [HV,K,K+V] fp32 pair, every rank receives [W,HV,K,K+V]
+    (fla/ops/cp/comm.py:19-41; ranks with nothing to send contribute zeros, like the reference)."""
+    world = dist.get_world_size(group=group)
+    out = torch.empty((world,) + tuple(local.shape), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(out, local.contiguous(), group=group)
+    return out
+
+
+def fold_prefix(gathered: torch.Tensor, rank: int, num: int, K: int, forward: bool,
+                apply: Callable[[torch.Tensor, torch.Tensor, torch.Tensor, bool], torch.Tensor]) -> Optional[torch.Tensor]:
+    """Compose the affine maps of the ``num`` neighbouring ranks.
+
+    forward:  x = 0; for j = rank-num .. rank-1:  x = M_j x + h_j      (start state of the first local sequence)
+    backward: x = 0; for j = rank+num .. rank+1:  x = M_j^T x + dh_j   (gradient at the end of the last local
+              sequence; the backward pairs already hold M^T, so no transpose is applied)
+    ``gathered[j] = [HV, K, K+V]`` with M in columns [0,K) and the state part in [K,K+V).
+    ``apply(M, x, b, transpose)`` returns M x + b.
+    """
+    if num <= 0:
+        return None
+    order = range(rank - num, rank) if forward else range(rank + num, rank, -1)
+    x = None
+    for j in order:
+        M = gathered[j, :, :, :K].contiguous()
+        b = gathered[j, :, :, K:].contiguous()
+        x = b if x is None else apply(M, x, b, False)
+    return x
+
+
+def _affine_apply(M: torch.Tensor, x: torch.Tensor, b: torch.Tensor, transpose: bool) -> torch.Tensor:
+    a = _lib.AffineArgs()
+    a.HV, a.K, a.V = M.shape[0], M.shape[1], x.shape[2]
+    a.transpose_m = int(transpose)
+    out = torch.empty_like(x)
+    a.M, a.x, a.b, a.out = M.data_ptr(), x.data_ptr(), _lib.ptr(b), out.data_ptr()
+    _lib.call('b200gdn_affine_apply', a, torch.cuda.current_stream(M.device).cuda_stream)
+    return out
+
+
+class ChunkGatedDeltaRuleCPFunction(torch.autograd.Function):
+    """Forward and backward of the op on one rank's shard, with the prefix exchange in between the
+    intra-chunk stage and the scan (fla/ops/gated_delta_rule/chunk.py:82-93, 183-200)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, scale, cp_context):
+        from .chunk import new_chunk_args, _stream
+        in_dtypes = (q.dtype, k.dtype, v.dtype, g.dtype, beta.dtype)
+        dev = q.device
+        group = cp_context.group
+        rank = dist.get_rank(group=group)
+        with torch.cuda.device(dev):
+            qb, kb, vb = (x.to(torch.bfloat16).contiguous() for x in (q, k, v))
+            gf, bf = g.float().contiguous(), beta.float().contiguous()
+            B, T, H, K = qb.shape
+            HV, V = vb.shape[2], vb.shape[3]
+            tables = tables_for(B, T, cp_context.cu_seqlens, cp_context.cu_seqlens_cpu, dev)
+            chunk_meta, seq_meta, (n_chunks, n_seq) = tables
+            rows = B * T
+            bf16 = dict(dtype=torch.bfloat16, device=dev)
+            f32 = dict(dtype=torch.float32, device=dev)
+            o = torch.empty(B, T, HV, V, **bf16)
+            gamma = torch.empty(rows, HV, **f32)
+            A = torch.empty(rows, HV, 64, **bf16)
+            w = torch.empty(rows, HV, K, **bf16)
+            u = torch.empty(rows, HV, V, **bf16)
+            h = torch.empty(n_chunks, HV, K, V, **bf16)
+            v_new = torch.empty(rows, HV, V, **bf16)
+            st = _stream(qb)
+
+            a = new_chunk_args(qb, kb, vb, scale, tables)
+            a.g, a.beta = gf.data_ptr(), bf.data_ptr()
+            a.gamma, a.A, a.w, a.u = gamma.data_ptr(), A.data_ptr(), w.data_ptr(), u.data_ptr()
+            a.stage_mask = _lib.FWD_INTRA
+            _lib.call('b200gdn_chunk_fwd', a, st)
+
+            # (M, h_ext) of the last local sequence, zero start state; zeros when nothing continues
+            hm = torch.zeros(HV, K, K + V, **f32)
+            if not cp_context.is_last_rank:
+                last = seq_meta[n_seq - 1:n_seq]
+                h_ext = torch.empty(1, HV, K, V, **f32)
+                p = new_chunk_args(qb, kb, vb, scale, (chunk_meta, last, (n_chunks, 1)))
+                p.gamma, p.w, p.u, p.ht = gamma.data_ptr(), w.data_ptr(), u.data_ptr(), h_ext.data_ptr()
+                p.stage_mask = _lib.FWD_SCAN
+                _lib.call('b200gdn_chunk_fwd', p, st)
+                eye = torch.eye(K, **f32).expand(1, HV, K, K).contiguous()
+                M = torch.empty(1, HV, K, K, **f32)
+                p = new_chunk_args(qb, kb, vb, scale, (chunk_meta, last, (n_chunks, 1)))
+                p.V = K
+                p.gamma, p.w, p.h0, p.ht = gamma.data_ptr(), w.data_ptr(), eye.data_ptr(), M.data_ptr()
+                p.stage_mask = _lib.FWD_SCAN
+                _lib.call('b200gdn_chunk_fwd', p, st)
+                hm[:, :, :K] = M[0]
+                hm[:, :, K:] = h_ext[0]
+            gathered = exchange(hm, group)
+            h0_first = fold_prefix(gathered, rank, cp_context.pre_num_ranks, K, True, _affine_apply)
+            h0 = None
+            if h0_first is not None:
+                h0 = torch.zeros(n_seq, HV, K, V, **f32)
+                h0[0] = h0_first
+
+            a.h0 = _lib.ptr(h0)
+            a.q = qb.data_ptr()
+            a.h, a.v_new, a.o = h.data_ptr(), v_new.data_ptr(), o.data_ptr()
+            a.stage_mask = _lib.FWD_SCAN | _lib.FWD_OUT
+            _lib.call('b200gdn_chunk_fwd', a, st)
+        ctx.save_for_backward(qb, kb, vb, bf, gamma, A, w, h, v_new, chunk_meta, seq_meta)
+        ctx.meta = (scale, n_chunks, n_seq, in_dtypes)
+        ctx.cp_context = cp_context
+        return o.to(q.dtype)
+
+    @staticmethod
+    def backward(ctx, do):
+        from .chunk import new_chunk_args, _stream
+        qb, kb, vb, bf, gamma, A, w, h, v_new, chunk_meta, seq_meta = ctx.saved_tensors
+        scale, n_chunks, n_seq, in_dtypes = ctx.meta
+        cp_context = ctx.cp_context
+        group = cp_context.group
+        rank = dist.get_rank(group=group)
+        dev = qb.device
+        with torch.cuda.device(dev):
+            B, T, H, K = qb.shape
+            HV, V = vb.shape[2], vb.shape[3]
+            rows = B * T
+            dob = do.to(torch.bfloat16).contiguous()
+            bf16 = dict(dtype=torch.bfloat16, device=dev)
+            f32 = dict(dtype=torch.float32, device=dev)
+            dq = torch.empty(B, T, H, K, **bf16)
+            dk = torch.empty(B, T, H, K, **bf16)
+            dv = torch.empty(B, T, HV, V, **bf16)
+            dg = torch.empty(B, T, HV, **f32)
+            dbeta = torch.empty(B, T, HV, **f32)
+            dh = torch.empty(n_chunks, HV, K, V, **bf16)
+            dv2 = torch.empty(rows, HV, V, **bf16)
+            dw = torch.empty(rows, HV, K, **bf16)
+            dk_part = torch.empty(rows, H, K, **f32)
+            dG = torch.empty(rows, HV, **f32)
+            dq_acc = torch.empty(rows, H, K, **f32) if HV > H else None
+            st = _stream(qb)
+            tables = (chunk_meta, seq_meta, (n_chunks, n_seq))
+
+            a = new_chunk_args(qb, kb, vb, scale, tables)
+            a.beta, a.gamma, a.A, a.w, a.h, a.v_new = (x.data_ptr() for x in (bf, gamma, A, w, h, v_new))
+            a.d_o = dob.data_ptr()
+            a.dq, a.dk, a.dv, a.dg, a.dbeta = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dg.data_ptr(), dbeta.data_ptr()
+            a.dh, a.dv2, a.dw, a.dk_part, a.dG, a.dq_acc = dh.data_ptr(), dv2.data_ptr(), dw.data_ptr(), \
+                dk_part.data_ptr(), dG.data_ptr(), _lib.ptr(dq_acc)
+            a.stage_mask = _lib.BWD_DVLOCAL
+            _lib.call('b200gdn_chunk_bwd', a, st)
+
+            # (M^T, dh_ext) of the first local sequence, zero end gradient; zeros when nothing precedes
+            dhm = torch.zeros(HV, K, K + V, **f32)
+            if not cp_context.is_first_rank:
+                first = seq_meta[0:1]
+                len0 = int(cp_context.cu_seqlens_cpu[1])
+                tmp = dv2[:len0].clone()            # the scan completes dv2 in place; keep dv_local intact
+                dh_ext = torch.empty(1, HV, K, V, **f32)
+                p = new_chunk_args(qb, kb, vb, scale, (chunk_meta, first, (n_chunks, 1)))
+                p.gamma, p.w, p.d_o, p.dv2, p.dh0 = gamma.data_ptr(), w.data_ptr(), dob.data_ptr(), tmp.data_ptr(), \
+                    dh_ext.data_ptr()
+                p.stage_mask = _lib.BWD_SCAN
+                _lib.call('b200gdn_chunk_bwd', p, st)
+                eye = torch.eye(K, **f32).expand(1, HV, K, K).contiguous()
+                zeros = torch.zeros(len0, HV, K, **bf16)
+                dM = torch.empty(1, HV, K, K, **f32)
+                p = new_chunk_args(qb, kb, vb, scale, (chunk_meta, first, (n_chunks, 1)))
+                p.V = K
+                p.gamma, p.w, p.dv2, p.dht, p.dh0 = gamma.data_ptr(), w.data_ptr(), zeros.data_ptr(), eye.data_ptr(), \
+                    dM.data_ptr()
+                p.stage_mask = _lib.BWD_SCAN
+                _lib.call('b200gdn_chunk_bwd', p, st)
+                dhm[:, :, :K] = dM[0]
+                dhm[:, :, K:] = dh_ext[0]
+            gathered = exchange(dhm, group)
+            dht_last = fold_prefix(gathered, rank, cp_context.post_num_ranks, K, False, _affine_apply)
+            dht = None
+            if dht_last is not None:
+                dht = torch.zeros(n_seq, HV, K, V, **f32)
+                dht[n_seq - 1] = dht_last
+            a.dht = _lib.ptr(dht)
+            a.stage_mask = _lib.BWD_SCAN | _lib.BWD_DQKWG | _lib.BWD_WY
+            _lib.call('b200gdn_chunk_bwd', a, st)
+        qd, kd, vd, gd, bd = in_dtypes
+        return dq.to(qd), dk.to(kd), dv.to(vd), dg.to(gd), dbeta.to(bd), None, None
+
+
+def chunk_gated_delta_rule_cp(q, k, v, g, beta, scale, cp_context: FLACPContext) -> torch.Tensor:
+    """The op on this rank's shard ``[1, T/W, ...]``; inputs are already pre-processed (l2norm, gate, beta)."""
+    if q.shape[0] != 1:
+        raise ValueError('context parallelism expects a packed batch with B == 1')
+    return ChunkGatedDeltaRuleCPFunction.apply(q, k, v, g, beta, scale, cp_context)

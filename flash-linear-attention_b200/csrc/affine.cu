@@ -1,0 +1,69 @@
+// out = M x + b (or M^T x + b) per head, fp32: folds a received state prefix through a shard's K x K
+// transition matrix for context parallelism (merge step of fla/ops/cp/chunk_delta_h.py:332-460).
+// Tiny (2 K^2 V flop per head), so a plain shared-memory tiled fp32 kernel: exact fp32 keeps the
+// chained prefix as accurate as the reference's fp32 merge.
+#include "gdn_common.cuh"
+
+namespace gdn {
+namespace {
+
+constexpr int TM = 64, TN = 64, TK = 16;
+
+__global__ void __launch_bounds__(256) affine_kernel(const b200gdn_affine_args a) {
+  __shared__ float Ms[TK][TM + 1];
+  __shared__ float Xs[TK][TN + 1];
+  const int hv = blockIdx.z, i0 = blockIdx.y * TM, j0 = blockIdx.x * TN;
+  const int K = a.K, V = a.V;
+  const float* M = a.M + (int64_t)hv * K * K;
+  const float* x = a.x + (int64_t)hv * K * V;
+  const int tid = threadIdx.x, ty = tid / 16, tx = tid % 16;
+  float acc[4][4] = {};
+  for (int m0 = 0; m0 < K; m0 += TK) {
+    for (int idx = tid; idx < TK * TM; idx += 256) {
+      int mm = idx / TM, ii = idx % TM;
+      int gi = i0 + ii, gm = m0 + mm;
+      float val = 0.f;
+      if (gi < K && gm < K) val = a.transpose_m ? M[(int64_t)gm * K + gi] : M[(int64_t)gi * K + gm];
+      Ms[mm][ii] = val;
+    }
+    for (int idx = tid; idx < TK * TN; idx += 256) {
+      int mm = idx / TN, jj = idx % TN;
+      int gm = m0 + mm, gj = j0 + jj;
+      Xs[mm][jj] = (gm < K && gj < V) ? x[(int64_t)gm * V + gj] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int mm = 0; mm < TK; ++mm) {
+      float am[4], bx[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) am[r] = Ms[mm][ty * 4 + r];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) bx[c] = Xs[mm][tx * 4 + c];
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[r][c] += am[r] * bx[c];
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      int gi = i0 + ty * 4 + r, gj = j0 + tx * 4 + c;
+      if (gi < K && gj < V) {
+        int64_t o = (int64_t)hv * K * V + (int64_t)gi * V + gj;
+        a.out[o] = acc[r][c] + (a.b ? a.b[o] : 0.f);
+      }
+    }
+}
+
+}  // namespace
+
+int launch_affine(const b200gdn_affine_args& a, cudaStream_t st) {
+  dim3 grid((a.V + TN - 1) / TN, (a.K + TM - 1) / TM, a.HV);
+  affine_kernel<<<grid, 256, 0, st>>>(a);
+  return check_launch("affine_apply");
+}
+
+}  // namespace gdn

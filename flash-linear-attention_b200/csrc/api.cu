@@ -1,0 +1,160 @@
+// C ABI of the library (declared in include/b200gdn.h): argument checks, stage sequencing, error text.
+#include <cstdarg>
+#include <cstdio>
+
+#include "gdn_common.cuh"
+
+namespace gdn {
+
+static thread_local char g_err[512] = "";
+static thread_local int g_launches = 0;
+
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(B200GDN_ERR_CUDA, "%s launch: %s", what, cudaGetErrorString(e));
+  ++g_launches;
+  return 0;
+}
+
+static int check_chunk_args(const b200gdn_chunk_args* a, const char* who) {
+  if (a == nullptr) return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: args is NULL", who);
+  if (a->struct_bytes != (int32_t)sizeof(b200gdn_chunk_args))
+    return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: struct_bytes %d != %zu (ABI mismatch)", who, a->struct_bytes,
+                     sizeof(b200gdn_chunk_args));
+  if (a->rows <= 0 || a->H <= 0 || a->HV <= 0 || a->n_seq <= 0 || a->n_chunks <= 0)
+    return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: empty problem (rows=%d H=%d HV=%d n_seq=%d n_chunks=%d)", who, a->rows,
+                     a->H, a->HV, a->n_seq, a->n_chunks);
+  if (a->HV % a->H != 0) return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: HV=%d not a multiple of H=%d", who, a->HV, a->H);
+  if (a->chunk_meta == nullptr || a->seq_meta == nullptr)
+    return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: chunk tables missing", who);
+  if (a->HV > 65535 || a->n_seq > 65535)
+    return set_error(B200GDN_ERR_UNSUPPORTED, "%s: HV and n_seq are grid y/z dimensions (<= 65535)", who);
+  return 0;
+}
+
+#define REQUIRE(ptr, who)                                                                  \
+  if ((ptr) == nullptr) return gdn::set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: %s is NULL", who, #ptr)
+
+}  // namespace gdn
+
+extern "C" {
+
+int b200gdn_chunk_fwd(const b200gdn_chunk_args* a, void* stream) {
+  using namespace gdn;
+  g_launches = 0;
+  if (int e = check_chunk_args(a, "chunk_fwd")) return e;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const uint32_t m = a->stage_mask ? a->stage_mask : (B200GDN_FWD_INTRA | B200GDN_FWD_SCAN | B200GDN_FWD_OUT);
+  if (m & B200GDN_FWD_INTRA) {
+    REQUIRE(a->k, "chunk_fwd"); REQUIRE(a->v, "chunk_fwd"); REQUIRE(a->g, "chunk_fwd"); REQUIRE(a->beta, "chunk_fwd");
+    REQUIRE(a->gamma, "chunk_fwd"); REQUIRE(a->A, "chunk_fwd"); REQUIRE(a->w, "chunk_fwd"); REQUIRE(a->u, "chunk_fwd");
+    if (int e = launch_intra_fwd(*a, st)) return e;
+  }
+  if (m & B200GDN_FWD_SCAN) {
+    REQUIRE(a->k, "chunk_fwd"); REQUIRE(a->w, "chunk_fwd"); REQUIRE(a->gamma, "chunk_fwd");
+    if (int e = launch_scan_fwd(*a, st)) return e;
+  }
+  if (m & B200GDN_FWD_OUT) {
+    REQUIRE(a->q, "chunk_fwd"); REQUIRE(a->k, "chunk_fwd"); REQUIRE(a->v_new, "chunk_fwd"); REQUIRE(a->h, "chunk_fwd");
+    REQUIRE(a->gamma, "chunk_fwd"); REQUIRE(a->o, "chunk_fwd");
+    if (int e = launch_out_fwd(*a, st)) return e;
+  }
+  return 0;
+}
+
+int b200gdn_chunk_bwd(const b200gdn_chunk_args* a, void* stream) {
+  using namespace gdn;
+  g_launches = 0;
+  if (int e = check_chunk_args(a, "chunk_bwd")) return e;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const uint32_t m =
+      a->stage_mask ? a->stage_mask : (B200GDN_BWD_DVLOCAL | B200GDN_BWD_SCAN | B200GDN_BWD_DQKWG | B200GDN_BWD_WY);
+  if (m & B200GDN_BWD_DVLOCAL) {
+    REQUIRE(a->q, "chunk_bwd"); REQUIRE(a->k, "chunk_bwd"); REQUIRE(a->gamma, "chunk_bwd"); REQUIRE(a->d_o, "chunk_bwd");
+    REQUIRE(a->dv2, "chunk_bwd");
+    if (int e = launch_dv_local(*a, st)) return e;
+  }
+  if (m & B200GDN_BWD_SCAN) {
+    REQUIRE(a->q, "chunk_bwd"); REQUIRE(a->k, "chunk_bwd"); REQUIRE(a->w, "chunk_bwd"); REQUIRE(a->gamma, "chunk_bwd");
+    REQUIRE(a->dv2, "chunk_bwd");
+    if (int e = launch_scan_bwd(*a, st)) return e;
+  }
+  if (m & B200GDN_BWD_DQKWG) {
+    REQUIRE(a->q, "chunk_bwd"); REQUIRE(a->k, "chunk_bwd"); REQUIRE(a->v_new, "chunk_bwd"); REQUIRE(a->gamma, "chunk_bwd");
+    REQUIRE(a->h, "chunk_bwd"); REQUIRE(a->dh, "chunk_bwd"); REQUIRE(a->dv2, "chunk_bwd"); REQUIRE(a->d_o, "chunk_bwd");
+    REQUIRE(a->dq, "chunk_bwd"); REQUIRE(a->dk_part, "chunk_bwd"); REQUIRE(a->dw, "chunk_bwd"); REQUIRE(a->dG, "chunk_bwd");
+    if (int e = launch_dqkwg(*a, st)) return e;
+  }
+  if (m & B200GDN_BWD_WY) {
+    REQUIRE(a->k, "chunk_bwd"); REQUIRE(a->v, "chunk_bwd"); REQUIRE(a->beta, "chunk_bwd"); REQUIRE(a->gamma, "chunk_bwd");
+    REQUIRE(a->A, "chunk_bwd"); REQUIRE(a->dw, "chunk_bwd"); REQUIRE(a->dv2, "chunk_bwd"); REQUIRE(a->dk_part, "chunk_bwd");
+    REQUIRE(a->dG, "chunk_bwd"); REQUIRE(a->dk, "chunk_bwd"); REQUIRE(a->dv, "chunk_bwd"); REQUIRE(a->dg, "chunk_bwd");
+    REQUIRE(a->dbeta, "chunk_bwd");
+    if (int e = launch_wy_bwd(*a, st)) return e;
+  }
+  return 0;
+}
+
+int b200gdn_recurrent_fwd(const b200gdn_recurrent_args* a, void* stream) {
+  using namespace gdn;
+  g_launches = 0;
+  if (a == nullptr) return set_error(B200GDN_ERR_BAD_ARGUMENT, "recurrent_fwd: args is NULL");
+  if (a->struct_bytes != (int32_t)sizeof(b200gdn_recurrent_args))
+    return set_error(B200GDN_ERR_BAD_ARGUMENT, "recurrent_fwd: struct_bytes %d != %zu (ABI mismatch)", a->struct_bytes,
+                     sizeof(b200gdn_recurrent_args));
+  if (a->B <= 0 || a->T <= 0 || a->H <= 0 || a->HV <= 0 || a->n_seq <= 0 || a->HV % a->H != 0)
+    return set_error(B200GDN_ERR_BAD_ARGUMENT, "recurrent_fwd: bad sizes B=%d T=%d H=%d HV=%d n_seq=%d", a->B, a->T, a->H,
+                     a->HV, a->n_seq);
+  if (a->qkv_dtype < 0 || a->qkv_dtype > 2) return set_error(B200GDN_ERR_BAD_ARGUMENT, "recurrent_fwd: qkv_dtype %d", a->qkv_dtype);
+  if (a->HV > 65535 || a->n_seq > 65535)
+    return set_error(B200GDN_ERR_UNSUPPORTED, "recurrent_fwd: HV and n_seq are grid dimensions (<= 65535)");
+  REQUIRE(a->q, "recurrent_fwd"); REQUIRE(a->k, "recurrent_fwd"); REQUIRE(a->v, "recurrent_fwd");
+  REQUIRE(a->beta, "recurrent_fwd"); REQUIRE(a->o, "recurrent_fwd");
+  return launch_recurrent(*a, static_cast<cudaStream_t>(stream));
+}
+
+int b200gdn_affine_apply(const b200gdn_affine_args* a, void* stream) {
+  using namespace gdn;
+  g_launches = 0;
+  if (a == nullptr) return set_error(B200GDN_ERR_BAD_ARGUMENT, "affine_apply: args is NULL");
+  if (a->struct_bytes != (int32_t)sizeof(b200gdn_affine_args))
+    return set_error(B200GDN_ERR_BAD_ARGUMENT, "affine_apply: struct_bytes %d != %zu (ABI mismatch)", a->struct_bytes,
+                     sizeof(b200gdn_affine_args));
+  if (a->HV <= 0 || a->K <= 0 || a->V <= 0) return set_error(B200GDN_ERR_BAD_ARGUMENT, "affine_apply: bad sizes");
+  REQUIRE(a->M, "affine_apply"); REQUIRE(a->x, "affine_apply"); REQUIRE(a->out, "affine_apply");
+  return launch_affine(*a, static_cast<cudaStream_t>(stream));
+}
+
+int64_t b200gdn_saved_bytes(int32_t rows, int32_t H, int32_t HV, int32_t K, int32_t V, int32_t n_chunks) {
+  (void)H;
+  int64_t r = rows, hv = HV;
+  return r * hv * 4                      /* gamma */
+         + r * hv * 64 * 2               /* A */
+         + r * hv * K * 2                /* w */
+         + r * hv * V * 2 * 2            /* u, v_new */
+         + (int64_t)n_chunks * hv * K * V * 2; /* h */
+}
+
+int64_t b200gdn_bwd_workspace_bytes(int32_t rows, int32_t H, int32_t HV, int32_t K, int32_t V, int32_t n_chunks) {
+  int64_t r = rows, hv = HV;
+  return (int64_t)n_chunks * hv * K * V * 2 /* dh */
+         + r * hv * V * 2                    /* dv2 */
+         + r * hv * K * 2                    /* dw */
+         + r * H * K * 4                     /* dk_part */
+         + r * hv * 4                        /* dG */
+         + (HV > H ? r * H * K * 4 : 0);     /* dq_acc */
+}
+
+int b200gdn_last_launch_count(void) { return gdn::g_launches; }
+int b200gdn_abi_version(void) { return B200GDN_ABI_VERSION; }
+const char* b200gdn_last_error(void) { return gdn::g_err; }
+
+}  // extern "C"

@@ -1,0 +1,284 @@
+// Shared device helpers for the gated-delta-rule kernels (sm_100a).
+//
+// Tiles are 64 tokens (one chunk) by a head dimension, staged in shared memory as bf16 with a row
+// stride of (cols + 8) elements so that the eight 16-byte rows an ldmatrix touches fall in distinct
+// banks.  Warp-level contractions use mma.sync m16n8k16 (bf16 in, fp32 accumulate); operand
+// fragments are fetched with ldmatrix, transposed by the instruction where the contraction needs
+// the other major-ness, never by a physical transpose.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b200gdn.h"
+
+namespace gdn {
+
+constexpr int BT = 64;
+constexpr int PAD = 8;  // bf16 elements of row padding
+
+struct ChunkMeta {
+  int seq, row, len, local;
+};
+
+__device__ __forceinline__ ChunkMeta load_chunk_meta(const int32_t* chunk_meta, int c) {
+  int4 m = reinterpret_cast<const int4*>(chunk_meta)[c];
+  return ChunkMeta{m.x, m.y, m.z, m.w};
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ---- async global -> shared copies (16 bytes; zero-fill when !pred) -------------------------------
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool pred) {
+  uint32_t s = smem_u32(smem);
+  int bytes = pred ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+// Copy a [64][COLS] bf16 tile (global row stride `gstride` elements) into shared memory with row
+// stride COLS+PAD; rows >= valid are zero-filled.  `src` points at (first row, first column).
+template <int COLS, int NTHREADS>
+__device__ __forceinline__ void load_tile_async(__nv_bfloat16* dst, const __nv_bfloat16* src, int64_t gstride,
+                                                int valid, int tid) {
+  constexpr int CPR = COLS / 8;  // 16-byte chunks per row
+  constexpr int TOTAL = BT * CPR;
+  static_assert(TOTAL % NTHREADS == 0, "tile/threads mismatch");
+#pragma unroll
+  for (int it = 0; it < TOTAL / NTHREADS; ++it) {
+    int idx = it * NTHREADS + tid;
+    int r = idx / CPR, c = idx % CPR;
+    bool ok = r < valid;
+    const __nv_bfloat16* g = src + (ok ? (int64_t)r * gstride : 0) + c * 8;
+    cp_async16(dst + r * (COLS + PAD) + c * 8, g, ok);
+  }
+}
+
+// Same for a [ROWS][COLS] tile that is always fully valid (state snapshots).
+template <int ROWS, int COLS, int NTHREADS>
+__device__ __forceinline__ void load_rows_async(__nv_bfloat16* dst, const __nv_bfloat16* src, int64_t gstride,
+                                                int tid) {
+  constexpr int CPR = COLS / 8;
+  constexpr int TOTAL = ROWS * CPR;
+  static_assert(TOTAL % NTHREADS == 0, "tile/threads mismatch");
+#pragma unroll
+  for (int it = 0; it < TOTAL / NTHREADS; ++it) {
+    int idx = it * NTHREADS + tid;
+    int r = idx / CPR, c = idx % CPR;
+    cp_async16(dst + r * (COLS + PAD) + c * 8, src + (int64_t)r * gstride + c * 8, true);
+  }
+}
+
+// Write a [ROWS][COLS] bf16 tile from shared memory (row stride COLS+PAD) to global, 16 bytes per
+// thread and access, rows < valid only.
+template <int ROWS, int COLS, int NTHREADS>
+__device__ __forceinline__ void store_tile(__nv_bfloat16* dst, int64_t gstride, const __nv_bfloat16* src, int valid,
+                                           int tid) {
+  constexpr int CPR = COLS / 8;
+  constexpr int TOTAL = ROWS * CPR;
+  static_assert(TOTAL % NTHREADS == 0, "tile/threads mismatch");
+#pragma unroll
+  for (int it = 0; it < TOTAL / NTHREADS; ++it) {
+    int idx = it * NTHREADS + tid;
+    int r = idx / CPR, c = idx % CPR;
+    if (r < valid) {
+      uint4 val = *reinterpret_cast<const uint4*>(src + r * (COLS + PAD) + c * 8);
+      *reinterpret_cast<uint4*>(dst + (int64_t)r * gstride + c * 8) = val;
+    }
+  }
+}
+
+// ---- fragments -------------------------------------------------------------------------------------
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+// A fragment (16 rows x 16 k) of a row-major operand As[m][k]; `p` points at (m0, k0).
+__device__ __forceinline__ void load_a(uint32_t (&a)[4], const __nv_bfloat16* p, int ld, int lane) {
+  ldsm_x4(a, smem_u32(p + (lane & 15) * ld + ((lane >> 4) << 3)));
+}
+// A fragment of an operand stored transposed, As[k][m]; `p` points at (k0, m0).
+__device__ __forceinline__ void load_a_t(uint32_t (&a)[4], const __nv_bfloat16* p, int ld, int lane) {
+  ldsm_x4_t(a, smem_u32(p + ((lane & 7) + ((lane >> 4) << 3)) * ld + (((lane >> 3) & 1) << 3)));
+}
+// B fragments for two adjacent n-tiles (16 k x 16 n) of an operand stored Bs[n][k]; `p` at (n0, k0).
+// b[0],b[1] feed n-tile 0 and b[2],b[3] n-tile 1.
+__device__ __forceinline__ void load_b_nk(uint32_t (&b)[4], const __nv_bfloat16* p, int ld, int lane) {
+  ldsm_x4(b, smem_u32(p + ((lane & 7) + ((lane >> 4) << 3)) * ld + (((lane >> 3) & 1) << 3)));
+}
+// B fragments for two adjacent n-tiles of an operand stored Bs[k][n]; `p` at (k0, n0).
+__device__ __forceinline__ void load_b_kn(uint32_t (&b)[4], const __nv_bfloat16* p, int ld, int lane) {
+  ldsm_x4_t(b, smem_u32(p + ((lane & 7) + (((lane >> 3) & 1) << 3)) * ld + ((lane >> 4) << 3)));
+}
+
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float2 unpack_bf16(uint32_t v) {
+  __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(&v);
+  return __bfloat1622float2(b);
+}
+
+enum class AMajor { Row, Trans };
+enum class BMajor { NK, KN };
+
+// acc[NT][4] += A(16 x 16*KS) * B(16*KS x 8*NT) for one warp.
+//  AMajor::Row   : As[m][k], pa -> (m0, 0)        AMajor::Trans : As[k][m], pa -> (0, m0)
+//  BMajor::NK    : Bs[n][k], pb -> (n0, 0)        BMajor::KN    : Bs[k][n], pb -> (0, n0)
+// NEG_A flips the sign of A (both bf16 halves) so that the product is subtracted.
+template <int NT, int KS, AMajor AM, BMajor BM, bool NEG_A = false>
+__device__ __forceinline__ void warp_mma(float (&acc)[NT][4], const __nv_bfloat16* pa, int lda, const __nv_bfloat16* pb,
+                                         int ldb, int lane) {
+  static_assert(NT % 2 == 0, "n-tiles come in pairs");
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    uint32_t a[4];
+    if (AM == AMajor::Row)
+      load_a(a, pa + ks * 16, lda, lane);
+    else
+      load_a_t(a, pa + ks * 16 * lda, lda, lane);
+    if (NEG_A) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] ^= 0x80008000u;
+    }
+#pragma unroll
+    for (int np = 0; np < NT / 2; ++np) {
+      uint32_t b[4];
+      if (BM == BMajor::NK)
+        load_b_nk(b, pb + np * 16 * ldb + ks * 16, ldb, lane);
+      else
+        load_b_kn(b, pb + ks * 16 * ldb + np * 16, ldb, lane);
+      mma16816(acc[2 * np], a, b[0], b[1]);
+      mma16816(acc[2 * np + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+// Same with the A operand already in registers as KS fragments (a 16 x 16*KS bf16 matrix that was
+// produced by a previous accumulator: see acc_to_afrag).
+template <int NT, int KS, BMajor BM>
+__device__ __forceinline__ void warp_mma_ra(float (&acc)[NT][4], const uint32_t (&afrag)[KS][4],
+                                            const __nv_bfloat16* pb, int ldb, int lane) {
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+    for (int np = 0; np < NT / 2; ++np) {
+      uint32_t b[4];
+      if (BM == BMajor::NK)
+        load_b_nk(b, pb + np * 16 * ldb + ks * 16, ldb, lane);
+      else
+        load_b_kn(b, pb + ks * 16 * ldb + np * 16, ldb, lane);
+      mma16816(acc[2 * np], afrag[ks], b[0], b[1]);
+      mma16816(acc[2 * np + 1], afrag[ks], b[2], b[3]);
+    }
+  }
+}
+
+// A 16 x (8*NT) fp32 accumulator, rounded to bf16, is exactly the A operand (16 x 16*(NT/2)) of the
+// next contraction: thread (g = lane/4, t = lane%4) holds rows g, g+8 and columns 2t, 2t+1 of every
+// n-tile, which is the m16n8k16 A layout when two n-tiles are paired.
+template <int NT>
+__device__ __forceinline__ void acc_to_afrag(uint32_t (&afrag)[NT / 2][4], const float (&acc)[NT][4]) {
+#pragma unroll
+  for (int ks = 0; ks < NT / 2; ++ks) {
+    afrag[ks][0] = pack_bf16(acc[2 * ks][0], acc[2 * ks][1]);
+    afrag[ks][1] = pack_bf16(acc[2 * ks][2], acc[2 * ks][3]);
+    afrag[ks][2] = pack_bf16(acc[2 * ks + 1][0], acc[2 * ks + 1][1]);
+    afrag[ks][3] = pack_bf16(acc[2 * ks + 1][2], acc[2 * ks + 1][3]);
+  }
+}
+
+// Store a warp's 16 x (8*NT) accumulator as bf16 into a shared tile; `p` points at (m0, n0).
+template <int NT>
+__device__ __forceinline__ void acc_to_smem(__nv_bfloat16* p, int ld, const float (&acc)[NT][4], int lane) {
+  int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    *reinterpret_cast<uint32_t*>(p + g * ld + nt * 8 + 2 * t) = pack_bf16(acc[nt][0], acc[nt][1]);
+    *reinterpret_cast<uint32_t*>(p + (g + 8) * ld + nt * 8 + 2 * t) = pack_bf16(acc[nt][2], acc[nt][3]);
+  }
+}
+
+template <int NT>
+__device__ __forceinline__ void zero_acc(float (&acc)[NT][4]) {
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+  }
+}
+
+// Row-wise dot of a warp's accumulator with a bf16 shared tile at the same coordinates:
+// r_lo = sum_n acc(g, n) * T(g, n), r_hi for row g+8; complete after the quad reduction.
+template <int NT>
+__device__ __forceinline__ void row_dot(float& r_lo, float& r_hi, const float (&acc)[NT][4], const __nv_bfloat16* p,
+                                        int ld, int lane) {
+  int g = lane >> 2, t = lane & 3;
+  float lo = 0.f, hi = 0.f;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    float2 a = unpack_bf16(*reinterpret_cast<const uint32_t*>(p + g * ld + nt * 8 + 2 * t));
+    float2 b = unpack_bf16(*reinterpret_cast<const uint32_t*>(p + (g + 8) * ld + nt * 8 + 2 * t));
+    lo += acc[nt][0] * a.x + acc[nt][1] * a.y;
+    hi += acc[nt][2] * b.x + acc[nt][3] * b.y;
+  }
+  lo += __shfl_xor_sync(0xffffffffu, lo, 1);
+  lo += __shfl_xor_sync(0xffffffffu, lo, 2);
+  hi += __shfl_xor_sync(0xffffffffu, hi, 1);
+  hi += __shfl_xor_sync(0xffffffffu, hi, 2);
+  r_lo = lo;
+  r_hi = hi;
+}
+
+// gamma of a chunk into shared memory; rows past the valid length repeat the last valid value so
+// that 2^(gamma_last - gamma_i) is 1 there.
+__device__ __forceinline__ void load_gamma(float* gs, const float* gamma, int row0, int len, int HV, int hv, int tid) {
+  if (tid < BT) {
+    int r = tid < len ? tid : len - 1;
+    gs[tid] = gamma[(int64_t)(row0 + r) * HV + hv];
+  }
+}
+
+}  // namespace gdn
+
+// ---- host-side launch plumbing (one translation unit per kernel, collected by api.cu) ---------------
+namespace gdn {
+int launch_intra_fwd(const b200gdn_chunk_args& a, cudaStream_t st);
+int launch_scan_fwd(const b200gdn_chunk_args& a, cudaStream_t st);
+int launch_out_fwd(const b200gdn_chunk_args& a, cudaStream_t st);
+int launch_dv_local(const b200gdn_chunk_args& a, cudaStream_t st);
+int launch_scan_bwd(const b200gdn_chunk_args& a, cudaStream_t st);
+int launch_dqkwg(const b200gdn_chunk_args& a, cudaStream_t st);
+int launch_wy_bwd(const b200gdn_chunk_args& a, cudaStream_t st);
+int launch_recurrent(const b200gdn_recurrent_args& a, cudaStream_t st);
+int launch_affine(const b200gdn_affine_args& a, cudaStream_t st);
+int set_error(int code, const char* fmt, ...);
+int check_launch(const char* what);
+
+template <typename Kern>
+int ensure_smem(Kern kern, size_t bytes) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e != cudaSuccess) return set_error(B200GDN_ERR_CUDA, "cudaFuncSetAttribute(%zu B): %s", bytes, cudaGetErrorString(e));
+  return 0;
+}
+}  // namespace gdn

@@ -1,0 +1,160 @@
+/*
+ * b200gdn — C ABI of the B200 (sm_100a) gated-delta-rule kernels.
+ *
+ * The reference (fla-org/flash-linear-attention 0.5.2) has no native ABI: its kernels are Triton
+ * functions launched from Python.  Each entry point below replaces one Python-level orchestration
+ * function of the reference; a backend plugin (fla/ops/backends/__init__.py:33-88, BaseBackend) or
+ * any other host binds these symbols with ctypes / cffi / dlopen.
+ *
+ * Conventions
+ *  - plain C: raw device pointers, 32-bit sizes, no torch types, no exceptions, no allocation
+ *    (every buffer, including workspaces, is supplied by the caller);
+ *  - every call only enqueues work on `stream` (a cudaStream_t passed as void*) of the CURRENT device
+ *    and returns 0, or a negative b200gdn_status; b200gdn_last_error() gives the text;
+ *  - token-major layout of the reference ([B,T,H,...], head_first is not supported) flattened to rows:
+ *    q,k [rows,H,K]; v,o,do [rows,HV,V]; g,beta [rows,HV]; states [n_seq,HV,K,V] fp32;
+ *    rows = B*T (dense) or the packed token count (cu_seqlens input, B == 1);
+ *  - q/k/v/o/do and the saved tensors are bf16; gates, beta and states are fp32;
+ *  - chunking (64 tokens, restarting at every sequence start) is described by two int32 tables that the
+ *    host builds once per shape (fla/ops/utils/index.py:155-172 computes the same information):
+ *      chunk_meta[n_chunks][4] = { sequence id, first row, valid rows (1..64), chunk index inside its sequence }
+ *      seq_meta  [n_seq][2]    = { first chunk (global index), number of chunks }
+ */
+#ifndef B200GDN_H_
+#define B200GDN_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200GDN_ABI_VERSION 1
+#define B200GDN_CHUNK 64
+
+typedef enum b200gdn_status {
+  B200GDN_OK = 0,
+  B200GDN_ERR_BAD_ARGUMENT = -1,   /* null pointer, wrong struct size, zero size */
+  B200GDN_ERR_UNSUPPORTED = -2,    /* head dimension / option not built */
+  B200GDN_ERR_CUDA = -3,           /* a CUDA runtime call failed; see b200gdn_last_error() */
+  B200GDN_ERR_TOO_LARGE = -4       /* size exceeds a fixed capacity (static-scratch entry point) */
+} b200gdn_status;
+
+/* stage masks: run only some kernels of a pass (unit tests and profiling); 0 means all */
+#define B200GDN_FWD_INTRA 1u     /* gamma, A, w, u         <- k, v, g, beta */
+#define B200GDN_FWD_SCAN 2u      /* h, v_new, ht           <- k, w, u, gamma, h0 */
+#define B200GDN_FWD_OUT 4u       /* o                      <- q, k, v_new, h, gamma */
+#define B200GDN_BWD_DVLOCAL 1u   /* dv2 (local part)       <- q, k, gamma, do */
+#define B200GDN_BWD_SCAN 2u      /* dh, dh0, dv2           <- q, k, w, gamma, do, dht */
+#define B200GDN_BWD_DQKWG 4u     /* dq, dk_part, dw, dG    <- q, k, v_new, gamma, h, dv2, do, dh */
+#define B200GDN_BWD_WY 8u        /* dk, dv, dbeta, dg      <- k, v, beta, gamma, A, dw, dv2, dk_part, dG */
+
+typedef struct b200gdn_chunk_args {
+  int32_t struct_bytes;          /* = sizeof(b200gdn_chunk_args), checked */
+  int32_t rows, H, HV, K, V;
+  int32_t n_seq, n_chunks;
+  float scale;
+  uint32_t stage_mask;           /* 0 = all stages of the pass */
+  const int32_t* chunk_meta;     /* device, [n_chunks][4] */
+  const int32_t* seq_meta;       /* device, [n_seq][2] */
+  /* inputs */
+  const void* q;                 /* bf16 [rows,H,K] */
+  const void* k;                 /* bf16 [rows,H,K] */
+  const void* v;                 /* bf16 [rows,HV,V] */
+  const float* g;                /* [rows,HV] log-space decay per token (forward only) */
+  const float* beta;             /* [rows,HV] */
+  const float* h0;               /* [n_seq,HV,K,V] or NULL */
+  /* forward outputs */
+  void* o;                       /* bf16 [rows,HV,V] */
+  float* ht;                     /* [n_seq,HV,K,V] or NULL */
+  /* written by the forward pass, read by the backward pass */
+  float* gamma;                  /* [rows,HV]  chunk-local cumsum(g) * log2(e) */
+  void* A;                       /* bf16 [rows,HV,64]  rows of (I + L)^-1 */
+  void* w;                       /* bf16 [rows,HV,K] */
+  void* u;                       /* bf16 [rows,HV,V] */
+  void* h;                       /* bf16 [n_chunks,HV,K,V]  state at each chunk start */
+  void* v_new;                   /* bf16 [rows,HV,V] */
+  /* backward inputs */
+  const void* d_o;               /* bf16 [rows,HV,V] */
+  const float* dht;              /* [n_seq,HV,K,V] or NULL */
+  /* backward outputs */
+  void* dq;                      /* bf16 [rows,H,K] */
+  void* dk;                      /* bf16 [rows,H,K] */
+  void* dv;                      /* bf16 [rows,HV,V] */
+  float* dg;                     /* [rows,HV] */
+  float* dbeta;                  /* [rows,HV] */
+  float* dh0;                    /* [n_seq,HV,K,V] or NULL */
+  /* backward workspace */
+  void* dh;                      /* bf16 [n_chunks,HV,K,V] */
+  void* dv2;                     /* bf16 [rows,HV,V] */
+  void* dw;                      /* bf16 [rows,HV,K] */
+  float* dk_part;                /* [rows,H,K] */
+  float* dG;                     /* [rows,HV] */
+  float* dq_acc;                 /* [rows,H,K], only read/written when HV > H */
+} b200gdn_chunk_args;
+
+/* Replaces chunk_gated_delta_rule_fwd (fla/ops/gated_delta_rule/chunk.py:33-123):
+ * chunk_local_cumsum + chunk_gated_delta_rule_fwd_intra + chunk_gated_delta_rule_fwd_h + chunk_fwd_o. */
+int b200gdn_chunk_fwd(const b200gdn_chunk_args* args, void* stream);
+
+/* Replaces chunk_gated_delta_rule_bwd (fla/ops/gated_delta_rule/chunk.py:126-250):
+ * chunk_bwd_dv_local + chunk_gated_delta_rule_bwd_dhu + chunk_bwd_dqkwg + prepare_wy_repr_bwd +
+ * the reverse chunk_local_cumsum of dg.  Reads the tensors the forward pass saved. */
+int b200gdn_chunk_bwd(const b200gdn_chunk_args* args, void* stream);
+
+typedef struct b200gdn_recurrent_args {
+  int32_t struct_bytes;
+  int32_t B, T, H, HV, K, V;     /* dense: B sequences of T tokens; packed: B = 1, T = total tokens */
+  int32_t n_seq;
+  float scale;
+  uint32_t flags;                /* B200GDN_REC_* */
+  int32_t qkv_dtype;             /* 0 = bf16, 1 = fp16, 2 = fp32: element type of q, k, v and o */
+  const int32_t* cu_seqlens;     /* device [n_seq+1] or NULL */
+  const void* q;                 /* [B,T,H,K] */
+  const void* k;                 /* [B,T,H,K] */
+  const void* v;                 /* [B,T,HV,V] */
+  const float* g;                /* [B,T,HV] or NULL */
+  const float* beta;             /* [B,T,HV] */
+  const float* A_log;            /* [HV] (gate in kernel) or NULL */
+  const float* dt_bias;          /* [HV] or NULL */
+  const float* h0;               /* [n_seq,HV,K,V] ([.,.,V,K] when V-first) or NULL */
+  void* o;                       /* [B,T,HV,V] */
+  float* ht;                     /* like h0, or NULL; may alias h0 for an in-place update */
+} b200gdn_recurrent_args;
+
+#define B200GDN_REC_L2NORM 1u         /* q, k <- x * rsqrt(sum x^2 + 1e-6) */
+#define B200GDN_REC_GATE 2u           /* g <- -exp(A_log) * softplus(g + dt_bias) */
+#define B200GDN_REC_BETA_SIGMOID 4u   /* beta <- sigmoid(beta) */
+#define B200GDN_REC_NEG_EIGVAL 8u     /* beta <- 2 * sigmoid(beta) (with BETA_SIGMOID) */
+#define B200GDN_REC_STATE_V_FIRST 16u /* states stored [V,K] */
+
+/* Replaces fused_recurrent_gated_delta_rule_fwd (fla/ops/gated_delta_rule/fused_recurrent.py:184-250). */
+int b200gdn_recurrent_fwd(const b200gdn_recurrent_args* args, void* stream);
+
+/* Context parallelism (fla/ops/cp/chunk_delta_h.py:747-936).  The transition of a whole shard is affine,
+ * S_end = M S_start + h_ext; these produce M ([HV,K,K] fp32) for the rank's last (forward) or first
+ * (backward) local sequence and fold a received prefix:  out = M x + b. */
+typedef struct b200gdn_affine_args {
+  int32_t struct_bytes;
+  int32_t HV, K, V;
+  int32_t transpose_m;           /* 0: out = M x + b ; 1: out = M^T x + b */
+  const float* M;                /* [HV,K,K] */
+  const float* x;                /* [HV,K,V] */
+  const float* b;                /* [HV,K,V] or NULL */
+  float* out;                    /* [HV,K,V] */
+} b200gdn_affine_args;
+int b200gdn_affine_apply(const b200gdn_affine_args* args, void* stream);
+
+/* Bytes of forward-saved tensors and of backward workspace for a problem (what the caller allocates). */
+int64_t b200gdn_saved_bytes(int32_t rows, int32_t H, int32_t HV, int32_t K, int32_t V, int32_t n_chunks);
+int64_t b200gdn_bwd_workspace_bytes(int32_t rows, int32_t H, int32_t HV, int32_t K, int32_t V, int32_t n_chunks);
+
+/* Number of kernels the last call on this thread enqueued (bench bookkeeping). */
+int b200gdn_last_launch_count(void);
+int b200gdn_abi_version(void);
+const char* b200gdn_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200GDN_H_ */

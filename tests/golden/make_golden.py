@@ -25,9 +25,9 @@ sys.path.insert(0, os.path.abspath(os.path.join(HERE, '..', '..')))
 CASES = {
     # name: (B, T, H, HV, K, V, cu_seqlens, seed, with_grads)
     'config1_naive_cpu': (1, 1024, 4, 4, 64, 64, None, 0, False),
-    'small_dense': (2, 128, 2, 2, 32, 32, None, 1, True),
-    'gva_dense': (1, 192, 2, 4, 32, 64, None, 2, True),
-    'varlen_ragged': (1, 300, 2, 4, 32, 32, [0, 37, 101, 165, 300], 3, True),
+    'small_dense': (2, 128, 2, 2, 64, 64, None, 1, True),
+    'gva_dense': (1, 192, 2, 4, 64, 64, None, 2, True),
+    'varlen_ragged': (1, 300, 2, 4, 64, 64, [0, 37, 101, 165, 300], 3, True),
     'd128_dense': (1, 128, 1, 1, 128, 128, None, 4, True),
 }
 

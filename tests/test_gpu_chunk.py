@@ -1,0 +1,179 @@
+"""GPU parity of the chunk path: every stage through the C ABI against the oracle's stage, then the
+public API against the naive recurrence with the reference's own tolerances
+(tests/ops/test_gdn.py:108-200: o/ht 0.005, dq/dk/dv/dh0 0.008, dbeta/dg 0.02)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import gdn_oracle as O
+from tests.golden.make_golden import CASES
+from tests.gpu_util import flat, make_case, oracle_chain, run_abi
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), 'golden')
+
+STAGE_CASES = {
+    'd64_dense': dict(B=2, T=128, H=2, HV=2, K=64, V=64),
+    'd128_dense': dict(B=2, T=256, H=2, HV=2, K=128, V=128),
+    'd128_gva': dict(B=1, T=192, H=2, HV=4, K=128, V=128),
+    'd128_ragged': dict(B=1, T=333, H=1, HV=2, K=128, V=128, cu=[0, 1, 16, 80, 143, 270, 333]),
+    'd64_ragged_gva': dict(B=1, T=300, H=2, HV=4, K=64, V=64, cu=[0, 37, 101, 165, 300]),
+    'd128_nh0': dict(B=1, T=100, H=2, HV=2, K=128, V=128, with_h0=False),
+}
+
+# err-ratio bounds per tensor (bf16 storage: eps = 2^-8 = 0.0039 per rounding)
+FWD_TOL = dict(gamma=1e-5, A=0.005, w=0.005, u=0.005, h=0.005, v_new=0.005, ht=0.005, o=0.005)
+BWD_TOL = dict(dh=0.008, dh0=0.008, dv2=0.008, dq=0.008, dw=0.008, dk=0.008, dv=0.008, dbeta=0.02, dg=0.02)
+
+
+@pytest.mark.parametrize('name', list(STAGE_CASES))
+def test_stages_against_oracle(name):
+    d = make_case(seed=3, **STAGE_CASES[name])
+    fwd, bwd = oracle_chain(d)
+    out = run_abi(d)
+    for n, tol in FWD_TOL.items():
+        O.assert_close(f'{name}:{n}', fwd[n], out[n], tol)
+    if d['h0'] is None:
+        BWD = {k: v for k, v in BWD_TOL.items() if k != 'dh0'}
+    else:
+        BWD = BWD_TOL
+    for n, tol in BWD.items():
+        O.assert_close(f'{name}:{n}', bwd[n], out[n], tol)
+
+
+@pytest.mark.parametrize('name', ['d128_dense', 'd64_ragged_gva'])
+def test_backward_stages_isolated(name):
+    """Each backward kernel alone, fed with the oracle's inputs for that stage."""
+    from b200gdn import _lib
+    d = make_case(seed=5, **STAGE_CASES[name])
+    fwd, bwd = oracle_chain(d)
+    saved = {n: fwd[n] for n in ('gamma', 'A', 'w', 'h', 'v_new')}
+    o1 = run_abi(d, fwd_mask=-1, bwd_mask=_lib.BWD_DVLOCAL, overrides=dict(saved))
+    O.assert_close('dv_local', bwd['dv_local'], o1['dv2'], 0.005)
+    o2 = run_abi(d, fwd_mask=-1, bwd_mask=_lib.BWD_SCAN, overrides=dict(saved, dv2=bwd['dv_local']))
+    for n in ('dh', 'dh0', 'dv2'):
+        O.assert_close(n, bwd[n], o2[n], 0.005)
+    o3 = run_abi(d, fwd_mask=-1, bwd_mask=_lib.BWD_DQKWG, overrides=dict(saved, dv2=bwd['dv2'], dh=bwd['dh']))
+    for n, m in (('dq', 'dq'), ('dk_part', 'dk_part'), ('dw', 'dw'), ('dG', 'dG')):
+        O.assert_close(n, bwd[m], o3[n], 0.005)
+    o4 = run_abi(d, fwd_mask=-1, bwd_mask=_lib.BWD_WY,
+                 overrides=dict(saved, dv2=bwd['dv2'], dw=bwd['dw'], dk_part=bwd['dk_part'], dG=bwd['dG']))
+    for n in ('dk', 'dv', 'dbeta', 'dg'):
+        O.assert_close(n, bwd[n], o4[n], 0.005)
+
+
+@pytest.mark.parametrize('name', [n for n in CASES if CASES[n][-1]])
+def test_public_api_against_reference_fixture(name):
+    """chunk_gated_delta_rule + autograd against the reference's own outputs and gradients."""
+    from b200gdn import chunk_gated_delta_rule
+    B, T, H, HV, K, V, cu, seed, _ = CASES[name]
+    gold = {k: torch.from_numpy(v) for k, v in np.load(os.path.join(GOLD, name + '.npz')).items()}
+    d = O.make_inputs(B, T, H, HV, K, V, seed=seed, cu_seqlens=cu)
+    dev = 'cuda'
+    q, k, v = (d[n].to(dev).to(torch.bfloat16).requires_grad_(True) for n in ('q', 'k', 'v'))
+    g, beta, h0 = (d[n].to(dev).requires_grad_(True) for n in ('g', 'beta', 'h0'))
+    cu_t = None if cu is None else torch.tensor(cu, dtype=torch.long, device=dev)
+    o, ht = chunk_gated_delta_rule(q, k, v, g, beta, initial_state=h0, output_final_state=True, cu_seqlens=cu_t)
+    ((o.float() * d['do'].to(dev)).sum() + (ht * d['dht'].to(dev)).sum()).backward()
+    assert o.dtype == torch.bfloat16 and ht.dtype == torch.float32
+    O.assert_close('o', gold['o'], o.float().cpu(), 0.005)
+    O.assert_close('ht', gold['ht'], ht.cpu(), 0.005)
+    O.assert_close('dq', gold['dq'], q.grad.float().cpu(), 0.008)
+    O.assert_close('dk', gold['dk'], k.grad.float().cpu(), 0.008)
+    O.assert_close('dv', gold['dv'], v.grad.float().cpu(), 0.008)
+    O.assert_close('dh0', gold['dh0'], h0.grad.cpu(), 0.008)
+    O.assert_close('dbeta', gold['dbeta'], beta.grad.cpu(), 0.02)
+    O.assert_close('dg', gold['dg'], g.grad.cpu(), 0.02)
+
+
+def test_options_equal_preprocessing():
+    """In-kernel options == the op on pre-processed inputs (tests/ops/test_gdn.py:281-448, 881-1190)."""
+    from b200gdn import chunk_gated_delta_rule
+    dev = 'cuda'
+    B, T, H, HV, K, V = 2, 150, 2, 4, 128, 128
+    gen = torch.Generator().manual_seed(9)
+    q = torch.randn(B, T, H, K, generator=gen).to(dev).to(torch.bfloat16)
+    k = torch.randn(B, T, H, K, generator=gen).to(dev).to(torch.bfloat16)
+    v = torch.randn(B, T, HV, V, generator=gen).to(dev).to(torch.bfloat16)
+    graw = torch.randn(B, T, HV, generator=gen).to(dev)
+    braw = torch.randn(B, T, HV, generator=gen).to(dev)
+    A_log = (torch.randn(HV, generator=gen) * 0.3).to(dev)
+    dt_bias = (torch.randn(HV, generator=gen) * 0.3).to(dev)
+    h0 = (torch.randn(B, HV, V, K, generator=gen) * 0.1).to(dev)
+
+    def run(in_kernel):
+        leaves = [x.clone().requires_grad_(True) for x in (q, k, v, graw, braw, A_log, dt_bias, h0)]
+        q_, k_, v_, g_, b_, A_, dt_, h0_ = leaves
+        if in_kernel:
+            o, ht = chunk_gated_delta_rule(q_, k_, v_, g_, b_, initial_state=h0_, output_final_state=True,
+                                           use_qk_l2norm_in_kernel=True, use_beta_sigmoid_in_kernel=True,
+                                           allow_neg_eigval=True, state_v_first=True, use_gate_in_kernel=True,
+                                           A_log=A_, dt_bias=dt_, chunk_size=32)
+        else:
+            qn = O.l2norm(q_.float()).to(torch.bfloat16)
+            kn = O.l2norm(k_.float()).to(torch.bfloat16)
+            o, ht = chunk_gated_delta_rule(qn, kn, v_, O.gdn_gate(g_, A_, dt_), 2 * torch.sigmoid(b_),
+                                           initial_state=h0_.transpose(-1, -2), output_final_state=True)
+            ht = ht.transpose(-1, -2)
+        (o.float().square().sum() + ht.square().sum()).backward()
+        return [o.float(), ht] + [x.grad.float() for x in leaves]
+    a, b = run(True), run(False)
+    for i, (x, y) in enumerate(zip(a, b)):
+        O.assert_close(f'option-equivalence[{i}]', y.cpu(), x.cpu(), 1e-4)
+
+
+def test_api_errors():
+    from b200gdn import chunk_gated_delta_rule
+    dev = 'cuda'
+    q = torch.zeros(2, 64, 2, 128, device=dev, dtype=torch.bfloat16)
+    v = torch.zeros(2, 64, 3, 128, device=dev, dtype=torch.bfloat16)
+    g = torch.zeros(2, 64, 3, device=dev)
+    with pytest.raises(ValueError, match='evenly divisible'):
+        chunk_gated_delta_rule(q, q, v, g, g)
+    v = torch.zeros(2, 64, 2, 128, device=dev, dtype=torch.bfloat16)
+    g = torch.zeros(2, 64, 2, device=dev)
+    with pytest.raises(ValueError, match='batch size is expected to be 1'):
+        chunk_gated_delta_rule(q, q, v, g, g, cu_seqlens=torch.tensor([0, 64, 128], device=dev))
+    with pytest.raises(DeprecationWarning):
+        chunk_gated_delta_rule(q, q, v, g, g, head_first=True)
+    with pytest.raises(ValueError, match='chunk_size'):
+        chunk_gated_delta_rule(q, q, v, g, g, chunk_size=128)
+    with pytest.raises(ValueError, match='allow_neg_eigval'):
+        chunk_gated_delta_rule(q, q, v, g, g, allow_neg_eigval=True)
+
+
+def test_determinism_and_no_uninitialised_reads():
+    """Two runs are bit-identical (no atomics anywhere), and outputs never contain the NaN the buffers
+    were poisoned with (the reference's NaN-poison fixture, tests/conftest.py:135-148)."""
+    d = make_case(seed=7, **STAGE_CASES['d128_ragged'])
+    a = run_abi(d)
+    b = run_abi(d)
+    for n in ('o', 'ht', 'dq', 'dk', 'dv', 'dg', 'dbeta', 'dh0'):
+        assert not torch.isnan(a[n]).any(), n
+        assert torch.equal(a[n], b[n]), n
+
+
+def test_full_size_properties():
+    """Headline shape (B4 T4096 H16 K=V=128): the oracle is too slow here, so check properties:
+    chunk path == token-by-token kernel (an independent implementation), and linearity in v."""
+    from b200gdn import chunk_gated_delta_rule, fused_recurrent_gated_delta_rule
+    dev = 'cuda'
+    B, T, H, K = 4, 4096, 16, 128
+    gen = torch.Generator(device=dev).manual_seed(0)
+    q = torch.nn.functional.normalize(torch.randn(B, T, H, K, device=dev, generator=gen), dim=-1).to(torch.bfloat16)
+    k = torch.nn.functional.normalize(torch.randn(B, T, H, K, device=dev, generator=gen), dim=-1).to(torch.bfloat16)
+    v1 = torch.randn(B, T, H, K, device=dev, generator=gen).to(torch.bfloat16)
+    v2 = torch.randn(B, T, H, K, device=dev, generator=gen).to(torch.bfloat16)
+    g = torch.nn.functional.logsigmoid(torch.randn(B, T, H, device=dev, generator=gen))
+    beta = torch.sigmoid(torch.randn(B, T, H, device=dev, generator=gen))
+    h0 = torch.randn(B, H, K, K, device=dev, generator=gen) * 0.1
+    o_c, ht_c = chunk_gated_delta_rule(q, k, v1, g, beta, initial_state=h0, output_final_state=True)
+    o_r, ht_r = fused_recurrent_gated_delta_rule(q, k, v1, g, beta, initial_state=h0, output_final_state=True)
+    O.assert_close('o chunk vs recurrent', o_r.float().cpu(), o_c.float().cpu(), 0.005)
+    O.assert_close('ht chunk vs recurrent', ht_r.cpu(), ht_c.cpu(), 0.005)
+    o1, _ = chunk_gated_delta_rule(q, k, v1, g, beta)
+    o2, _ = chunk_gated_delta_rule(q, k, v2, g, beta)
+    o12, _ = chunk_gated_delta_rule(q, k, (v1.float() + v2.float()).to(torch.bfloat16), g, beta)
+    O.assert_close('linearity in v', (o1.float() + o2.float()).cpu(), o12.float().cpu(), 0.01)

@@ -1,0 +1,92 @@
+"""GPU parity of the decode path against the oracle recurrence (reference tolerance 0.002,
+tests/ops/test_gdn.py:48-105; fp32 inputs are held to 1e-5)."""
+import pytest
+import torch
+
+from oracle import gdn_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(B, T, H, HV, K, V, seed, dtype):
+    gen = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, T, H, K, generator=gen).to(dtype)
+    k = torch.randn(B, T, H, K, generator=gen).to(dtype)
+    v = torch.randn(B, T, HV, V, generator=gen).to(dtype)
+    graw = torch.randn(B, T, HV, generator=gen)
+    braw = torch.randn(B, T, HV, generator=gen)
+    A_log = torch.randn(HV, generator=gen) * 0.3
+    dt_bias = torch.randn(HV, generator=gen) * 0.3
+    return q, k, v, graw, braw, A_log, dt_bias, gen
+
+
+@pytest.mark.parametrize('K,V', [(128, 128), (64, 64), (32, 64), (256, 128)])
+@pytest.mark.parametrize('v_first', [False, True])
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
+def test_recurrent_options(K, V, v_first, dtype):
+    from b200gdn import fused_recurrent_gated_delta_rule
+    B, T, H, HV = 2, 9, 2, 4
+    q, k, v, graw, braw, A_log, dt_bias, gen = _inputs(B, T, H, HV, K, V, 1, dtype)
+    h0 = torch.randn(B, HV, *((V, K) if v_first else (K, V)), generator=gen) * 0.5
+    ref_o, ref_ht = O.recurrent_step_options(
+        q.float(), k.float(), v.float(), graw, braw, None, h0, True, True, True, A_log, dt_bias, True, True, v_first)
+    dev = 'cuda'
+    o, ht = fused_recurrent_gated_delta_rule(
+        q.to(dev), k.to(dev), v.to(dev), graw.to(dev), beta=braw.to(dev), initial_state=h0.to(dev),
+        output_final_state=True, use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True, A_log=A_log.to(dev),
+        dt_bias=dt_bias.to(dev), use_beta_sigmoid_in_kernel=True, allow_neg_eigval=True, state_v_first=v_first)
+    assert o.dtype == dtype and ht.dtype == torch.float32
+    tol = 1e-5 if dtype == torch.float32 else 0.004
+    O.assert_close('o', ref_o, o.float().cpu(), tol)
+    O.assert_close('ht', ref_ht, ht.cpu(), 1e-5)
+
+
+def test_recurrent_plain_varlen_and_inplace():
+    from b200gdn import fused_recurrent_gated_delta_rule
+    H, HV, K, V = 2, 2, 128, 128
+    cu = [0, 3, 4, 20, 31]
+    T = cu[-1]
+    d = O.make_inputs(1, T, H, HV, K, V, seed=2, cu_seqlens=cu, h0_std=0.5)
+    ref_o, ref_ht = O.naive_recurrent(d['q'], d['k'], d['v'], d['g'], d['beta'], None, d['h0'], True, cu)
+    dev = 'cuda'
+    state = d['h0'].to(dev).clone()
+    o, ht = fused_recurrent_gated_delta_rule(
+        d['q'].to(dev), d['k'].to(dev), d['v'].to(dev), d['g'].to(dev), beta=d['beta'].to(dev), initial_state=state,
+        output_final_state=True, cu_seqlens=torch.tensor(cu, device=dev), inplace_state=True)
+    assert ht.data_ptr() == state.data_ptr()
+    O.assert_close('o', ref_o, o.cpu(), 1e-5)
+    O.assert_close('ht', ref_ht, ht.cpu(), 1e-5)
+    # no initial state, no final state, beta defaults to ones
+    o2, none = fused_recurrent_gated_delta_rule(d['q'].to(dev), d['k'].to(dev), d['v'].to(dev), d['g'].to(dev))
+    ref_o2, _ = O.naive_recurrent(d['q'], d['k'], d['v'], d['g'], torch.ones_like(d['beta']), None, None, False)
+    assert none is None
+    O.assert_close('o2', ref_o2, o2.cpu(), 1e-5)
+
+
+def test_recurrent_matches_config1_fixture():
+    """BASELINE config 1 (B1 T1024 H4 K=V=64 fp32) against the reference's own output."""
+    import os
+    import numpy as np
+    from b200gdn import fused_recurrent_gated_delta_rule
+    gold = np.load(os.path.join(os.path.dirname(__file__), 'golden', 'config1_naive_cpu.npz'))
+    d = O.make_inputs(1, 1024, 4, 4, 64, 64, seed=0)
+    dev = 'cuda'
+    o, ht = fused_recurrent_gated_delta_rule(d['q'].to(dev), d['k'].to(dev), d['v'].to(dev), d['g'].to(dev),
+                                             beta=d['beta'].to(dev), initial_state=d['h0'].to(dev),
+                                             output_final_state=True)
+    O.assert_close('o', torch.from_numpy(gold['o']), o.cpu()[:, ::8], 1e-5)
+    O.assert_close('ht', torch.from_numpy(gold['ht']), ht.cpu(), 1e-5)
+
+
+def test_recurrent_errors():
+    from b200gdn import fused_recurrent_gated_delta_rule
+    dev = 'cuda'
+    q = torch.zeros(1, 4, 2, 64, device=dev)
+    g = torch.zeros(1, 4, 2, device=dev)
+    with pytest.raises(NotImplementedError):
+        fused_recurrent_gated_delta_rule(q, q, q, g, gk=q)
+    with pytest.raises(ValueError, match='A_log'):
+        fused_recurrent_gated_delta_rule(q, q, q, g, use_gate_in_kernel=True)
+    o, _ = fused_recurrent_gated_delta_rule(q.requires_grad_(True), q, q, g)
+    with pytest.raises(NotImplementedError):
+        o.sum().backward()
