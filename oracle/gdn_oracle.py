@@ -295,7 +295,7 @@ def chunk_fwd(q, k, v, g, beta, scale, h0, bounds, emulate_bf16=False):
     gam, A, w, u = stage_intra(k, v, g, beta, bounds, emulate_bf16)
     h, v_new, ht = stage_scan_fwd(k, w, u, gam, h0, bounds, emulate_bf16)
     o = stage_out(q, k, v_new, h, gam, scale, bounds, emulate_bf16)
-    return dict(gam=gam, A=A, w=w, u=u, h=h, v_new=v_new, ht=ht, o=o)
+    return dict(gamma=gam, A=A, w=w, u=u, h=h, v_new=v_new, ht=ht, o=o)
 
 
 # --------------------------------------------------------------------------- backward stages
@@ -478,7 +478,7 @@ def chunk_bwd(q, k, v, g, beta, scale, h0, do, dht, bounds, fwd=None, emulate_bf
     """All backward stages chained (fla/ops/gated_delta_rule/chunk.py:126-250)."""
     if fwd is None:
         fwd = chunk_fwd(q, k, v, g, beta, scale, h0, bounds, emulate_bf16)
-    gam = fwd['gam']
+    gam = fwd['gamma']
     dv_local = stage_dv_local(q, k, gam, do, scale, bounds, emulate_bf16)
     dh, dh0, dv2 = stage_scan_bwd(q, k, fwd['w'], gam, do, dv_local, dht, scale, bounds, emulate_bf16)
     dq, dk_part, dw, dG = stage_dqkwg(q, k, fwd['v_new'], gam, fwd['h'], dv2, do, dh, scale, bounds, emulate_bf16)

@@ -170,7 +170,7 @@ def test_full_size_properties():
     beta = torch.sigmoid(torch.randn(B, T, H, device=dev, generator=gen))
     h0 = torch.randn(B, H, K, K, device=dev, generator=gen) * 0.1
     o_c, ht_c = chunk_gated_delta_rule(q, k, v1, g, beta, initial_state=h0, output_final_state=True)
-    o_r, ht_r = fused_recurrent_gated_delta_rule(q, k, v1, g, beta, initial_state=h0, output_final_state=True)
+    o_r, ht_r = fused_recurrent_gated_delta_rule(q, k, v1, g, beta=beta, initial_state=h0, output_final_state=True)
     O.assert_close('o chunk vs recurrent', o_r.float().cpu(), o_c.float().cpu(), 0.005)
     O.assert_close('ht chunk vs recurrent', ht_r.cpu(), ht_c.cpu(), 0.005)
     o1, _ = chunk_gated_delta_rule(q, k, v1, g, beta)
