@@ -118,9 +118,9 @@ def exchange(local: torch.Tensor, group) -> torch.Tensor:
     """All ranks contribute their [HV,K,K+V] fp32 pair, every rank receives [W,HV,K,K+V]
     (fla/ops/cp/comm.py:19-41; ranks with nothing to send contribute zeros, like the reference)."""
     world = dist.get_world_size(group=group)
-    out = torch.empty((world,) + tuple(local.shape), dtype=local.dtype, device=local.device)
-    dist.all_gather_into_tensor(out, local.contiguous(), group=group)
-    return out
+    out = torch.empty(world * local.numel(), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(out, local.contiguous().view(-1), group=group)
+    return out.view((world,) + tuple(local.shape))
 
 
 def fold_prefix(gathered: torch.Tensor, rank: int, num: int, K: int, forward: bool,
