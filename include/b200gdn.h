@@ -97,6 +97,20 @@ typedef struct b200gdn_chunk_args {
  * chunk_local_cumsum + chunk_gated_delta_rule_fwd_intra + chunk_gated_delta_rule_fwd_h + chunk_fwd_o. */
 int b200gdn_chunk_fwd(const b200gdn_chunk_args* args, void* stream);
 
+/* No counterpart in the reference.  Same result as b200gdn_chunk_fwd (o and, when ht != NULL, the final state)
+ * for callers that cannot allocate device memory (a server whose own pool already owns all of it, a plug-in
+ * inside a foreign CUDA context, a C host that owns only inputs and outputs): the six intermediate tensors live
+ * in one array built into the library, B200GDN_STATIC_SCRATCH_BYTES bytes per GPU that loads the library, held
+ * until exit.  The gamma/A/w/u/h/v_new fields of `args` are ignored and nothing is saved for a backward pass.
+ * Limit: align256(rows*HV*4) + align256(rows*HV*128) + align256(rows*HV*K*2) + 2*align256(rows*HV*V*2)
+ *        + align256(n_chunks*HV*K*V*2)  <=  B200GDN_STATIC_SCRATCH_BYTES
+ * (e.g. 2048 tokens x 16 heads at K = V = 128); larger problems return B200GDN_ERR_TOO_LARGE and launch nothing.
+ * Makes no allocating call.  The first call on each device looks up the array's address and should come before
+ * any stream capture.  All calls on a device share the array (it keeps the previous call's contents; no stage
+ * needs it cleared), so calls that can overlap on the GPU race: issue them in stream order. */
+#define B200GDN_STATIC_SCRATCH_BYTES (64u << 20)
+int b200gdn_chunk_fwd_static(const b200gdn_chunk_args* args, void* stream);
+
 /* Replaces chunk_gated_delta_rule_bwd (fla/ops/gated_delta_rule/chunk.py:126-250):
  * chunk_bwd_dv_local + chunk_gated_delta_rule_bwd_dhu + chunk_bwd_dqkwg + prepare_wy_repr_bwd +
  * the reverse chunk_local_cumsum of dg.  Reads the tensors the forward pass saved. */
