@@ -40,11 +40,11 @@ STAGE_FLOPS = {
     'out_fwd': 2 * K * V + 2 * BT * (K + V),
     'dv_local': 2 * BT * (K + V),
     'scan_bwd': 6 * K * V,
-    'dqkwg': 6 * K * V + 2 * BT * (V + 2 * K),
-    'wy_bwd': 2 * BT * (5 * K + 2 * V + 2 * BT),
+    'bwd_dqk': 4 * K * V + 2 * BT * (V + 2 * K),                       # dP, do h^T, v dh^T, dP k, dP^T q
+    'bwd_wy': 2 * K * V + 2 * BT * (5 * K + 2 * V + 2 * BT),           # dv2 h^T + WY backward
 }
 F_FWD = sum(STAGE_FLOPS[s] for s in ('intra_fwd', 'scan_fwd', 'out_fwd'))
-F_BWD = sum(STAGE_FLOPS[s] for s in ('dv_local', 'scan_bwd', 'dqkwg', 'wy_bwd'))
+F_BWD = sum(STAGE_FLOPS[s] for s in ('dv_local', 'scan_bwd', 'bwd_dqk', 'bwd_wy'))
 assert F_FWD == 180224 and F_BWD == 409600
 
 
@@ -150,7 +150,7 @@ def time_stages(batch, steps):
                h=torch.empty(n_chunks, HV, K, V, **bf), v_new=torch.empty(rows, HV, V, **bf),
                dq=torch.empty(rows, H, K, **bf), dk=torch.empty(rows, H, K, **bf), dv=torch.empty(rows, HV, V, **bf),
                dg=torch.empty(rows, HV, **f32), dbeta=torch.empty(rows, HV, **f32), dh0=torch.empty(n_seq, HV, K, V, **f32),
-               dh=torch.empty(n_chunks, HV, K, V, **bf), dv2=torch.empty(rows, HV, V, **bf), dw=torch.empty(rows, HV, K, **bf),
+               dh=torch.empty(n_chunks, HV, K, V, **bf), dv2=torch.empty(rows, HV, V, **bf),
                dk_part=torch.empty(rows, H, K, **f32), dG=torch.empty(rows, HV, **f32))
     a = new_chunk_args(batch['q'], batch['k'], batch['v'], K ** -0.5, tables)
     a.g, a.beta, a.h0 = batch['g'].data_ptr(), batch['beta'].data_ptr(), batch['h0'].data_ptr()
@@ -160,8 +160,8 @@ def time_stages(batch, steps):
     stream = torch.cuda.current_stream(dev)
     plan = [('intra_fwd', 'b200gdn_chunk_fwd', _lib.FWD_INTRA), ('scan_fwd', 'b200gdn_chunk_fwd', _lib.FWD_SCAN),
             ('out_fwd', 'b200gdn_chunk_fwd', _lib.FWD_OUT), ('dv_local', 'b200gdn_chunk_bwd', _lib.BWD_DVLOCAL),
-            ('scan_bwd', 'b200gdn_chunk_bwd', _lib.BWD_SCAN), ('dqkwg', 'b200gdn_chunk_bwd', _lib.BWD_DQKWG),
-            ('wy_bwd', 'b200gdn_chunk_bwd', _lib.BWD_WY)]
+            ('scan_bwd', 'b200gdn_chunk_bwd', _lib.BWD_SCAN), ('bwd_dqk', 'b200gdn_chunk_bwd', _lib.BWD_DQKWG),
+            ('bwd_wy', 'b200gdn_chunk_bwd', _lib.BWD_WY)]
     total = {n: 0.0 for n, _, _ in plan}
     for it in range(steps + 1):
         evs = []

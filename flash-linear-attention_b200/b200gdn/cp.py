@@ -248,7 +248,6 @@ class ChunkGatedDeltaRuleCPFunction(torch.autograd.Function):
             dbeta = torch.empty(B, T, HV, **f32)
             dh = torch.empty(n_chunks, HV, K, V, **bf16)
             dv2 = torch.empty(rows, HV, V, **bf16)
-            dw = torch.empty(rows, HV, K, **bf16)
             dk_part = torch.empty(rows, H, K, **f32)
             dG = torch.empty(rows, HV, **f32)
             dq_acc = torch.empty(rows, H, K, **f32) if HV > H else None
@@ -259,7 +258,7 @@ class ChunkGatedDeltaRuleCPFunction(torch.autograd.Function):
             a.beta, a.gamma, a.A, a.w, a.h, a.v_new = (x.data_ptr() for x in (bf, gamma, A, w, h, v_new))
             a.d_o = dob.data_ptr()
             a.dq, a.dk, a.dv, a.dg, a.dbeta = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dg.data_ptr(), dbeta.data_ptr()
-            a.dh, a.dv2, a.dw, a.dk_part, a.dG, a.dq_acc = dh.data_ptr(), dv2.data_ptr(), dw.data_ptr(), \
+            a.dh, a.dv2, a.dk_part, a.dG, a.dq_acc = dh.data_ptr(), dv2.data_ptr(), \
                 dk_part.data_ptr(), dG.data_ptr(), _lib.ptr(dq_acc)
             a.stage_mask = _lib.BWD_DVLOCAL
             _lib.call('b200gdn_chunk_bwd', a, st)

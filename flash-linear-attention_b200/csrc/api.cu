@@ -90,15 +90,15 @@ int b200gdn_chunk_bwd(const b200gdn_chunk_args* a, void* stream) {
   if (m & B200GDN_BWD_DQKWG) {
     REQUIRE(a->q, "chunk_bwd"); REQUIRE(a->k, "chunk_bwd"); REQUIRE(a->v_new, "chunk_bwd"); REQUIRE(a->gamma, "chunk_bwd");
     REQUIRE(a->h, "chunk_bwd"); REQUIRE(a->dh, "chunk_bwd"); REQUIRE(a->dv2, "chunk_bwd"); REQUIRE(a->d_o, "chunk_bwd");
-    REQUIRE(a->dq, "chunk_bwd"); REQUIRE(a->dk_part, "chunk_bwd"); REQUIRE(a->dw, "chunk_bwd"); REQUIRE(a->dG, "chunk_bwd");
-    if (int e = launch_dqkwg(*a, st)) return e;
+    REQUIRE(a->dq, "chunk_bwd"); REQUIRE(a->dk_part, "chunk_bwd"); REQUIRE(a->dG, "chunk_bwd");
+    if (int e = launch_bwd_dqk(*a, st)) return e;
   }
   if (m & B200GDN_BWD_WY) {
     REQUIRE(a->k, "chunk_bwd"); REQUIRE(a->v, "chunk_bwd"); REQUIRE(a->beta, "chunk_bwd"); REQUIRE(a->gamma, "chunk_bwd");
-    REQUIRE(a->A, "chunk_bwd"); REQUIRE(a->dw, "chunk_bwd"); REQUIRE(a->dv2, "chunk_bwd"); REQUIRE(a->dk_part, "chunk_bwd");
+    REQUIRE(a->A, "chunk_bwd"); REQUIRE(a->h, "chunk_bwd"); REQUIRE(a->dv2, "chunk_bwd"); REQUIRE(a->dk_part, "chunk_bwd");
     REQUIRE(a->dG, "chunk_bwd"); REQUIRE(a->dk, "chunk_bwd"); REQUIRE(a->dv, "chunk_bwd"); REQUIRE(a->dg, "chunk_bwd");
     REQUIRE(a->dbeta, "chunk_bwd");
-    if (int e = launch_wy_bwd(*a, st)) return e;
+    if (int e = launch_bwd_wy(*a, st)) return e;
   }
   return 0;
 }

@@ -1,0 +1,331 @@
+// Chunk-local gradients of q and k and of the cumulative gate, on tcgen05 tensor cores with TMEM
+// accumulators (replaces chunk_bwd_kernel_dqkwg of fla/ops/common/chunk_o.py:172-342 except for dw,
+// which the WY-backward kernel now forms itself so that it never touches HBM):
+//     dP   = tril(do v_new^T 2^(gamma_i - gamma_j)) scale
+//     dq   = (do scale 2^gamma) h^T + dP k
+//     dk   = dP^T q + (v_new 2^(gamma_last - gamma)) dh^T
+//     dG_i = <dq_i,q_i> - <dk_i,k_i>  (+ at the last valid row: 2^gamma_last <h,dh> + sum_i <dk_state_i,k_i>)
+//
+// One CTA (4 warps) per (chunk, q/k head), looping over the value heads of the group.  Operand tiles sit
+// in shared memory in the 128-byte-swizzled layout; one thread issues tcgen05.mma; the 64-row
+// accumulators (dq | dk_state, dP, dk_intra) share 256 TMEM columns, so two CTAs fit on an SM and one
+// CTA's epilogue overlaps the other's MMAs.  h and dh are streamed in 64-column panels through one
+// buffer pair, which keeps the CTA at ~106 KiB of shared memory.
+#include "tc5_tile.cuh"
+
+namespace gdn {
+namespace {
+
+constexpr int NTHREADS = 128;
+__device__ int g_dqk_timeout = 0;
+
+template <int DK, int DV>
+struct DqkSmem {
+  static constexpr size_t o_do = 0;
+  static constexpr size_t o_vn = o_do + BT * DV * 2;
+  static constexpr size_t o_q = o_vn + BT * DV * 2;
+  static constexpr size_t o_k = o_q + BT * DK * 2;
+  static constexpr size_t o_hp = o_k + BT * DK * 2;      // h panel  [DK][64]; later output staging
+  static constexpr size_t o_dhp = o_hp + DK * 128;       // dh panel [DK][64]
+  static constexpr size_t o_p = o_dhp + DK * 128;        // dP~ [64][64]
+  static constexpr size_t o_vec = o_p + BT * 128;
+  static constexpr size_t bytes = o_vec + 1024 + 1024;   // + vectors + alignment slack
+  static_assert(2 * DK * 128 >= BT * DK * 2, "staging fits in the panel buffers");
+};
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(NTHREADS) bwd_dqk_kernel(const b200gdn_chunk_args a) {
+  using S = DqkSmem<DK, DV>;
+  constexpr int NP = DV / 64;  // value panels
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* Do = smem + S::o_do;
+  unsigned char* Vn = smem + S::o_vn;
+  unsigned char* Qs = smem + S::o_q;
+  unsigned char* Ks = smem + S::o_k;
+  unsigned char* Hp = smem + S::o_hp;
+  unsigned char* dHp = smem + S::o_dhp;
+  unsigned char* Ps = smem + S::o_p;
+  float* gs = reinterpret_cast<float*>(smem + S::o_vec);
+  float* dGs = gs + BT;
+  float* red = dGs + BT;                                   // [0..3] <h,dh>, [4..7] sum rs
+  uint64_t* bar = reinterpret_cast<uint64_t*>(red + 16);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int c = blockIdx.x, hq = blockIdx.y;
+  const int G = a.HV / a.H;
+  const ChunkMeta cm = load_chunk_meta(a.chunk_meta, c);
+  const int64_t row0 = cm.row;
+  const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
+
+  if (warp == 0) tc5::tmem_alloc(tmem_slot, 256);
+  if (tid == 0) {
+    tc5::mbar_init(bar, 1);
+    tc5::fence_mbar_init();
+  }
+  load_tile_swz<BT, DK, NTHREADS>(Qs, reinterpret_cast<const __nv_bfloat16*>(a.q) + (row0 * a.H + hq) * DK, (int64_t)a.H * DK,
+                                  cm.len, tid);
+  load_tile_swz<BT, DK, NTHREADS>(Ks, reinterpret_cast<const __nv_bfloat16*>(a.k) + (row0 * a.H + hq) * DK, (int64_t)a.H * DK,
+                                  cm.len, tid);
+  cp_async_commit();
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tm = *tmem_slot;
+  const uint32_t TM_DQ = tm, TM_DKS = tm + 128, TM_DP = tm + 128, TM_DKI = tm;
+  PhaseBarrier ph{bar, 0u, &g_dqk_timeout};
+  bool failed = false;
+
+  const Operand opQ{tc5::smem_addr(Qs), BT, 1};   // B of dP~^T q : (k = token, n = key dim)
+  const Operand opK{tc5::smem_addr(Ks), BT, 1};   // B of dP~ k
+  const Operand opPk{tc5::smem_addr(Ps), BT, 0};  // dP~ as A(m = i, k = j)
+  const Operand opPm{tc5::smem_addr(Ps), BT, 1};  // dP~ as A(m = j, k = i)
+
+  for (int gi = 0; gi < G && !failed; ++gi) {
+    const int hv = hq * G + gi;
+    const bool first = gi == 0, last = gi == G - 1;
+    const __nv_bfloat16* hg = reinterpret_cast<const __nv_bfloat16*>(a.h) + ((int64_t)c * a.HV + hv) * DK * DV;
+    const __nv_bfloat16* dhg = reinterpret_cast<const __nv_bfloat16*>(a.dh) + ((int64_t)c * a.HV + hv) * DK * DV;
+    __syncthreads();  // previous head fully consumed (staging, gs, red)
+    load_tile_swz<BT, DV, NTHREADS>(Do, reinterpret_cast<const __nv_bfloat16*>(a.d_o) + (row0 * a.HV + hv) * DV,
+                                    (int64_t)a.HV * DV, cm.len, tid);
+    load_tile_swz<BT, DV, NTHREADS>(Vn, reinterpret_cast<const __nv_bfloat16*>(a.v_new) + (row0 * a.HV + hv) * DV,
+                                    (int64_t)a.HV * DV, cm.len, tid);
+    load_tile_swz<DK, 64, NTHREADS>(Hp, hg, DV, DK, tid);
+    load_tile_swz<DK, 64, NTHREADS>(dHp, dhg, DV, DK, tid);
+    cp_async_commit();
+    load_gamma(gs, a.gamma, cm.row, cm.len, a.HV, hv, tid);
+    cp_async_wait<0>();
+    tc5::fence_async_smem();
+    __syncthreads();
+
+    // ---- phase 1: dP = do v_new^T
+    if (tid == 0) {
+      tc5::fence_after_sync();
+      issue_mma(TM_DP, Operand{tc5::smem_addr(Do), BT, 0}, Operand{tc5::smem_addr(Vn), BT, 0}, 64, 64, DV / 16, 0);
+      ph.commit();
+    }
+    const float g_lo = gs[r_lo], g_hi = gs[r_hi], glast = gs[BT - 1];
+    float hd = 0.f;  // <h, dh> partial of this thread
+    auto add_hd = [&]() {
+      for (int idx = tid; idx < DK * 8; idx += NTHREADS) {  // 16-byte chunks; same position in both panels
+        uint4 x = *reinterpret_cast<const uint4*>(Hp + idx * 16);
+        uint4 y = *reinterpret_cast<const uint4*>(dHp + idx * 16);
+        const uint32_t* xu = reinterpret_cast<const uint32_t*>(&x);
+        const uint32_t* yu = reinterpret_cast<const uint32_t*>(&y);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float2 p = unpack_bf16(xu[e]), q2 = unpack_bf16(yu[e]);
+          hd += p.x * q2.x + p.y * q2.y;
+        }
+      }
+    };
+    add_hd();
+    if (__syncthreads_or(!ph.wait())) { failed = true; break; }
+
+    // ---- epilogue 1: dP~ -> shared; rescale do and v_new rows in place
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      float r[16];
+      acc_ld32(TM_DP, warp, b * 32, r);
+      tc5::tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int j0 = b * 32 + i * 8 + 2 * t;
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int ii = (e & 2) ? r_hi : r_lo, jj = j0 + (e & 1);
+          const float gi_ = (e & 2) ? g_hi : g_lo;
+          v[e] = (ii >= jj) ? r[4 * i + e] * a.scale * exp2f(gi_ - gs[jj]) : 0.f;
+        }
+        *swz_ptr32(Ps, r_lo, j0, BT) = pack_bf16(v[0], v[1]);
+        *swz_ptr32(Ps, r_hi, j0, BT) = pack_bf16(v[2], v[3]);
+      }
+    }
+    for (int idx = tid; idx < BT * DV / 8; idx += NTHREADS) {
+      const int row = (idx % (BT * 8)) / 8;
+      const float fo = a.scale * exp2f(gs[row]), fv = exp2f(glast - gs[row]);
+      uint4* po = reinterpret_cast<uint4*>(Do + idx * 16);
+      uint4* pv = reinterpret_cast<uint4*>(Vn + idx * 16);
+      uint4 x = *po, y = *pv;
+      uint32_t* xu = reinterpret_cast<uint32_t*>(&x);
+      uint32_t* yu = reinterpret_cast<uint32_t*>(&y);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float2 p = unpack_bf16(xu[e]), q2 = unpack_bf16(yu[e]);
+        xu[e] = pack_bf16(p.x * fo, p.y * fo);
+        yu[e] = pack_bf16(q2.x * fv, q2.y * fv);
+      }
+      *po = x;
+      *pv = y;
+    }
+    tc5::fence_async_smem();
+    tc5::fence_before_sync();
+    __syncthreads();
+
+    // ---- phase 2: dq = do_s h^T + dP~ k ; dk_state = v~ dh^T   (h, dh streamed by 64-column panels)
+    for (int p = 0; p < NP && !failed; ++p) {
+      if (p > 0) {
+        load_tile_swz<DK, 64, NTHREADS>(Hp, hg + p * 64, DV, DK, tid);
+        load_tile_swz<DK, 64, NTHREADS>(dHp, dhg + p * 64, DV, DK, tid);
+        cp_async_commit();
+        cp_async_wait<0>();
+        tc5::fence_async_smem();
+        __syncthreads();
+      }
+      if (tid == 0) {
+        tc5::fence_after_sync();
+        issue_mma(TM_DQ, Operand{tc5::smem_addr(Do) + p * BT * 128, BT, 0}, Operand{tc5::smem_addr(Hp), DK, 0}, 64, DK, 4, p > 0);
+        issue_mma(TM_DKS, Operand{tc5::smem_addr(Vn) + p * BT * 128, BT, 0}, Operand{tc5::smem_addr(dHp), DK, 0}, 64, DK, 4,
+                  p > 0);
+        if (p == NP - 1) issue_mma(TM_DQ, opPk, opK, 64, DK, 4, 1);
+        ph.commit();
+      }
+      if (p > 0) add_hd();
+      if (__syncthreads_or(!ph.wait())) { failed = true; break; }
+    }
+    if (failed) break;
+
+    // ---- epilogue 2: dq
+    float rq_lo = 0.f, rq_hi = 0.f;
+#pragma unroll
+    for (int b = 0; b < DK / 32; ++b) {
+      float r[16];
+      acc_ld32(TM_DQ, warp, b * 32, r);
+      tc5::tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int col = b * 32 + i * 8 + 2 * t;
+        const float2 qa = swz_ld2(Qs, r_lo, col, BT), qb = swz_ld2(Qs, r_hi, col, BT);
+        rq_lo += r[4 * i] * qa.x + r[4 * i + 1] * qa.y;
+        rq_hi += r[4 * i + 2] * qb.x + r[4 * i + 3] * qb.y;
+        if (G > 1) {
+          float* buf = a.dq_acc + (row0 * a.H + hq) * DK;
+          const int64_t stride = (int64_t)a.H * DK;
+          if (r_lo < cm.len) {
+            float2* pp = reinterpret_cast<float2*>(buf + r_lo * stride + col);
+            if (!first) { float2 o = *pp; r[4 * i] += o.x; r[4 * i + 1] += o.y; }
+            if (!last) *pp = make_float2(r[4 * i], r[4 * i + 1]);
+          }
+          if (r_hi < cm.len) {
+            float2* pp = reinterpret_cast<float2*>(buf + r_hi * stride + col);
+            if (!first) { float2 o = *pp; r[4 * i + 2] += o.x; r[4 * i + 3] += o.y; }
+            if (!last) *pp = make_float2(r[4 * i + 2], r[4 * i + 3]);
+          }
+        }
+        if (last) {
+          *swz_ptr32(Hp, r_lo, col, BT) = pack_bf16(r[4 * i], r[4 * i + 1]);
+          *swz_ptr32(Hp, r_hi, col, BT) = pack_bf16(r[4 * i + 2], r[4 * i + 3]);
+        }
+      }
+    }
+    rq_lo += __shfl_xor_sync(0xffffffffu, rq_lo, 1);
+    rq_lo += __shfl_xor_sync(0xffffffffu, rq_lo, 2);
+    rq_hi += __shfl_xor_sync(0xffffffffu, rq_hi, 1);
+    rq_hi += __shfl_xor_sync(0xffffffffu, rq_hi, 2);
+    tc5::fence_before_sync();
+    __syncthreads();  // every warp has drained the dq columns; staging tile complete
+
+    // ---- phase 3: dk_intra = dP~^T q (into the columns dq just left)
+    if (tid == 0) {
+      tc5::fence_after_sync();
+      issue_mma(TM_DKI, opPm, opQ, 64, DK, 4, 0);
+      ph.commit();
+    }
+    if (last)
+      store_tile_swz<BT, DK, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.dq) + (row0 * a.H + hq) * DK, (int64_t)a.H * DK, Hp,
+                                       cm.len, tid);
+    if (__syncthreads_or(!ph.wait())) { failed = true; break; }
+
+    // ---- epilogue 3: dk = dk_state + dk_intra, gate-gradient rows, tail
+    float rk_lo = 0.f, rk_hi = 0.f, rs = 0.f;
+    {
+      float* buf = a.dk_part + (row0 * a.H + hq) * DK;
+      const int64_t stride = (int64_t)a.H * DK;
+#pragma unroll
+      for (int b = 0; b < DK / 32; ++b) {
+        float r[16], s[16];
+        acc_ld32(TM_DKS, warp, b * 32, s);
+        acc_ld32(TM_DKI, warp, b * 32, r);
+        tc5::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int col = b * 32 + i * 8 + 2 * t;
+          const float2 ka = swz_ld2(Ks, r_lo, col, BT), kb = swz_ld2(Ks, r_hi, col, BT);
+          rs += s[4 * i] * ka.x + s[4 * i + 1] * ka.y + s[4 * i + 2] * kb.x + s[4 * i + 3] * kb.y;
+          const float d0 = r[4 * i] + s[4 * i], d1 = r[4 * i + 1] + s[4 * i + 1];
+          const float d2 = r[4 * i + 2] + s[4 * i + 2], d3 = r[4 * i + 3] + s[4 * i + 3];
+          rk_lo += d0 * ka.x + d1 * ka.y;
+          rk_hi += d2 * kb.x + d3 * kb.y;
+          if (r_lo < cm.len) {
+            float2* pp = reinterpret_cast<float2*>(buf + r_lo * stride + col);
+            float2 o = first ? make_float2(0.f, 0.f) : *pp;
+            *pp = make_float2(d0 + o.x, d1 + o.y);
+          }
+          if (r_hi < cm.len) {
+            float2* pp = reinterpret_cast<float2*>(buf + r_hi * stride + col);
+            float2 o = first ? make_float2(0.f, 0.f) : *pp;
+            *pp = make_float2(d2 + o.x, d3 + o.y);
+          }
+        }
+      }
+    }
+    rk_lo += __shfl_xor_sync(0xffffffffu, rk_lo, 1);
+    rk_lo += __shfl_xor_sync(0xffffffffu, rk_lo, 2);
+    rk_hi += __shfl_xor_sync(0xffffffffu, rk_hi, 1);
+    rk_hi += __shfl_xor_sync(0xffffffffu, rk_hi, 2);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      rs += __shfl_xor_sync(0xffffffffu, rs, o);
+      hd += __shfl_xor_sync(0xffffffffu, hd, o);
+    }
+    if (lane == 0) {
+      red[warp] = hd;
+      red[4 + warp] = rs;
+    }
+    if (t == 0) {
+      dGs[r_lo] = rq_lo - rk_lo;
+      dGs[r_hi] = rq_hi - rk_hi;
+    }
+    tc5::fence_before_sync();
+    __syncthreads();
+    if (tid < cm.len) {
+      const float tail = exp2f(glast) * (red[0] + red[1] + red[2] + red[3]) + (red[4] + red[5] + red[6] + red[7]);
+      a.dG[(row0 + tid) * a.HV + hv] = dGs[tid] + (tid == cm.len - 1 ? tail : 0.f);
+    }
+  }
+
+  if (failed && tid == 0) atomicExch(&g_dqk_timeout, 1);
+  tc5::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc5::tmem_dealloc(tm, 256);
+}
+
+template <int DK, int DV>
+int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
+  using S = DqkSmem<DK, DV>;
+  if (int e = ensure_smem(bwd_dqk_kernel<DK, DV>, S::bytes)) return e;
+  dim3 grid(a.n_chunks, a.H);
+  bwd_dqk_kernel<DK, DV><<<grid, NTHREADS, S::bytes, st>>>(a);
+  return check_launch("bwd_dqk");
+}
+
+}  // namespace
+
+int launch_bwd_dqk(const b200gdn_chunk_args& a, cudaStream_t st) {
+  if (a.HV > a.H && a.dq_acc == nullptr) return set_error(B200GDN_ERR_BAD_ARGUMENT, "bwd_dqk: dq_acc is required when HV > H");
+  if (a.K == 128 && a.V == 128) return launch<128, 128>(a, st);
+  if (a.K == 64 && a.V == 64) return launch<64, 64>(a, st);
+  return set_error(B200GDN_ERR_UNSUPPORTED, "bwd_dqk: K=%d V=%d not built (64/64 and 128/128 are)", a.K, a.V);
+}
+
+int bwd_dqk_timeout_flag() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_dqk_timeout, sizeof(int));
+  return v;
+}
+
+}  // namespace gdn

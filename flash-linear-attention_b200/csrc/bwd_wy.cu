@@ -1,0 +1,418 @@
+// Backward of the WY representation on tcgen05 tensor cores with TMEM accumulators, fused with
+// dw = -dv2 h^T (so dw never touches HBM), the final sum of dk and the reverse chunk-local cumsum of dg.
+// Replaces prepare_wy_repr_bwd_kernel (fla/ops/gated_delta_rule/wy_fast.py:123-251), the dw part of
+// chunk_bwd_kernel_dqkwg (fla/ops/common/chunk_o.py:246-260) and chunk.py:244-246 of the reference.
+//
+//     dW   = -dU h^T                                    dU = dv2
+//     dA   = strict_tril((dW K^T) (beta 2^gamma)_j + (dU V^T) beta_j)
+//     M    = -strict_tril(A^T dA A^T) 2^(gamma_i - gamma_j),   M2 = M beta_i
+//     dk   = dk_part + (A beta 2^gamma)_col^T dW + M2 K + M2^T K
+//     dv   = (A^T dU) beta_i
+//     dbeta= colsum(A . dW K^T) 2^gamma + colsum(A . dU V^T) + rowsum(M . K K^T)
+//     dG   = dG_part + colsum(A . dW K^T) beta 2^gamma + beta rowsum(M . K K^T) - colsum(M2 . K K^T)
+//     dg   = reverse cumsum of dG inside the chunk
+// All row scalings are folded into operands and all 128-wide row-dots are replaced by sums over 64x64
+// tiles that exist anyway (dW K^T, dU V^T, K K^T), so the three dk terms accumulate in one TMEM tile.
+// One CTA (4 warps) per (chunk, q/k head); 256 TMEM columns and ~99 KiB shared memory: two CTAs per SM.
+#include "tc5_tile.cuh"
+
+namespace gdn {
+namespace {
+
+constexpr int NTHREADS = 128;
+__device__ int g_wy_timeout = 0;
+
+template <int DK, int DV>
+struct WyTcSmem {
+  static constexpr size_t o_k = 0;
+  static constexpr size_t o_v = o_k + BT * DK * 2;     // V; later dA (8 KiB) | Y (8 KiB)
+  static constexpr size_t v_bytes = BT * DV * 2 > 2 * BT * 128 ? BT * DV * 2 : 2 * BT * 128;
+  static constexpr size_t o_du = o_v + v_bytes;
+  static constexpr size_t o_a = o_du + BT * DV * 2;    // A
+  static constexpr size_t o_ab = o_a + BT * 128;       // A (beta 2^gamma)_col
+  static constexpr size_t o_h = o_ab + BT * 128;       // h [DK][DV]; later dW (BT*DK*2) | dv staging / M2
+  static constexpr size_t h_bytes = DK * DV * 2 > BT * DK * 2 + BT * DV * 2 ? DK * DV * 2 : BT * DK * 2 + BT * DV * 2;
+  static constexpr size_t o_vec = o_h + h_bytes;
+  static constexpr size_t bytes = o_vec + 4096 + 1024;
+};
+
+// sum over the 8 row-lanes of a warp (lanes that differ in bits 2..4), result valid in lanes with g == 0
+__device__ __forceinline__ float sum_over_g(float x) {
+  x += __shfl_xor_sync(0xffffffffu, x, 4);
+  x += __shfl_xor_sync(0xffffffffu, x, 8);
+  x += __shfl_xor_sync(0xffffffffu, x, 16);
+  return x;
+}
+__device__ __forceinline__ float sum_over_t(float x) {
+  x += __shfl_xor_sync(0xffffffffu, x, 1);
+  x += __shfl_xor_sync(0xffffffffu, x, 2);
+  return x;
+}
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(NTHREADS) bwd_wy_kernel(const b200gdn_chunk_args a) {
+  using S = WyTcSmem<DK, DV>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* Ks = smem + S::o_k;
+  unsigned char* Vs = smem + S::o_v;
+  unsigned char* dAs = smem + S::o_v;
+  unsigned char* Ys = smem + S::o_v + BT * 128;
+  unsigned char* dUs = smem + S::o_du;
+  unsigned char* As = smem + S::o_a;
+  unsigned char* Abs = smem + S::o_ab;
+  unsigned char* Hs = smem + S::o_h;
+  unsigned char* dWs = smem + S::o_h;
+  unsigned char* Stg = smem + S::o_h + BT * DK * 2;   // dv staging, then M2
+  unsigned char* M2s = Stg;
+  float* gs = reinterpret_cast<float*>(smem + S::o_vec);
+  float* bet = gs + BT;
+  float* bge = bet + BT;
+  float* eg = bge + BT;
+  float* dGin = eg + BT;
+  float* dGs = dGin + BT;
+  float* c_kbg = dGs + BT;   // colsum(A . dW K^T)
+  float* c_vb = c_kbg + BT;  // colsum(A . dU V^T)
+  float* c_m2 = c_vb + BT;   // colsum(M2 . K K^T)
+  float* r_mk = c_m2 + BT;   // rowsum(M . K K^T)
+  uint64_t* bar = reinterpret_cast<uint64_t*>(r_mk + BT);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int c = blockIdx.x, hq = blockIdx.y;
+  const int G = a.HV / a.H;
+  const ChunkMeta cm = load_chunk_meta(a.chunk_meta, c);
+  const int64_t row0 = cm.row;
+  const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
+
+  if (warp == 0) tc5::tmem_alloc(tmem_slot, 256);
+  if (tid == 0) {
+    tc5::mbar_init(bar, 1);
+    tc5::fence_mbar_init();
+  }
+  load_tile_swz<BT, DK, NTHREADS>(Ks, reinterpret_cast<const __nv_bfloat16*>(a.k) + (row0 * a.H + hq) * DK, (int64_t)a.H * DK,
+                                  cm.len, tid);
+  cp_async_commit();
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tm = *tmem_slot;
+  const uint32_t TM_BIG = tm, TM_S1 = tm + 128, TM_KK = tm + 192;   // 128 | 64 | 64 columns
+  PhaseBarrier ph{bar, 0u, &g_wy_timeout};
+  bool failed = false;
+
+  const Operand opK_k{tc5::smem_addr(Ks), BT, 0};    // K as (n = token, k = key dim)
+  const Operand opK_mn{tc5::smem_addr(Ks), BT, 1};   // K as (k = token, n = key dim)
+  const Operand opA_k{tc5::smem_addr(As), BT, 0};    // A as (n = row j, k = col b)
+  const Operand opA_mn{tc5::smem_addr(As), BT, 1};   // A^T : (m = col, k = row)
+  const Operand opAb_mn{tc5::smem_addr(Abs), BT, 1};
+  const Operand opdU_k{tc5::smem_addr(dUs), BT, 0};
+  const Operand opdU_mn{tc5::smem_addr(dUs), BT, 1};
+  const Operand opdW_k{tc5::smem_addr(dWs), BT, 0};
+  const Operand opdW_mn{tc5::smem_addr(dWs), BT, 1};
+
+  for (int gi = 0; gi < G && !failed; ++gi) {
+    const int hv = hq * G + gi;
+    const bool last = gi == G - 1;
+    __syncthreads();
+    load_tile_swz<BT, DV, NTHREADS>(Vs, reinterpret_cast<const __nv_bfloat16*>(a.v) + (row0 * a.HV + hv) * DV,
+                                    (int64_t)a.HV * DV, cm.len, tid);
+    load_tile_swz<BT, DV, NTHREADS>(dUs, reinterpret_cast<const __nv_bfloat16*>(a.dv2) + (row0 * a.HV + hv) * DV,
+                                    (int64_t)a.HV * DV, cm.len, tid);
+    load_tile_swz<BT, BT, NTHREADS>(As, reinterpret_cast<const __nv_bfloat16*>(a.A) + (row0 * a.HV + hv) * BT,
+                                    (int64_t)a.HV * BT, cm.len, tid);
+    load_tile_swz<DK, DV, NTHREADS>(Hs, reinterpret_cast<const __nv_bfloat16*>(a.h) + ((int64_t)c * a.HV + hv) * DK * DV, DV, DK,
+                                    tid);
+    cp_async_commit();
+    load_gamma(gs, a.gamma, cm.row, cm.len, a.HV, hv, tid);
+    if (tid < BT) {
+      const bool ok = tid < cm.len;
+      bet[tid] = ok ? a.beta[(row0 + tid) * a.HV + hv] : 0.f;
+      dGin[tid] = ok ? a.dG[(row0 + tid) * a.HV + hv] : 0.f;
+      c_kbg[tid] = 0.f;
+      c_vb[tid] = 0.f;
+      c_m2[tid] = 0.f;
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+    if (tid < BT) {
+      const float e = exp2f(gs[tid]);
+      eg[tid] = e;
+      bge[tid] = bet[tid] * e;
+    }
+    __syncthreads();
+    // A with its columns scaled by beta 2^gamma
+    for (int idx = tid; idx < BT * BT / 2; idx += NTHREADS) {
+      const int i = idx / (BT / 2), j = (idx % (BT / 2)) * 2;
+      const float2 x = swz_ld2(As, i, j, BT);
+      *swz_ptr32(Abs, i, j, BT) = pack_bf16(x.x * bge[j], x.y * bge[j + 1]);
+    }
+    tc5::fence_async_smem();
+    __syncthreads();
+
+    // ---- phase 1: dW = -dU h^T | dA2 = dU V^T | KK = K K^T
+    if (tid == 0) {
+      tc5::fence_after_sync();
+      issue_mma(TM_BIG, opdU_k, Operand{tc5::smem_addr(Hs), DK, 0}, 64, DK, DV / 16, 0, /*neg_a=*/1);
+      issue_mma(TM_S1, opdU_k, Operand{tc5::smem_addr(Vs), BT, 0}, 64, 64, DV / 16, 0);
+      issue_mma(TM_KK, opK_k, opK_k, 64, 64, DK / 16, 0);
+      ph.commit();
+    }
+    const float g_lo = gs[r_lo], g_hi = gs[r_hi];
+    const float b_lo = bet[r_lo], b_hi = bet[r_hi];
+    if (__syncthreads_or(!ph.wait())) { failed = true; break; }
+
+    // ---- epilogue 1: dW -> shared (over the h buffer); dA2 -> registers; colsum(A . dA2)
+#pragma unroll
+    for (int b = 0; b < DK / 32; ++b) {
+      float r[16];
+      acc_ld32(TM_BIG, warp, b * 32, r);
+      tc5::tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int col = b * 32 + i * 8 + 2 * t;
+        *swz_ptr32(dWs, r_lo, col, BT) = pack_bf16(r[4 * i], r[4 * i + 1]);
+        *swz_ptr32(dWs, r_hi, col, BT) = pack_bf16(r[4 * i + 2], r[4 * i + 3]);
+      }
+    }
+    float dA2[2][16];
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      acc_ld32(TM_S1, warp, b * 32, dA2[b]);
+    }
+    tc5::tmem_ld_wait();
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int col = b * 32 + i * 8 + 2 * t;
+        const float2 al = swz_ld2(As, r_lo, col, BT), ah = swz_ld2(As, r_hi, col, BT);
+        float s0 = sum_over_g(al.x * dA2[b][4 * i] + ah.x * dA2[b][4 * i + 2]);
+        float s1 = sum_over_g(al.y * dA2[b][4 * i + 1] + ah.y * dA2[b][4 * i + 3]);
+        if (g == 0) {
+          atomicAdd(&c_vb[col], s0);
+          atomicAdd(&c_vb[col + 1], s1);
+        }
+      }
+    }
+    tc5::fence_async_smem();
+    tc5::fence_before_sync();
+    __syncthreads();
+
+    // ---- phase 2: dA1 = dW K^T | dVb = A^T dU
+    if (tid == 0) {
+      tc5::fence_after_sync();
+      issue_mma(TM_S1, opdW_k, opK_k, 64, 64, DK / 16, 0);
+      issue_mma(TM_BIG, opA_mn, opdU_mn, 64, DV, 4, 0);
+      ph.commit();
+    }
+    if (__syncthreads_or(!ph.wait())) { failed = true; break; }
+
+    // ---- epilogue 2: dA -> shared (over V); colsum(A . dA1); dv = dVb beta -> global
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      float r[16];
+      acc_ld32(TM_S1, warp, b * 32, r);
+      tc5::tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int col = b * 32 + i * 8 + 2 * t;
+        const float2 al = swz_ld2(As, r_lo, col, BT), ah = swz_ld2(As, r_hi, col, BT);
+        float s0 = sum_over_g(al.x * r[4 * i] + ah.x * r[4 * i + 2]);
+        float s1 = sum_over_g(al.y * r[4 * i + 1] + ah.y * r[4 * i + 3]);
+        if (g == 0) {
+          atomicAdd(&c_kbg[col], s0);
+          atomicAdd(&c_kbg[col + 1], s1);
+        }
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int ii = (e & 2) ? r_hi : r_lo, jj = col + (e & 1);
+          v[e] = (ii > jj) ? r[4 * i + e] * bge[jj] + dA2[b][4 * i + e] * bet[jj] : 0.f;
+        }
+        *swz_ptr32(dAs, r_lo, col, BT) = pack_bf16(v[0], v[1]);
+        *swz_ptr32(dAs, r_hi, col, BT) = pack_bf16(v[2], v[3]);
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < DV / 32; ++b) {
+      float r[16];
+      acc_ld32(TM_BIG, warp, b * 32, r);
+      tc5::tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int col = b * 32 + i * 8 + 2 * t;
+        *swz_ptr32(Stg, r_lo, col, BT) = pack_bf16(r[4 * i] * b_lo, r[4 * i + 1] * b_lo);
+        *swz_ptr32(Stg, r_hi, col, BT) = pack_bf16(r[4 * i + 2] * b_hi, r[4 * i + 3] * b_hi);
+      }
+    }
+    tc5::fence_async_smem();
+    tc5::fence_before_sync();
+    __syncthreads();
+
+    // ---- phase 3: Y = dA A^T | dk = (A beta 2^gamma)^T dW
+    if (tid == 0) {
+      tc5::fence_after_sync();
+      issue_mma(TM_S1, Operand{tc5::smem_addr(dAs), BT, 0}, opA_k, 64, 64, 4, 0);
+      issue_mma(TM_BIG, opAb_mn, opdW_mn, 64, DK, 4, 0);
+      ph.commit();
+    }
+    store_tile_swz<BT, DV, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.dv) + (row0 * a.HV + hv) * DV, (int64_t)a.HV * DV, Stg,
+                                     cm.len, tid);
+    if (__syncthreads_or(!ph.wait())) { failed = true; break; }
+
+    // ---- epilogue 3: Y -> shared
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      float r[16];
+      acc_ld32(TM_S1, warp, b * 32, r);
+      tc5::tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int col = b * 32 + i * 8 + 2 * t;
+        *swz_ptr32(Ys, r_lo, col, BT) = pack_bf16(r[4 * i], r[4 * i + 1]);
+        *swz_ptr32(Ys, r_hi, col, BT) = pack_bf16(r[4 * i + 2], r[4 * i + 3]);
+      }
+    }
+    tc5::fence_async_smem();
+    tc5::fence_before_sync();
+    __syncthreads();
+
+    // ---- phase 4: X = A^T Y
+    if (tid == 0) {
+      tc5::fence_after_sync();
+      issue_mma(TM_S1, opA_mn, Operand{tc5::smem_addr(Ys), BT, 1}, 64, 64, 4, 0);
+      ph.commit();
+    }
+    if (__syncthreads_or(!ph.wait())) { failed = true; break; }
+
+    // ---- epilogue 4: M, M2 = M beta_i -> shared; rowsum(M . KK), colsum(M2 . KK)
+    float rmk_lo = 0.f, rmk_hi = 0.f;
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      float r[16], kk[16];
+      acc_ld32(TM_S1, warp, b * 32, r);
+      acc_ld32(TM_KK, warp, b * 32, kk);
+      tc5::tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int col = b * 32 + i * 8 + 2 * t;
+        float m[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int ii = (e & 2) ? r_hi : r_lo, jj = col + (e & 1);
+          const float gi_ = (e & 2) ? g_hi : g_lo;
+          m[e] = (ii > jj) ? -r[4 * i + e] * exp2f(gi_ - gs[jj]) : 0.f;
+        }
+        rmk_lo += m[0] * kk[4 * i] + m[1] * kk[4 * i + 1];
+        rmk_hi += m[2] * kk[4 * i + 2] + m[3] * kk[4 * i + 3];
+        const float m20 = m[0] * b_lo, m21 = m[1] * b_lo, m22 = m[2] * b_hi, m23 = m[3] * b_hi;
+        float s0 = sum_over_g(m20 * kk[4 * i] + m22 * kk[4 * i + 2]);
+        float s1 = sum_over_g(m21 * kk[4 * i + 1] + m23 * kk[4 * i + 3]);
+        if (g == 0) {
+          atomicAdd(&c_m2[col], s0);
+          atomicAdd(&c_m2[col + 1], s1);
+        }
+        *swz_ptr32(M2s, r_lo, col, BT) = pack_bf16(m20, m21);
+        *swz_ptr32(M2s, r_hi, col, BT) = pack_bf16(m22, m23);
+      }
+    }
+    rmk_lo = sum_over_t(rmk_lo);
+    rmk_hi = sum_over_t(rmk_hi);
+    if (t == 0) {
+      r_mk[r_lo] = rmk_lo;
+      r_mk[r_hi] = rmk_hi;
+    }
+    tc5::fence_async_smem();
+    tc5::fence_before_sync();
+    __syncthreads();
+
+    // ---- phase 5: dk += M2 K + M2^T K
+    if (tid == 0) {
+      tc5::fence_after_sync();
+      issue_mma(TM_BIG, Operand{tc5::smem_addr(M2s), BT, 0}, opK_mn, 64, DK, 4, 1);
+      issue_mma(TM_BIG, Operand{tc5::smem_addr(M2s), BT, 1}, opK_mn, 64, DK, 4, 1);
+      ph.commit();
+    }
+    // gate / beta gradients while the MMAs run
+    if (tid < BT) {
+      const int i = tid;
+      dGs[i] = c_kbg[i] * bge[i] + bet[i] * r_mk[i] - c_m2[i] + dGin[i];
+      if (i < cm.len) a.dbeta[(row0 + i) * a.HV + hv] = c_kbg[i] * eg[i] + c_vb[i] + r_mk[i];
+    }
+    if (__syncthreads_or(!ph.wait())) { failed = true; break; }
+    if (tid < cm.len) {
+      float s = 0.f;
+      for (int j = BT - 1; j >= tid; --j) s += dGs[j];
+      a.dg[(row0 + tid) * a.HV + hv] = s;
+    }
+
+    // ---- epilogue 5: dk = accumulator + part from the dq/dk kernel (group-accumulated in fp32)
+    {
+      float* buf = a.dk_part + (row0 * a.H + hq) * DK;
+      const int64_t stride = (int64_t)a.H * DK;
+#pragma unroll
+      for (int b = 0; b < DK / 32; ++b) {
+        float r[16];
+        acc_ld32(TM_BIG, warp, b * 32, r);
+        tc5::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int col = b * 32 + i * 8 + 2 * t;
+          if (r_lo < cm.len) {
+            float2* pp = reinterpret_cast<float2*>(buf + r_lo * stride + col);
+            const float2 o = *pp;
+            r[4 * i] += o.x; r[4 * i + 1] += o.y;
+            if (!last) *pp = make_float2(r[4 * i], r[4 * i + 1]);
+          }
+          if (r_hi < cm.len) {
+            float2* pp = reinterpret_cast<float2*>(buf + r_hi * stride + col);
+            const float2 o = *pp;
+            r[4 * i + 2] += o.x; r[4 * i + 3] += o.y;
+            if (!last) *pp = make_float2(r[4 * i + 2], r[4 * i + 3]);
+          }
+          if (last) {
+            *swz_ptr32(dWs, r_lo, col, BT) = pack_bf16(r[4 * i], r[4 * i + 1]);
+            *swz_ptr32(dWs, r_hi, col, BT) = pack_bf16(r[4 * i + 2], r[4 * i + 3]);
+          }
+        }
+      }
+    }
+    tc5::fence_before_sync();
+    __syncthreads();
+    if (last)
+      store_tile_swz<BT, DK, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.dk) + (row0 * a.H + hq) * DK, (int64_t)a.H * DK, dWs,
+                                       cm.len, tid);
+  }
+
+  if (failed && tid == 0) atomicExch(&g_wy_timeout, 1);
+  tc5::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc5::tmem_dealloc(tm, 256);
+}
+
+template <int DK, int DV>
+int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
+  using S = WyTcSmem<DK, DV>;
+  if (int e = ensure_smem(bwd_wy_kernel<DK, DV>, S::bytes)) return e;
+  dim3 grid(a.n_chunks, a.H);
+  bwd_wy_kernel<DK, DV><<<grid, NTHREADS, S::bytes, st>>>(a);
+  return check_launch("bwd_wy");
+}
+
+}  // namespace
+
+int launch_bwd_wy(const b200gdn_chunk_args& a, cudaStream_t st) {
+  if (a.K == 128 && a.V == 128) return launch<128, 128>(a, st);
+  if (a.K == 64 && a.V == 64) return launch<64, 64>(a, st);
+  return set_error(B200GDN_ERR_UNSUPPORTED, "bwd_wy: K=%d V=%d not built (64/64 and 128/128 are)", a.K, a.V);
+}
+
+int bwd_wy_timeout_flag() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_wy_timeout, sizeof(int));
+  return v;
+}
+
+}  // namespace gdn

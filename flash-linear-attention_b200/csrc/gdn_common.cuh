@@ -268,8 +268,8 @@ int launch_scan_fwd(const b200gdn_chunk_args& a, cudaStream_t st);
 int launch_out_fwd(const b200gdn_chunk_args& a, cudaStream_t st);
 int launch_dv_local(const b200gdn_chunk_args& a, cudaStream_t st);
 int launch_scan_bwd(const b200gdn_chunk_args& a, cudaStream_t st);
-int launch_dqkwg(const b200gdn_chunk_args& a, cudaStream_t st);
-int launch_wy_bwd(const b200gdn_chunk_args& a, cudaStream_t st);
+int launch_bwd_dqk(const b200gdn_chunk_args& a, cudaStream_t st);
+int launch_bwd_wy(const b200gdn_chunk_args& a, cudaStream_t st);
 int launch_recurrent(const b200gdn_recurrent_args& a, cudaStream_t st);
 int launch_affine(const b200gdn_affine_args& a, cudaStream_t st);
 int set_error(int code, const char* fmt, ...);

@@ -1,0 +1,95 @@
+// Tile-level helpers on top of tc5.cuh: swizzled staging of bf16 tiles, MMA issue loops over the
+// contraction dimension, and accumulator read-back in the mma-fragment layout.
+#pragma once
+#include "gdn_common.cuh"
+#include "tc5.cuh"
+
+namespace gdn {
+
+// ---- global -> shared, canonical swizzled layout -----------------------------------------------------
+// [ROWS][COLS] bf16 tile, global row stride `gstride` elements; rows >= valid are zero-filled.
+// Destination: 64-column panels of ROWS*128 bytes, 16-byte chunks XOR-swizzled with (row & 7).
+template <int ROWS, int COLS, int NTHREADS>
+__device__ __forceinline__ void load_tile_swz(unsigned char* dst, const __nv_bfloat16* src, int64_t gstride, int valid,
+                                              int tid) {
+  constexpr int CPR = COLS / 8;
+  constexpr int TOTAL = ROWS * CPR;
+  static_assert(TOTAL % NTHREADS == 0, "tile/threads mismatch");
+#pragma unroll
+  for (int it = 0; it < TOTAL / NTHREADS; ++it) {
+    int idx = it * NTHREADS + tid;
+    int r = idx / CPR, c = idx % CPR;
+    bool ok = r < valid;
+    const __nv_bfloat16* g = src + (ok ? (int64_t)r * gstride : 0) + c * 8;
+    unsigned char* d = dst + (c >> 3) * (ROWS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+    cp_async16(d, g, ok);
+  }
+}
+
+// Swizzled tile -> global (16 bytes per access), rows < valid.
+template <int ROWS, int COLS, int NTHREADS>
+__device__ __forceinline__ void store_tile_swz(__nv_bfloat16* dst, int64_t gstride, const unsigned char* src, int valid,
+                                               int tid) {
+  constexpr int CPR = COLS / 8;
+  constexpr int TOTAL = ROWS * CPR;
+  static_assert(TOTAL % NTHREADS == 0, "tile/threads mismatch");
+#pragma unroll
+  for (int it = 0; it < TOTAL / NTHREADS; ++it) {
+    int idx = it * NTHREADS + tid;
+    int r = idx / CPR, c = idx % CPR;
+    if (r < valid) {
+      uint4 val = *reinterpret_cast<const uint4*>(src + (c >> 3) * (ROWS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+      *reinterpret_cast<uint4*>(dst + (int64_t)r * gstride + c * 8) = val;
+    }
+  }
+}
+
+__device__ __forceinline__ uint32_t* swz_ptr32(unsigned char* tile, int row, int col, int rows) {
+  return reinterpret_cast<uint32_t*>(tile + tc5::swz_offset(row, col, rows));
+}
+__device__ __forceinline__ float2 swz_ld2(const unsigned char* tile, int row, int col, int rows) {
+  return unpack_bf16(*reinterpret_cast<const uint32_t*>(tile + tc5::swz_offset(row, col, rows)));
+}
+
+// ---- MMA issue (one thread) -----------------------------------------------------------------------------
+// Operand descriptions.  A tile is stored [rows][cols]; as a K-major operand its MN index runs over rows
+// and the contraction over columns; as an MN-major operand the MN index runs over columns and the
+// contraction over rows.
+struct Operand {
+  uint32_t saddr;   // shared address of the tile (1024-byte aligned) plus any panel offset
+  int rows;         // rows of the stored tile (panel stride = rows * 128 bytes)
+  int mn_major;     // 0: K-major, 1: MN-major
+};
+__device__ __forceinline__ uint64_t operand_desc(const Operand& o, int kstep) {
+  if (o.mn_major) return tc5::smem_desc(o.saddr + kstep * 2048, o.rows * 128, 1024);
+  return tc5::smem_desc(o.saddr + (kstep >> 2) * o.rows * 128 + (kstep & 3) * 32, 16, 1024);
+}
+// D[tmem] (+)= A B over `ksteps` steps of 16.  `acc` = 0 starts a fresh accumulator.
+__device__ __forceinline__ void issue_mma(uint32_t d_tmem, const Operand& a, const Operand& b, int M, int N, int ksteps,
+                                          int acc, int neg_a = 0) {
+  const uint32_t idesc = tc5::idesc_bf16(M, N, a.mn_major, b.mn_major, neg_a);
+  for (int ks = 0; ks < ksteps; ++ks) tc5::mma_ss(d_tmem, operand_desc(a, ks), operand_desc(b, ks), idesc, (acc || ks > 0) ? 1u : 0u);
+}
+
+// ---- accumulator read-back -------------------------------------------------------------------------------
+// 16 rows x 32 columns of an M = 64 accumulator for this warp (rows 16*warp .. +15): r[4*i + e] is
+// n-tile i (columns c0 + 8i ..), e = {row g col 2t, row g col 2t+1, row g+8 col 2t, row g+8 col 2t+1}.
+__device__ __forceinline__ void acc_ld32(uint32_t tmem_acc, int warp, int c0, float (&r)[16]) {
+  tc5::tmem_ld_16x256b_x4(tmem_acc + ((uint32_t)(warp * 32) << 16) + c0, r);
+}
+
+// One phase boundary: the issuing thread commits, everybody waits for the MMAs (bounded).
+struct PhaseBarrier {
+  uint64_t* bar;
+  uint32_t parity;
+  int* err;
+  __device__ __forceinline__ void commit() { tc5::mma_commit(bar); }
+  __device__ __forceinline__ bool wait() {
+    bool ok = tc5::mbar_wait(bar, parity);
+    parity ^= 1u;
+    tc5::fence_after_sync();
+    return ok;
+  }
+};
+
+}  // namespace gdn

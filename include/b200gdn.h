@@ -46,8 +46,8 @@ typedef enum b200gdn_status {
 #define B200GDN_FWD_OUT 4u       /* o                      <- q, k, v_new, h, gamma */
 #define B200GDN_BWD_DVLOCAL 1u   /* dv2 (local part)       <- q, k, gamma, do */
 #define B200GDN_BWD_SCAN 2u      /* dh, dh0, dv2           <- q, k, w, gamma, do, dht */
-#define B200GDN_BWD_DQKWG 4u     /* dq, dk_part, dw, dG    <- q, k, v_new, gamma, h, dv2, do, dh */
-#define B200GDN_BWD_WY 8u        /* dk, dv, dbeta, dg      <- k, v, beta, gamma, A, dw, dv2, dk_part, dG */
+#define B200GDN_BWD_DQKWG 4u     /* dq, dk_part, dG        <- q, k, v_new, gamma, h, dv2, do, dh */
+#define B200GDN_BWD_WY 8u        /* dk, dv, dbeta, dg      <- k, v, beta, gamma, A, h, dv2, dk_part, dG */
 
 typedef struct b200gdn_chunk_args {
   int32_t struct_bytes;          /* = sizeof(b200gdn_chunk_args), checked */
@@ -87,7 +87,7 @@ typedef struct b200gdn_chunk_args {
   /* backward workspace */
   void* dh;                      /* bf16 [n_chunks,HV,K,V] */
   void* dv2;                     /* bf16 [rows,HV,V] */
-  void* dw;                      /* bf16 [rows,HV,K] */
+  void* dw;                      /* unused (dw = -dv2 h^T stays on chip); may be NULL */
   float* dk_part;                /* [rows,H,K] */
   float* dG;                     /* [rows,HV] */
   float* dq_acc;                 /* [rows,H,K], only read/written when HV > H */

@@ -56,7 +56,7 @@ def run_abi(d, dev='cuda', fwd_mask=0, bwd_mask=0, overrides=None, do_bwd=True):
         dv=torch.full((rows, HV, V), nan, **bf), dg=torch.full((rows, HV), nan, **f32),
         dbeta=torch.full((rows, HV), nan, **f32), dh0=torch.full((n_seq, HV, K, V), nan, **f32),
         dh=torch.full((n_chunks, HV, K, V), nan, **bf), dv2=torch.full((rows, HV, V), nan, **bf),
-        dw=torch.full((rows, HV, K), nan, **bf), dk_part=torch.full((rows, H, K), nan, **f32),
+        dk_part=torch.full((rows, H, K), nan, **f32),
         dG=torch.full((rows, HV), nan, **f32), dq_acc=torch.full((rows, H, K), nan, **f32),
     )
     a = new_chunk_args(q, k, v, d['scale'], (chunk_meta, seq_meta, (n_chunks, n_seq)))

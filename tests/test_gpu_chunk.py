@@ -25,7 +25,7 @@ STAGE_CASES = {
 
 # err-ratio bounds per tensor (bf16 storage: eps = 2^-8 = 0.0039 per rounding)
 FWD_TOL = dict(gamma=1e-5, A=0.005, w=0.005, u=0.005, h=0.005, v_new=0.005, ht=0.005, o=0.005)
-BWD_TOL = dict(dh=0.008, dh0=0.008, dv2=0.008, dq=0.008, dw=0.008, dk=0.008, dv=0.008, dbeta=0.02, dg=0.02)
+BWD_TOL = dict(dh=0.008, dh0=0.008, dv2=0.008, dq=0.008, dk=0.008, dv=0.008, dbeta=0.02, dg=0.02)
 
 
 @pytest.mark.parametrize('name', list(STAGE_CASES))
@@ -56,10 +56,10 @@ def test_backward_stages_isolated(name):
     for n in ('dh', 'dh0', 'dv2'):
         O.assert_close(n, bwd[n], o2[n], 0.005)
     o3 = run_abi(d, fwd_mask=-1, bwd_mask=_lib.BWD_DQKWG, overrides=dict(saved, dv2=bwd['dv2'], dh=bwd['dh']))
-    for n, m in (('dq', 'dq'), ('dk_part', 'dk_part'), ('dw', 'dw'), ('dG', 'dG')):
+    for n, m in (('dq', 'dq'), ('dk_part', 'dk_part'), ('dG', 'dG')):
         O.assert_close(n, bwd[m], o3[n], 0.005)
     o4 = run_abi(d, fwd_mask=-1, bwd_mask=_lib.BWD_WY,
-                 overrides=dict(saved, dv2=bwd['dv2'], dw=bwd['dw'], dk_part=bwd['dk_part'], dG=bwd['dG']))
+                 overrides=dict(saved, dv2=bwd['dv2'], dk_part=bwd['dk_part'], dG=bwd['dG']))
     for n in ('dk', 'dv', 'dbeta', 'dg'):
         O.assert_close(n, bwd[n], o4[n], 0.005)
 
