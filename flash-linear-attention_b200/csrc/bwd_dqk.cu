@@ -191,11 +191,13 @@ __global__ void __launch_bounds__(NTHREADS) bwd_dqk_kernel(const b200gdn_chunk_a
 
     // ---- epilogue 2: dq
     float rq_lo = 0.f, rq_hi = 0.f;
+    float racc[DK / 32][16];
+#pragma unroll
+    for (int b = 0; b < DK / 32; ++b) acc_ld32(TM_DQ, warp, b * 32, racc[b]);
+    tc5::tmem_ld_wait();
 #pragma unroll
     for (int b = 0; b < DK / 32; ++b) {
-      float r[16];
-      acc_ld32(TM_DQ, warp, b * 32, r);
-      tc5::tmem_ld_wait();
+      float (&r)[16] = racc[b];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int col = b * 32 + i * 8 + 2 * t;

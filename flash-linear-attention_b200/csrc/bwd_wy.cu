@@ -164,16 +164,19 @@ __global__ void __launch_bounds__(NTHREADS) bwd_wy_kernel(const b200gdn_chunk_ar
     if (__syncthreads_or(!ph.wait())) { failed = true; break; }
 
     // ---- epilogue 1: dW -> shared (over the h buffer); dA2 -> registers; colsum(A . dA2)
+    {
+      float r[DK / 32][16];
 #pragma unroll
-    for (int b = 0; b < DK / 32; ++b) {
-      float r[16];
-      acc_ld32(TM_BIG, warp, b * 32, r);
+      for (int b = 0; b < DK / 32; ++b) acc_ld32(TM_BIG, warp, b * 32, r[b]);
       tc5::tmem_ld_wait();
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int col = b * 32 + i * 8 + 2 * t;
-        *swz_ptr32(dWs, r_lo, col, BT) = pack_bf16(r[4 * i], r[4 * i + 1]);
-        *swz_ptr32(dWs, r_hi, col, BT) = pack_bf16(r[4 * i + 2], r[4 * i + 3]);
+      for (int b = 0; b < DK / 32; ++b) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int col = b * 32 + i * 8 + 2 * t;
+          *swz_ptr32(dWs, r_lo, col, BT) = pack_bf16(r[b][4 * i], r[b][4 * i + 1]);
+          *swz_ptr32(dWs, r_hi, col, BT) = pack_bf16(r[b][4 * i + 2], r[b][4 * i + 3]);
+        }
       }
     }
     float dA2[2][16];
@@ -235,16 +238,19 @@ __global__ void __launch_bounds__(NTHREADS) bwd_wy_kernel(const b200gdn_chunk_ar
         *swz_ptr32(dAs, r_hi, col, BT) = pack_bf16(v[2], v[3]);
       }
     }
+    {
+      float r[DV / 32][16];
 #pragma unroll
-    for (int b = 0; b < DV / 32; ++b) {
-      float r[16];
-      acc_ld32(TM_BIG, warp, b * 32, r);
+      for (int b = 0; b < DV / 32; ++b) acc_ld32(TM_BIG, warp, b * 32, r[b]);
       tc5::tmem_ld_wait();
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int col = b * 32 + i * 8 + 2 * t;
-        *swz_ptr32(Stg, r_lo, col, BT) = pack_bf16(r[4 * i] * b_lo, r[4 * i + 1] * b_lo);
-        *swz_ptr32(Stg, r_hi, col, BT) = pack_bf16(r[4 * i + 2] * b_hi, r[4 * i + 3] * b_hi);
+      for (int b = 0; b < DV / 32; ++b) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int col = b * 32 + i * 8 + 2 * t;
+          *swz_ptr32(Stg, r_lo, col, BT) = pack_bf16(r[b][4 * i] * b_lo, r[b][4 * i + 1] * b_lo);
+          *swz_ptr32(Stg, r_hi, col, BT) = pack_bf16(r[b][4 * i + 2] * b_hi, r[b][4 * i + 3] * b_hi);
+        }
       }
     }
     tc5::fence_async_smem();
@@ -335,6 +341,16 @@ __global__ void __launch_bounds__(NTHREADS) bwd_wy_kernel(const b200gdn_chunk_ar
       issue_mma(TM_BIG, Operand{tc5::smem_addr(M2s), BT, 1}, opK_mn, 64, DK, 4, 1);
       ph.commit();
     }
+    // the dq/dk kernel's part of dk: fetched now so that its latency hides behind the MMAs
+    float* const dkbuf = a.dk_part + (row0 * a.H + hq) * DK;
+    const int64_t dkstride = (int64_t)a.H * DK;
+    float2 part[DK / 8][2];
+#pragma unroll
+    for (int n8 = 0; n8 < DK / 8; ++n8) {
+      const int col = n8 * 8 + 2 * t;
+      part[n8][0] = r_lo < cm.len ? *reinterpret_cast<const float2*>(dkbuf + r_lo * dkstride + col) : make_float2(0.f, 0.f);
+      part[n8][1] = r_hi < cm.len ? *reinterpret_cast<const float2*>(dkbuf + r_hi * dkstride + col) : make_float2(0.f, 0.f);
+    }
     // gate / beta gradients while the MMAs run
     if (tid < BT) {
       const int i = tid;
@@ -350,31 +366,23 @@ __global__ void __launch_bounds__(NTHREADS) bwd_wy_kernel(const b200gdn_chunk_ar
 
     // ---- epilogue 5: dk = accumulator + part from the dq/dk kernel (group-accumulated in fp32)
     {
-      float* buf = a.dk_part + (row0 * a.H + hq) * DK;
-      const int64_t stride = (int64_t)a.H * DK;
+      float r[DK / 32][16];
+#pragma unroll
+      for (int b = 0; b < DK / 32; ++b) acc_ld32(TM_BIG, warp, b * 32, r[b]);
+      tc5::tmem_ld_wait();
 #pragma unroll
       for (int b = 0; b < DK / 32; ++b) {
-        float r[16];
-        acc_ld32(TM_BIG, warp, b * 32, r);
-        tc5::tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int col = b * 32 + i * 8 + 2 * t;
-          if (r_lo < cm.len) {
-            float2* pp = reinterpret_cast<float2*>(buf + r_lo * stride + col);
-            const float2 o = *pp;
-            r[4 * i] += o.x; r[4 * i + 1] += o.y;
-            if (!last) *pp = make_float2(r[4 * i], r[4 * i + 1]);
-          }
-          if (r_hi < cm.len) {
-            float2* pp = reinterpret_cast<float2*>(buf + r_hi * stride + col);
-            const float2 o = *pp;
-            r[4 * i + 2] += o.x; r[4 * i + 3] += o.y;
-            if (!last) *pp = make_float2(r[4 * i + 2], r[4 * i + 3]);
-          }
-          if (last) {
-            *swz_ptr32(dWs, r_lo, col, BT) = pack_bf16(r[4 * i], r[4 * i + 1]);
-            *swz_ptr32(dWs, r_hi, col, BT) = pack_bf16(r[4 * i + 2], r[4 * i + 3]);
+          const int n8 = b * 4 + i, col = n8 * 8 + 2 * t;
+          const float d0 = r[b][4 * i] + part[n8][0].x, d1 = r[b][4 * i + 1] + part[n8][0].y;
+          const float d2 = r[b][4 * i + 2] + part[n8][1].x, d3 = r[b][4 * i + 3] + part[n8][1].y;
+          if (!last) {
+            if (r_lo < cm.len) *reinterpret_cast<float2*>(dkbuf + r_lo * dkstride + col) = make_float2(d0, d1);
+            if (r_hi < cm.len) *reinterpret_cast<float2*>(dkbuf + r_hi * dkstride + col) = make_float2(d2, d3);
+          } else {
+            *swz_ptr32(dWs, r_lo, col, BT) = pack_bf16(d0, d1);
+            *swz_ptr32(dWs, r_hi, col, BT) = pack_bf16(d2, d3);
           }
         }
       }

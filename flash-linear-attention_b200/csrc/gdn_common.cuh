@@ -36,6 +36,9 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool pr
   int bytes = pred ? 16 : 0;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
 }
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_u32(smem)), "l"(gmem));
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
@@ -256,6 +259,14 @@ __device__ __forceinline__ void load_gamma(float* gs, const float* gamma, int ro
   if (tid < BT) {
     int r = tid < len ? tid : len - 1;
     gs[tid] = gamma[(int64_t)(row0 + r) * HV + hv];
+  }
+}
+
+// Same through the async-copy path, so that the loading threads do not stall on the global latency.
+__device__ __forceinline__ void load_gamma_async(float* gs, const float* gamma, int row0, int len, int HV, int hv, int tid) {
+  if (tid < BT) {
+    int r = tid < len ? tid : len - 1;
+    cp_async4(gs + tid, gamma + (int64_t)(row0 + r) * HV + hv);
   }
 }
 

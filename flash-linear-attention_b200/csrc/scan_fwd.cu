@@ -52,8 +52,7 @@ __global__ void __launch_bounds__(128 * (BV / 32)) scan_fwd_kernel(const b200gdn
   const __nv_bfloat16* ubase = reinterpret_cast<const __nv_bfloat16*>(a.u);
 
   auto stage_ptr = [&](int s) { return smem + (size_t)s * S::stage_bytes; };
-  auto issue_loads = [&](int c, int s) {
-    const ChunkMeta cm = load_chunk_meta(a.chunk_meta, c);
+  auto issue_loads = [&](const ChunkMeta& cm, int s) {
     unsigned char* base = stage_ptr(s);
     __nv_bfloat16* Wt = reinterpret_cast<__nv_bfloat16*>(base);
     __nv_bfloat16* Kt = reinterpret_cast<__nv_bfloat16*>(base + S::w_bytes);
@@ -63,7 +62,7 @@ __global__ void __launch_bounds__(128 * (BV / 32)) scan_fwd_kernel(const b200gdn
     load_tile_async<DK, NTHREADS>(Kt, kbase + ((int64_t)cm.row * a.H + hq) * DK, (int64_t)a.H * DK, cm.len, tid);
     if (ubase != nullptr)
       load_tile_async<BV, NTHREADS>(Ut, ubase + ((int64_t)cm.row * a.HV + hv) * DV + v0, (int64_t)a.HV * DV, cm.len, tid);
-    load_gamma(gs, a.gamma, cm.row, cm.len, a.HV, hv, tid);
+    load_gamma_async(gs, a.gamma, cm.row, cm.len, a.HV, hv, tid);
   };
 
   // state fragments: rows rg*(DK/4) + mt*16 + {g, g+8}, columns cg*32 + nt*8 + 2t + {0,1}
@@ -82,12 +81,16 @@ __global__ void __launch_bounds__(128 * (BV / 32)) scan_fwd_kernel(const b200gdn
         }
   }
 
-  if (nc > 0) issue_loads(c_first, 0);
+  // chunk descriptors are fetched two iterations ahead so that no global-load latency sits on the chain
+  ChunkMeta cm_cur = load_chunk_meta(a.chunk_meta, c_first + (nc > 0 ? 0 : 0));
+  ChunkMeta cm_nxt = load_chunk_meta(a.chunk_meta, c_first + (nc > 1 ? 1 : 0));
+  if (nc > 0) issue_loads(cm_cur, 0);
   cp_async_commit();
 
   for (int ic = 0; ic < nc; ++ic) {
     const int c = c_first + ic, s = ic & 1;
-    const ChunkMeta cm = load_chunk_meta(a.chunk_meta, c);
+    const ChunkMeta cm = cm_cur;
+    const ChunkMeta cm_nn = load_chunk_meta(a.chunk_meta, c_first + (ic + 2 < nc ? ic + 2 : ic));
     unsigned char* base = stage_ptr(s);
     const __nv_bfloat16* Wt = reinterpret_cast<const __nv_bfloat16*>(base);
     const __nv_bfloat16* Kt = reinterpret_cast<const __nv_bfloat16*>(base + S::w_bytes);
@@ -96,8 +99,10 @@ __global__ void __launch_bounds__(128 * (BV / 32)) scan_fwd_kernel(const b200gdn
 
     cp_async_wait<0>();
     __syncthreads();  // stage s landed; every warp is done with the previous chunk (stage s^1, Sb, Vt)
-    if (ic + 1 < nc) issue_loads(c + 1, s ^ 1);
+    if (ic + 1 < nc) issue_loads(cm_nxt, s ^ 1);
     cp_async_commit();
+    cm_cur = cm_nxt;
+    cm_nxt = cm_nn;
 
     // bf16 snapshot of the state -> shared (operand of W S) and -> global h_c
 #pragma unroll
