@@ -17,24 +17,25 @@
 namespace gdn {
 namespace {
 
-template <int DK, int BV>
+template <int DK, int BV, int NSTAGE>
 struct ScanFwdSmem {
   static constexpr int LDK = DK + PAD, LDB = BV + PAD;
   static constexpr size_t w_bytes = sizeof(__nv_bfloat16) * BT * LDK;
   static constexpr size_t u_bytes = sizeof(__nv_bfloat16) * BT * LDB;
   static constexpr size_t stage_bytes = 2 * w_bytes + u_bytes + sizeof(float) * BT;  // W, K, U-slice, gamma
-  static constexpr size_t sb_off = 2 * stage_bytes;                                   // bf16 state [DK][LDB]
+  static constexpr size_t sb_off = NSTAGE * stage_bytes;                                   // bf16 state [DK][LDB]
   static constexpr size_t vn_off = sb_off + sizeof(__nv_bfloat16) * DK * LDB;         // bf16 v_new slice
   static constexpr size_t vt_off = vn_off + u_bytes;                                  // bf16 gated v_new slice
   static constexpr size_t bytes = vt_off + u_bytes;
 };
 
-template <int DK, int DV, int BV>
-__global__ void __launch_bounds__(128 * (BV / 32)) scan_fwd_kernel(const b200gdn_chunk_args a) {
-  constexpr int NCG = BV / 32;          // column groups
+template <int DK, int DV, int BV, int NSTAGE, int CW>
+__global__ void __launch_bounds__(128 * (BV / CW)) scan_fwd_kernel(const b200gdn_chunk_args a) {
+  constexpr int NCG = BV / CW;          // column groups of CW columns
+  constexpr int NT = CW / 8;            // n-tiles per warp
   constexpr int NTHREADS = 128 * NCG;
   constexpr int MT = DK / 64;           // 16-row m-tiles of the state per warp (4 row groups)
-  using S = ScanFwdSmem<DK, BV>;
+  using S = ScanFwdSmem<DK, BV, NSTAGE>;
   extern __shared__ __align__(16) unsigned char smem[];
   __nv_bfloat16* Sb = reinterpret_cast<__nv_bfloat16*>(smem + S::sb_off);
   __nv_bfloat16* Vn = reinterpret_cast<__nv_bfloat16*>(smem + S::vn_off);
@@ -66,48 +67,54 @@ __global__ void __launch_bounds__(128 * (BV / 32)) scan_fwd_kernel(const b200gdn
   };
 
   // state fragments: rows rg*(DK/4) + mt*16 + {g, g+8}, columns cg*32 + nt*8 + 2t + {0,1}
-  float S_[MT][4][4];
+  float S_[MT][NT][4];
   {
     const float* h0 = a.h0 ? a.h0 + ((int64_t)n * a.HV + hv) * DK * DV : nullptr;
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
+      for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           int r = rg * (DK / 4) + mt * 16 + g + ((e >> 1) << 3);
-          int col = v0 + cg * 32 + nt * 8 + 2 * t + (e & 1);
+          int col = v0 + cg * CW + nt * 8 + 2 * t + (e & 1);
           S_[mt][nt][e] = h0 ? h0[(int64_t)r * DV + col] : 0.f;
         }
   }
 
-  // chunk descriptors are fetched two iterations ahead so that no global-load latency sits on the chain
-  ChunkMeta cm_cur = load_chunk_meta(a.chunk_meta, c_first + (nc > 0 ? 0 : 0));
-  ChunkMeta cm_nxt = load_chunk_meta(a.chunk_meta, c_first + (nc > 1 ? 1 : 0));
-  if (nc > 0) issue_loads(cm_cur, 0);
-  cp_async_commit();
+  // NSTAGE-deep prefetch: the tiles of chunk ic + NSTAGE - 1 are requested while chunk ic is processed, so
+  // neither the tile loads nor the chunk descriptors they depend on sit on the recurrence's critical path.
+  ChunkMeta cm_q[NSTAGE];
+#pragma unroll
+  for (int s = 0; s < NSTAGE; ++s) cm_q[s] = load_chunk_meta(a.chunk_meta, c_first + (s < nc ? s : 0));
+#pragma unroll
+  for (int s = 0; s < NSTAGE - 1; ++s) {
+    if (s < nc) issue_loads(cm_q[s], s);
+    cp_async_commit();
+  }
 
   for (int ic = 0; ic < nc; ++ic) {
-    const int c = c_first + ic, s = ic & 1;
-    const ChunkMeta cm = cm_cur;
-    const ChunkMeta cm_nn = load_chunk_meta(a.chunk_meta, c_first + (ic + 2 < nc ? ic + 2 : ic));
+    const int c = c_first + ic, s = ic % NSTAGE;
+    const ChunkMeta cm = cm_q[0];
+    const ChunkMeta cm_far = load_chunk_meta(a.chunk_meta, c_first + (ic + NSTAGE < nc ? ic + NSTAGE : ic));
     unsigned char* base = stage_ptr(s);
     const __nv_bfloat16* Wt = reinterpret_cast<const __nv_bfloat16*>(base);
     const __nv_bfloat16* Kt = reinterpret_cast<const __nv_bfloat16*>(base + S::w_bytes);
     const __nv_bfloat16* Ut = reinterpret_cast<const __nv_bfloat16*>(base + 2 * S::w_bytes);
     const float* gs = reinterpret_cast<const float*>(base + 2 * S::w_bytes + S::u_bytes);
 
-    cp_async_wait<0>();
-    __syncthreads();  // stage s landed; every warp is done with the previous chunk (stage s^1, Sb, Vt)
-    if (ic + 1 < nc) issue_loads(cm_nxt, s ^ 1);
+    cp_async_wait<NSTAGE - 2>();
+    __syncthreads();  // stage s landed; every warp is done with the previous chunk (its stage, Sb, Vt)
+    if (ic + NSTAGE - 1 < nc) issue_loads(cm_q[NSTAGE - 1], (ic + NSTAGE - 1) % NSTAGE);
     cp_async_commit();
-    cm_cur = cm_nxt;
-    cm_nxt = cm_nn;
+#pragma unroll
+    for (int q = 0; q < NSTAGE - 1; ++q) cm_q[q] = cm_q[q + 1];
+    cm_q[NSTAGE - 1] = cm_far;
 
     // bf16 snapshot of the state -> shared (operand of W S) and -> global h_c
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
-      acc_to_smem<4>(Sb + (rg * (DK / 4) + mt * 16) * S::LDB + cg * 32, S::LDB, S_[mt], lane);
+      acc_to_smem<NT>(Sb + (rg * (DK / 4) + mt * 16) * S::LDB + cg * CW, S::LDB, S_[mt], lane);
     __syncthreads();
     if (a.h != nullptr) {
       __nv_bfloat16* hg = reinterpret_cast<__nv_bfloat16*>(a.h) + ((int64_t)c * a.HV + hv) * DK * DV + v0;
@@ -115,16 +122,16 @@ __global__ void __launch_bounds__(128 * (BV / 32)) scan_fwd_kernel(const b200gdn
     }
 
     // v_new = U - W S   (rows rg*16.., columns cg*32..)
-    float acc[4][4];
-    zero_acc<4>(acc);
-    warp_mma<4, DK / 16, AMajor::Row, BMajor::KN>(acc, Wt + rg * 16 * S::LDK, S::LDK, Sb + cg * 32, S::LDB, lane);
+    float acc[NT][4];
+    zero_acc<NT>(acc);
+    warp_mma<NT, DK / 16, AMajor::Row, BMajor::KN>(acc, Wt + rg * 16 * S::LDK, S::LDK, Sb + cg * CW, S::LDB, lane);
     const float glast = gs[BT - 1];
     {
       const int r_lo = rg * 16 + g, r_hi = r_lo + 8;
       const float e_lo = exp2f(glast - gs[r_lo]), e_hi = exp2f(glast - gs[r_hi]);
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
-        const int col = cg * 32 + nt * 8 + 2 * t;
+      for (int nt = 0; nt < NT; ++nt) {
+        const int col = cg * CW + nt * 8 + 2 * t;
         float2 u_lo = make_float2(0.f, 0.f), u_hi = make_float2(0.f, 0.f);
         if (ubase != nullptr) {
           u_lo = unpack_bf16(*reinterpret_cast<const uint32_t*>(Ut + r_lo * S::LDB + col));
@@ -149,10 +156,10 @@ __global__ void __launch_bounds__(128 * (BV / 32)) scan_fwd_kernel(const b200gdn
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
+      for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) S_[mt][nt][e] *= dec;
-      warp_mma<4, BT / 16, AMajor::Trans, BMajor::KN>(S_[mt], Kt + rg * (DK / 4) + mt * 16, S::LDK, Vt + cg * 32, S::LDB,
+      warp_mma<NT, BT / 16, AMajor::Trans, BMajor::KN>(S_[mt], Kt + rg * (DK / 4) + mt * 16, S::LDK, Vt + cg * CW, S::LDB,
                                                       lane);
     }
   }
@@ -162,29 +169,29 @@ __global__ void __launch_bounds__(128 * (BV / 32)) scan_fwd_kernel(const b200gdn
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
+      for (int nt = 0; nt < NT; ++nt) {
         int r = rg * (DK / 4) + mt * 16 + g;
-        int col = v0 + cg * 32 + nt * 8 + 2 * t;
+        int col = v0 + cg * CW + nt * 8 + 2 * t;
         *reinterpret_cast<float2*>(&ht[(int64_t)r * DV + col]) = make_float2(S_[mt][nt][0], S_[mt][nt][1]);
         *reinterpret_cast<float2*>(&ht[(int64_t)(r + 8) * DV + col]) = make_float2(S_[mt][nt][2], S_[mt][nt][3]);
       }
   }
 }
 
-template <int DK, int DV, int BV>
+template <int DK, int DV, int BV, int NSTAGE, int CW>
 int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
-  using S = ScanFwdSmem<DK, BV>;
-  if (int e = ensure_smem(scan_fwd_kernel<DK, DV, BV>, S::bytes)) return e;
+  using S = ScanFwdSmem<DK, BV, NSTAGE>;
+  if (int e = ensure_smem(scan_fwd_kernel<DK, DV, BV, NSTAGE, CW>, S::bytes)) return e;
   dim3 grid(DV / BV, a.HV, a.n_seq);
-  scan_fwd_kernel<DK, DV, BV><<<grid, 128 * (BV / 32), S::bytes, st>>>(a);
+  scan_fwd_kernel<DK, DV, BV, NSTAGE, CW><<<grid, 128 * (BV / CW), S::bytes, st>>>(a);
   return check_launch("scan_fwd");
 }
 
 }  // namespace
 
 int launch_scan_fwd(const b200gdn_chunk_args& a, cudaStream_t st) {
-  if (a.K == 128 && a.V == 128) return launch<128, 128, 64>(a, st);
-  if (a.K == 64 && a.V == 64) return launch<64, 64, 32>(a, st);
+  if (a.K == 128 && a.V == 128) return launch<128, 128, 64, 2, 32>(a, st);
+  if (a.K == 64 && a.V == 64) return launch<64, 64, 32, 2, 32>(a, st);
   return set_error(B200GDN_ERR_UNSUPPORTED, "scan_fwd: K=%d V=%d not built (64/64 and 128/128 are)", a.K, a.V);
 }
 
