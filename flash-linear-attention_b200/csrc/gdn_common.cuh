@@ -143,6 +143,37 @@ __device__ __forceinline__ float2 unpack_bf16(uint32_t v) {
   return __bfloat1622float2(b);
 }
 
+// ---- the same fragments from tiles in the 128-byte-swizzled panel layout (what TMA writes) -----------
+// A tile of `rows` rows is a stack of 64-column panels (rows*128 bytes each); inside a panel row r
+// starts at r*128 and its 16-byte chunk c sits at position c ^ (r & 7).  Every ldmatrix lane fetches one
+// chunk, so the swizzle is applied per lane and the eight rows of a matrix hit distinct banks.
+__device__ __forceinline__ uint32_t swz_chunk_addr(uint32_t tile, int rows, int r, int col8) {
+  return tile + (col8 >> 6) * (rows * 128) + r * 128 + ((((col8 >> 3) & 7) ^ (r & 7)) << 4);
+}
+// `tile` is the shared-memory address (u32) of the tile; (m0, k0) etc. are element coordinates.
+__device__ __forceinline__ void load_a_swz(uint32_t (&a)[4], uint32_t tile, int rows, int m0, int k0, int lane) {
+  ldsm_x4(a, swz_chunk_addr(tile, rows, m0 + (lane & 15), k0 + ((lane >> 4) << 3)));
+}
+__device__ __forceinline__ void load_a_t_swz(uint32_t (&a)[4], uint32_t tile, int rows, int k0, int m0, int lane) {
+  ldsm_x4_t(a, swz_chunk_addr(tile, rows, k0 + (lane & 7) + ((lane >> 4) << 3), m0 + (((lane >> 3) & 1) << 3)));
+}
+__device__ __forceinline__ void load_b_nk_swz(uint32_t (&b)[4], uint32_t tile, int rows, int n0, int k0, int lane) {
+  ldsm_x4(b, swz_chunk_addr(tile, rows, n0 + (lane & 7) + ((lane >> 4) << 3), k0 + (((lane >> 3) & 1) << 3)));
+}
+__device__ __forceinline__ void load_b_kn_swz(uint32_t (&b)[4], uint32_t tile, int rows, int k0, int n0, int lane) {
+  ldsm_x4_t(b, swz_chunk_addr(tile, rows, k0 + (lane & 7) + (((lane >> 3) & 1) << 3), n0 + ((lane >> 4) << 3)));
+}
+// 4-byte access to element pair (r, col), col even
+__device__ __forceinline__ uint32_t swz_pair_addr(uint32_t tile, int rows, int r, int col) {
+  return swz_chunk_addr(tile, rows, r, col & ~7) + ((col & 7) << 1);
+}
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) { asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(addr), "r"(v)); }
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+  return v;
+}
+
 enum class AMajor { Row, Trans };
 enum class BMajor { NK, KN };
 
@@ -175,6 +206,47 @@ __device__ __forceinline__ void warp_mma(float (&acc)[NT][4], const __nv_bfloat1
       mma16816(acc[2 * np], a, b[0], b[1]);
       mma16816(acc[2 * np + 1], a, b[2], b[3]);
     }
+  }
+}
+
+// The same contraction on swizzled tiles.  (am0, ak0) / (bn0, bk0) are the element coordinates of the
+// operand blocks inside their tiles; the contraction runs over KS steps of 16 from ak0 / bk0.
+template <int NT, int KS, AMajor AM, BMajor BM, bool NEG_A = false>
+__device__ __forceinline__ void warp_mma_swz(float (&acc)[NT][4], uint32_t atile, int arows, int am0, int ak0, uint32_t btile,
+                                             int brows, int bn0, int bk0, int lane) {
+  static_assert(NT % 2 == 0, "n-tiles come in pairs");
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    uint32_t a[4];
+    if (AM == AMajor::Row)
+      load_a_swz(a, atile, arows, am0, ak0 + ks * 16, lane);
+    else
+      load_a_t_swz(a, atile, arows, ak0 + ks * 16, am0, lane);
+    if (NEG_A) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] ^= 0x80008000u;
+    }
+#pragma unroll
+    for (int np = 0; np < NT / 2; ++np) {
+      uint32_t b[4];
+      if (BM == BMajor::NK)
+        load_b_nk_swz(b, btile, brows, bn0 + np * 16, bk0 + ks * 16, lane);
+      else
+        load_b_kn_swz(b, btile, brows, bk0 + ks * 16, bn0 + np * 16, lane);
+      mma16816(acc[2 * np], a, b[0], b[1]);
+      mma16816(acc[2 * np + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+// Store a warp's 16 x (8*NT) accumulator as bf16 into a swizzled tile at element (m0, n0).
+template <int NT>
+__device__ __forceinline__ void acc_to_swz(uint32_t tile, int rows, int m0, int n0, const float (&acc)[NT][4], int lane) {
+  int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    sts32(swz_pair_addr(tile, rows, m0 + g, n0 + nt * 8 + 2 * t), pack_bf16(acc[nt][0], acc[nt][1]));
+    sts32(swz_pair_addr(tile, rows, m0 + g + 8, n0 + nt * 8 + 2 * t), pack_bf16(acc[nt][2], acc[nt][3]));
   }
 }
 
