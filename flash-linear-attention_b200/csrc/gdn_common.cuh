@@ -181,31 +181,43 @@ enum class BMajor { NK, KN };
 //  AMajor::Row   : As[m][k], pa -> (m0, 0)        AMajor::Trans : As[k][m], pa -> (0, m0)
 //  BMajor::NK    : Bs[n][k], pb -> (n0, 0)        BMajor::KN    : Bs[k][n], pb -> (0, n0)
 // NEG_A flips the sign of A (both bf16 halves) so that the product is subtracted.
+// The operand fetches are software-pipelined by hand: the ldmatrix of step i+1 is issued before the
+// MMAs of step i (the asm statements are volatile, so the compiler keeps this order), which takes the
+// shared-memory latency off the dependent chain of MMAs.
 template <int NT, int KS, AMajor AM, BMajor BM, bool NEG_A = false>
 __device__ __forceinline__ void warp_mma(float (&acc)[NT][4], const __nv_bfloat16* pa, int lda, const __nv_bfloat16* pb,
                                          int ldb, int lane) {
   static_assert(NT % 2 == 0, "n-tiles come in pairs");
-#pragma unroll
-  for (int ks = 0; ks < KS; ++ks) {
-    uint32_t a[4];
+  constexpr int NP = NT / 2, STEPS = KS * NP;
+  uint32_t a[2][4], b[2][4];
+  auto ld_a = [&](int ks, uint32_t (&dst)[4]) {
     if (AM == AMajor::Row)
-      load_a(a, pa + ks * 16, lda, lane);
+      load_a(dst, pa + ks * 16, lda, lane);
     else
-      load_a_t(a, pa + ks * 16 * lda, lda, lane);
+      load_a_t(dst, pa + ks * 16 * lda, lda, lane);
     if (NEG_A) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] ^= 0x80008000u;
+      for (int i = 0; i < 4; ++i) dst[i] ^= 0x80008000u;
     }
+  };
+  auto ld_b = [&](int ks, int np, uint32_t (&dst)[4]) {
+    if (BM == BMajor::NK)
+      load_b_nk(dst, pb + np * 16 * ldb + ks * 16, ldb, lane);
+    else
+      load_b_kn(dst, pb + ks * 16 * ldb + np * 16, ldb, lane);
+  };
+  ld_a(0, a[0]);
+  ld_b(0, 0, b[0]);
 #pragma unroll
-    for (int np = 0; np < NT / 2; ++np) {
-      uint32_t b[4];
-      if (BM == BMajor::NK)
-        load_b_nk(b, pb + np * 16 * ldb + ks * 16, ldb, lane);
-      else
-        load_b_kn(b, pb + ks * 16 * ldb + np * 16, ldb, lane);
-      mma16816(acc[2 * np], a, b[0], b[1]);
-      mma16816(acc[2 * np + 1], a, b[2], b[3]);
+  for (int st = 0; st < STEPS; ++st) {
+    const int ks = st / NP, np = st % NP;
+    if (st + 1 < STEPS) {
+      const int ks1 = (st + 1) / NP, np1 = (st + 1) % NP;
+      if (np1 == 0) ld_a(ks1, a[ks1 & 1]);
+      ld_b(ks1, np1, b[(st + 1) & 1]);
     }
+    mma16816(acc[2 * np], a[ks & 1], b[st & 1][0], b[st & 1][1]);
+    mma16816(acc[2 * np + 1], a[ks & 1], b[st & 1][2], b[st & 1][3]);
   }
 }
 
@@ -215,27 +227,36 @@ template <int NT, int KS, AMajor AM, BMajor BM, bool NEG_A = false>
 __device__ __forceinline__ void warp_mma_swz(float (&acc)[NT][4], uint32_t atile, int arows, int am0, int ak0, uint32_t btile,
                                              int brows, int bn0, int bk0, int lane) {
   static_assert(NT % 2 == 0, "n-tiles come in pairs");
-#pragma unroll
-  for (int ks = 0; ks < KS; ++ks) {
-    uint32_t a[4];
+  constexpr int NP = NT / 2, STEPS = KS * NP;
+  uint32_t a[2][4], b[2][4];
+  auto ld_a = [&](int ks, uint32_t (&dst)[4]) {
     if (AM == AMajor::Row)
-      load_a_swz(a, atile, arows, am0, ak0 + ks * 16, lane);
+      load_a_swz(dst, atile, arows, am0, ak0 + ks * 16, lane);
     else
-      load_a_t_swz(a, atile, arows, ak0 + ks * 16, am0, lane);
+      load_a_t_swz(dst, atile, arows, ak0 + ks * 16, am0, lane);
     if (NEG_A) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] ^= 0x80008000u;
+      for (int i = 0; i < 4; ++i) dst[i] ^= 0x80008000u;
     }
+  };
+  auto ld_b = [&](int ks, int np, uint32_t (&dst)[4]) {
+    if (BM == BMajor::NK)
+      load_b_nk_swz(dst, btile, brows, bn0 + np * 16, bk0 + ks * 16, lane);
+    else
+      load_b_kn_swz(dst, btile, brows, bk0 + ks * 16, bn0 + np * 16, lane);
+  };
+  ld_a(0, a[0]);
+  ld_b(0, 0, b[0]);
 #pragma unroll
-    for (int np = 0; np < NT / 2; ++np) {
-      uint32_t b[4];
-      if (BM == BMajor::NK)
-        load_b_nk_swz(b, btile, brows, bn0 + np * 16, bk0 + ks * 16, lane);
-      else
-        load_b_kn_swz(b, btile, brows, bk0 + ks * 16, bn0 + np * 16, lane);
-      mma16816(acc[2 * np], a, b[0], b[1]);
-      mma16816(acc[2 * np + 1], a, b[2], b[3]);
+  for (int st = 0; st < STEPS; ++st) {
+    const int ks = st / NP, np = st % NP;
+    if (st + 1 < STEPS) {
+      const int ks1 = (st + 1) / NP, np1 = (st + 1) % NP;
+      if (np1 == 0) ld_a(ks1, a[ks1 & 1]);
+      ld_b(ks1, np1, b[(st + 1) & 1]);
     }
+    mma16816(acc[2 * np], a[ks & 1], b[st & 1][0], b[st & 1][1]);
+    mma16816(acc[2 * np + 1], a[ks & 1], b[st & 1][2], b[st & 1][3]);
   }
 }
 
@@ -255,18 +276,21 @@ __device__ __forceinline__ void acc_to_swz(uint32_t tile, int rows, int m0, int 
 template <int NT, int KS, BMajor BM>
 __device__ __forceinline__ void warp_mma_ra(float (&acc)[NT][4], const uint32_t (&afrag)[KS][4],
                                             const __nv_bfloat16* pb, int ldb, int lane) {
+  constexpr int NP = NT / 2, STEPS = KS * NP;
+  uint32_t b[2][4];
+  auto ld_b = [&](int ks, int np, uint32_t (&dst)[4]) {
+    if (BM == BMajor::NK)
+      load_b_nk(dst, pb + np * 16 * ldb + ks * 16, ldb, lane);
+    else
+      load_b_kn(dst, pb + ks * 16 * ldb + np * 16, ldb, lane);
+  };
+  ld_b(0, 0, b[0]);
 #pragma unroll
-  for (int ks = 0; ks < KS; ++ks) {
-#pragma unroll
-    for (int np = 0; np < NT / 2; ++np) {
-      uint32_t b[4];
-      if (BM == BMajor::NK)
-        load_b_nk(b, pb + np * 16 * ldb + ks * 16, ldb, lane);
-      else
-        load_b_kn(b, pb + ks * 16 * ldb + np * 16, ldb, lane);
-      mma16816(acc[2 * np], afrag[ks], b[0], b[1]);
-      mma16816(acc[2 * np + 1], afrag[ks], b[2], b[3]);
-    }
+  for (int st = 0; st < STEPS; ++st) {
+    const int ks = st / NP, np = st % NP;
+    if (st + 1 < STEPS) ld_b((st + 1) / NP, (st + 1) % NP, b[(st + 1) & 1]);
+    mma16816(acc[2 * np], afrag[ks], b[st & 1][0], b[st & 1][1]);
+    mma16816(acc[2 * np + 1], afrag[ks], b[st & 1][2], b[st & 1][3]);
   }
 }
 

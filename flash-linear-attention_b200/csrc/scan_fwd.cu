@@ -1,34 +1,35 @@
-// Forward state scan: for every (sequence, value head) walk the chunks in order with the K x V state
-// resident on chip (fp32 accumulator fragments in registers):
+// Forward state scan: for every (sequence, value head) walk the chunks in order with the K x V fp32 state
+// resident in tensor memory (TMEM):
 //     h_c = S (bf16 snapshot, state at chunk start);  v_new = U - W S;
 //     S <- 2^gamma_last S + (K 2^(gamma_last - gamma))^T v_new.
 // Replaces chunk_gated_delta_rule_fwd_kernel_h_blockdim64 (fla/ops/common/chunk_delta_h.py:58-348).
 //
-// The recurrence is a chain of 64-row steps, so what matters is the latency of one step.  Global-memory
-// instructions issued by the compute warps used to dominate it, therefore data movement is taken off
-// those warps entirely:
-//   * a producer warp feeds a ring of NSTAGE stages with TMA (cp.async.bulk.tensor, 128-byte swizzle):
-//     W [64 x K], K [64 x K] and the U slice [64 x 64] of chunk c + NSTAGE - 1 are in flight while chunk
-//     c is processed; full/empty mbarriers hand the stages over;
-//   * eight compute warps (4 row groups x 2 column groups of one 64-column slice of the state) run the
-//     two dependent contractions with mma.sync from the swizzled tiles;
-//   * the bf16 state snapshot h_c and v_new leave through TMA stores from double-buffered shared tiles.
+// The recurrence is a chain of 64-row steps, so what matters is the latency of one step.  One CTA owns a
+// 64-column slice of one state and is specialised by warp:
+//   * producer warp: TMA (cp.async.bulk.tensor, 128-byte swizzle) fills a ring of NSTAGE stages with
+//     W [64 x K], K [64 x K] and the U slice [64 x 64] of the chunks ahead; full/empty mbarriers;
+//   * MMA warp (one thread): tcgen05.mma  V_acc = W S_bf16  (64 x 64 x K) and  S += K^T V~  (K x 64 x 64),
+//     operands straight from the swizzled tiles, accumulators in TMEM; it also issues the TMA stores of
+//     the state snapshot h_c and of v_new from double-buffered shared tiles;
+//   * eight epilogue warps: read S from TMEM, round it to bf16 into shared memory, write it back scaled
+//     by 2^gamma_last (tcgen05.st), and turn V_acc into v_new and the gated V~.
+// Per step the chain is  S -> bf16 -> MMA -> v_new -> MMA, with four mbarrier hand-offs.
 // A ragged last chunk is loaded as a full box (rows of the next sequence or zero fill); its extra rows
 // are masked where v_new is formed, and its v_new rows are written with plain predicated stores.
 //
 // The same kernel produces the transition matrix of a whole shard for context parallelism
 // (fla/ops/cp/chunk_delta_h.py:254-315): with u == NULL (zeros), h0 = identity and V := K the final
 // state is M = prod_c (2^gamma_last I - K~^T W).
-#include "gdn_common.cuh"
-#include "tc5.cuh"
+#include "tc5_tile.cuh"
 #include "tma.cuh"
 
 namespace gdn {
 namespace {
 
-constexpr int BV = 64;            // state columns per CTA
-constexpr int NCOMPUTE = 256;     // 8 compute warps
-constexpr int NTHREADS = NCOMPUTE + 32;
+constexpr int BV = 64;          // state columns per CTA
+constexpr int NEPI = 256;       // 8 epilogue warps
+constexpr int WARP_PROD = NEPI / 32, WARP_MMA = NEPI / 32 + 1;
+constexpr int NTHREADS = NEPI + 64;
 __device__ int g_scan_fwd_timeout = 0;
 
 template <int DK, int NSTAGE>
@@ -42,24 +43,29 @@ struct ScanFwdSmem {
   static constexpr size_t o_vt = o_vn + 2 * u_bytes;        // gated v_new slice
   static constexpr size_t o_gam = o_vt + u_bytes;           // NSTAGE x 64 floats
   static constexpr size_t o_bar = o_gam + NSTAGE * BT * 4;
-  static constexpr size_t bytes = o_bar + 2 * NSTAGE * 8 + 1024;  // + alignment slack
+  static constexpr size_t bytes = o_bar + (2 * NSTAGE + 4) * 8 + 16 + 1024;  // + alignment slack
 };
 
 struct ScanFwdMaps {
   CUtensorMap w, k, u, h, vn;
 };
 
-__device__ __forceinline__ void bar_compute(int id) { asm volatile("bar.sync %0, %1;\n" ::"r"(id), "n"(NCOMPUTE) : "memory"); }
+__device__ __forceinline__ void bar_epi() { asm volatile("bar.sync 1, %0;\n" ::"n"(NEPI) : "memory"); }
 
 template <int DK, int DV, int NSTAGE>
 __global__ void __launch_bounds__(NTHREADS) scan_fwd_kernel(const b200gdn_chunk_args a, const __grid_constant__ ScanFwdMaps maps) {
   using S = ScanFwdSmem<DK, NSTAGE>;
-  constexpr int MT = DK / 64;   // 16-row m-tiles of the state per warp
+  constexpr int NH = DK / 64;   // 16-row halves of the state per epilogue warp
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* gam_all = reinterpret_cast<float*>(smem + S::o_gam);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::o_bar);
   uint64_t* empty = full + NSTAGE;
+  uint64_t* s_ready = empty + NSTAGE;   // S accumulated (MMA 2 done)
+  uint64_t* sb_ready = s_ready + 1;     // bf16 snapshot in shared memory, scaled S back in TMEM
+  uint64_t* v_ready = sb_ready + 1;     // V_acc done (MMA 1)
+  uint64_t* vt_ready = v_ready + 1;     // v_new / V~ tiles written
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(vt_ready + 1);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int v0 = blockIdx.x * BV, hv = blockIdx.y, n = blockIdx.z;
@@ -67,32 +73,37 @@ __global__ void __launch_bounds__(NTHREADS) scan_fwd_kernel(const b200gdn_chunk_
   const int c_first = a.seq_meta[2 * n], nc = a.seq_meta[2 * n + 1];
   const bool has_u = a.u != nullptr;
 
-  if (tid == 0) {
+  if (warp == 0) tc5::tmem_alloc(tmem_slot, 128);
+  if (tid == 32) {
     for (int s = 0; s < NSTAGE; ++s) {
-      tc5::mbar_init(&full[s], 2);               // producer's expect_tx arrive + its gamma arrive
-      tc5::mbar_init(&empty[s], NCOMPUTE / 32);  // one arrive per compute warp
+      tc5::mbar_init(&full[s], 2);    // producer's expect_tx arrive + its gamma arrive
+      tc5::mbar_init(&empty[s], 1);   // tcgen05.commit of the step's second MMA
     }
+    tc5::mbar_init(s_ready, 1);
+    tc5::mbar_init(sb_ready, NEPI / 32);
+    tc5::mbar_init(v_ready, 1);
+    tc5::mbar_init(vt_ready, NEPI / 32);
     tc5::fence_mbar_init();
   }
+  tc5::fence_before_sync();
   __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tm = *tmem_slot;
+  const uint32_t TM_S = tm, TM_V = tm + 64;
+  bool failed = false;
 
-  if (warp == NCOMPUTE / 32) {
-    // ================= producer warp =================
+  if (warp == WARP_PROD) {
+    // ================= producer warp: TMA loads =================
     if (lane == 0) {
       tma::prefetch_map(&maps.w);
       tma::prefetch_map(&maps.k);
       if (has_u) tma::prefetch_map(&maps.u);
     }
     const uint32_t tx_bytes = (uint32_t)(2 * S::w_bytes + (has_u ? S::u_bytes : 0));
-    for (int ic = 0; ic < nc; ++ic) {
+    for (int ic = 0; ic < nc && !failed; ++ic) {
       const int s = ic % NSTAGE;
       const ChunkMeta cm = load_chunk_meta(a.chunk_meta, c_first + ic);
-      if (ic >= NSTAGE) {
-        if (!tc5::mbar_wait(&empty[s], ((ic / NSTAGE) - 1) & 1)) {
-          if (lane == 0) atomicExch(&g_scan_fwd_timeout, 1);
-          break;
-        }
-      }
+      if (ic >= NSTAGE && !tc5::mbar_wait(&empty[s], ((ic / NSTAGE) - 1) & 1)) { failed = true; break; }
       unsigned char* base = smem + (size_t)s * S::stage_bytes;
       if (lane == 0) {
         tc5::mbar_expect_tx(&full[s], tx_bytes);
@@ -114,94 +125,141 @@ __global__ void __launch_bounds__(NTHREADS) scan_fwd_kernel(const b200gdn_chunk_
       __syncwarp();
       if (lane == 0) tc5::mbar_arrive(&full[s]);
     }
-    return;
-  }
-
-  // ================= compute warps =================
-  const int rg = warp & 3, cg = warp >> 2;
-  const int g = lane >> 2, t = lane & 3;
-  const uint32_t sb_base = smem_u32(smem + S::o_sb);
-  const uint32_t vn_base = smem_u32(smem + S::o_vn);
-  const uint32_t vt_tile = smem_u32(smem + S::o_vt);
-
-  // state fragments: rows rg*(DK/4) + mt*16 + {g, g+8}, columns cg*32 + nt*8 + 2t + {0,1}
-  float S_[MT][4][4];
-  {
-    const float* h0 = a.h0 ? a.h0 + ((int64_t)n * a.HV + hv) * DK * DV : nullptr;
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          int r = rg * (DK / 4) + mt * 16 + g + ((e >> 1) << 3);
-          int col = v0 + cg * 32 + nt * 8 + 2 * t + (e & 1);
-          S_[mt][nt][e] = h0 ? h0[(int64_t)r * DV + col] : 0.f;
+  } else if (warp == WARP_MMA) {
+    // ================= MMA warp: one thread issues the contractions and the TMA stores =================
+    if (lane == 0) {
+      const uint32_t vt_addr = tc5::smem_addr(smem + S::o_vt);
+      for (int ic = 0; ic < nc; ++ic) {
+        const int c = c_first + ic, s = ic % NSTAGE, buf = ic & 1;
+        const ChunkMeta cm = load_chunk_meta(a.chunk_meta, c);
+        const uint32_t w_addr = tc5::smem_addr(smem + (size_t)s * S::stage_bytes);
+        const uint32_t k_addr = w_addr + (uint32_t)S::w_bytes;
+        unsigned char* sb_ptr = smem + S::o_sb + buf * S::sb_bytes;
+        if (!tc5::mbar_wait(&full[s], (ic / NSTAGE) & 1) || !tc5::mbar_wait(sb_ready, ic & 1)) { failed = true; break; }
+        tc5::fence_after_sync();
+        // V_acc = W S_bf16
+        issue_mma(TM_V, Operand{w_addr, BT, 0}, Operand{tc5::smem_addr(sb_ptr), DK, 1}, 64, BV, DK / 16, 0);
+        tc5::mma_commit(v_ready);
+        if (a.h != nullptr) {
+          tma::store_2d(&maps.h, v0, (c * a.HV + hv) * DK, sb_ptr);
+          tma::store_commit();
         }
-  }
+        if (!tc5::mbar_wait(vt_ready, ic & 1)) { failed = true; break; }
+        // every store older than this step's h_c has released its shared tile (they are re-written next step)
+        if (a.h != nullptr) tma::store_wait_read<1>(); else tma::store_wait_read<0>();
+        tc5::fence_after_sync();
+        // S += K^T V~
+        issue_mma(TM_S, Operand{k_addr, BT, 1}, Operand{vt_addr, BT, 1}, DK, BV, BT / 16, 1);
+        tc5::mma_commit(s_ready);
+        tc5::mma_commit(&empty[s]);
+        if (a.v_new != nullptr && cm.len == BT) {
+          tma::store_2d(&maps.vn, hv * DV + v0, cm.row, smem + S::o_vn + buf * S::u_bytes);
+          tma::store_commit();
+        }
+      }
+      tma::store_wait_all<0>();   // shared tiles must outlive the stores that read them
+    }
+  } else {
+    // ================= epilogue warps =================
+    const int q = warp & 3, hc = warp >> 2;
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t sb_base = smem_u32(smem + S::o_sb);
+    const uint32_t vn_base = smem_u32(smem + S::o_vn);
+    const uint32_t vt_tile = smem_u32(smem + S::o_vt);
+    const int srow0 = (DK / 4) * q;           // first state row of this warp
+    const uint32_t s_lane = (uint32_t)(32 * q) << 16;
 
-  bool failed = false;
-  for (int ic = 0; ic < nc; ++ic) {
-    const int c = c_first + ic, s = ic % NSTAGE, buf = ic & 1;
-    const ChunkMeta cm = load_chunk_meta(a.chunk_meta, c);   // consumed late in the step: latency is hidden
-    const uint32_t w_tile = smem_u32(smem + (size_t)s * S::stage_bytes);
-    const uint32_t k_tile = w_tile + (uint32_t)S::w_bytes;
-    const uint32_t u_tile = w_tile + 2 * (uint32_t)S::w_bytes;
-    const float* gs = gam_all + s * BT;
-    const uint32_t sb_tile = sb_base + buf * (uint32_t)S::sb_bytes;
-    const uint32_t vn_tile = vn_base + buf * (uint32_t)S::u_bytes;
-
-    // bf16 snapshot of the state -> shared (operand of W S, and the source of the h_c store).
-    // The buffer was last read two steps ago (contraction) and by the store that thread 0 has waited for.
+    // state block of this thread: rows srow0 + 16*half + {g, g+8}, columns 32*hc + 8*i + 2t + {0,1}
+    float Sr[NH][16];
+    {
+      const float* h0 = a.h0 ? a.h0 + ((int64_t)n * a.HV + hv) * DK * DV : nullptr;
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) acc_to_swz<4>(sb_tile, DK, rg * (DK / 4) + mt * 16, cg * 32, S_[mt], lane);
-    tc5::fence_async_smem();
-    if (!tc5::mbar_wait(&full[s], (ic / NSTAGE) & 1)) failed = true;   // tiles of this chunk have landed
-    bar_compute(1);
-    if (tid == 0 && a.h != nullptr) {
-      tma::store_2d(&maps.h, v0, (c * a.HV + hv) * DK, smem + S::o_sb + buf * S::sb_bytes);
-      tma::store_commit();
+      for (int hf = 0; hf < NH; ++hf)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int r = srow0 + 16 * hf + g + ((e >> 1) << 3);
+            const int col = v0 + 32 * hc + 8 * i + 2 * t + (e & 1);
+            Sr[hf][4 * i + e] = h0 ? h0[(int64_t)r * DV + col] : 0.f;
+          }
     }
 
-    // v_new = U - W S   (rows rg*16.., columns cg*32..)
-    float acc[4][4];
-    zero_acc<4>(acc);
-    warp_mma_swz<4, DK / 16, AMajor::Row, BMajor::KN>(acc, w_tile, BT, rg * 16, 0, sb_tile, DK, cg * 32, 0, lane);
-    const float glast = gs[BT - 1];
-    {
-      const int r_lo = rg * 16 + g, r_hi = r_lo + 8;
+    for (int ic = 0; ic < nc; ++ic) {
+      const int c = c_first + ic, s = ic % NSTAGE, buf = ic & 1;
+      const ChunkMeta cm = load_chunk_meta(a.chunk_meta, c);   // consumed late in the step
+      const uint32_t u_tile = smem_u32(smem + (size_t)s * S::stage_bytes + 2 * S::w_bytes);
+      const float* gs = gam_all + s * BT;
+      const uint32_t sb_tile = sb_base + buf * (uint32_t)S::sb_bytes;
+      const uint32_t vn_tile = vn_base + buf * (uint32_t)S::u_bytes;
+
+      if (ic > 0) {
+        if (!tc5::mbar_wait(s_ready, (ic - 1) & 1)) { failed = true; break; }
+        tc5::fence_after_sync();
+#pragma unroll
+        for (int hf = 0; hf < NH; ++hf) tc5::tmem_ld_16x256b_x4(TM_S + s_lane + ((uint32_t)(16 * hf) << 16) + 32 * hc, Sr[hf]);
+        tc5::tmem_ld_wait();
+      }
+      // bf16 snapshot (operand of W S and source of the h_c store) ...
+#pragma unroll
+      for (int hf = 0; hf < NH; ++hf)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int col = 32 * hc + 8 * i + 2 * t, r = srow0 + 16 * hf + g;
+          sts32(swz_pair_addr(sb_tile, DK, r, col), pack_bf16(Sr[hf][4 * i], Sr[hf][4 * i + 1]));
+          sts32(swz_pair_addr(sb_tile, DK, r + 8, col), pack_bf16(Sr[hf][4 * i + 2], Sr[hf][4 * i + 3]));
+        }
+      // ... and the decayed state back to TMEM, where the second contraction accumulates onto it
+      if (!tc5::mbar_wait(&full[s], (ic / NSTAGE) & 1)) { failed = true; break; }
+      const float glast = gs[BT - 1];
+      const float dec = exp2f(glast);
+#pragma unroll
+      for (int hf = 0; hf < NH; ++hf) {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) Sr[hf][e] *= dec;
+        tc5::tmem_st_16x256b_x4(TM_S + s_lane + ((uint32_t)(16 * hf) << 16) + 32 * hc, Sr[hf]);
+      }
+      tc5::tmem_st_wait();
+      tc5::fence_async_smem();
+      tc5::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive(sb_ready);
+
+      // v_new = U - V_acc  (rows 16q + {g, g+8}, columns 32*hc ..)
+      const int r_lo = 16 * q + g, r_hi = r_lo + 8;
+      float2 u_lo[4], u_hi[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int col = 32 * hc + 8 * i + 2 * t;
+        u_lo[i] = has_u ? unpack_bf16(lds32(swz_pair_addr(u_tile, BT, r_lo, col))) : make_float2(0.f, 0.f);
+        u_hi[i] = has_u ? unpack_bf16(lds32(swz_pair_addr(u_tile, BT, r_hi, col))) : make_float2(0.f, 0.f);
+      }
       const float e_lo = r_lo < cm.len ? exp2f(glast - gs[r_lo]) : 0.f;   // rows past the chunk's end contribute nothing
       const float e_hi = r_hi < cm.len ? exp2f(glast - gs[r_hi]) : 0.f;
+      if (!tc5::mbar_wait(v_ready, ic & 1)) { failed = true; break; }
+      tc5::fence_after_sync();
+      float acc[16];
+      tc5::tmem_ld_16x256b_x4(TM_V + s_lane + 32 * hc, acc);
+      tc5::tmem_ld_wait();
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
-        const int col = cg * 32 + nt * 8 + 2 * t;
-        float2 u_lo = make_float2(0.f, 0.f), u_hi = make_float2(0.f, 0.f);
-        if (has_u) {
-          u_lo = unpack_bf16(lds32(swz_pair_addr(u_tile, BT, r_lo, col)));
-          u_hi = unpack_bf16(lds32(swz_pair_addr(u_tile, BT, r_hi, col)));
-        }
-        const float v00 = u_lo.x - acc[nt][0], v01 = u_lo.y - acc[nt][1];
-        const float v10 = u_hi.x - acc[nt][2], v11 = u_hi.y - acc[nt][3];
+      for (int i = 0; i < 4; ++i) {
+        const int col = 32 * hc + 8 * i + 2 * t;
+        const float v00 = u_lo[i].x - acc[4 * i], v01 = u_lo[i].y - acc[4 * i + 1];
+        const float v10 = u_hi[i].x - acc[4 * i + 2], v11 = u_hi[i].y - acc[4 * i + 3];
         sts32(swz_pair_addr(vn_tile, BT, r_lo, col), pack_bf16(v00, v01));
         sts32(swz_pair_addr(vn_tile, BT, r_hi, col), pack_bf16(v10, v11));
         sts32(swz_pair_addr(vt_tile, BT, r_lo, col), pack_bf16(v00 * e_lo, v01 * e_lo));
         sts32(swz_pair_addr(vt_tile, BT, r_hi, col), pack_bf16(v10 * e_hi, v11 * e_hi));
       }
-    }
-    tc5::fence_async_smem();
-    if (tid == 0) {   // every store older than this step's h_c has released its shared tile
-      if (a.h != nullptr) tma::store_wait_read<1>(); else tma::store_wait_read<0>();
-    }
-    bar_compute(2);
-    if (a.v_new != nullptr) {
-      if (cm.len == BT) {
-        if (tid == 0) {
-          tma::store_2d(&maps.vn, hv * DV + v0, cm.row, smem + S::o_vn + buf * S::u_bytes);
-          tma::store_commit();
-        }
-      } else {
+      tc5::fence_async_smem();
+      tc5::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive(vt_ready);
+
+      if (a.v_new != nullptr && cm.len < BT) {   // ragged chunk: predicated stores of the valid rows
+        bar_epi();
         __nv_bfloat16* vg = reinterpret_cast<__nv_bfloat16*>(a.v_new) + ((int64_t)cm.row * a.HV + hv) * DV + v0;
-        for (int idx = tid; idx < BT * 8; idx += NCOMPUTE) {
+        for (int idx = tid; idx < BT * 8; idx += NEPI) {
           const int r = idx >> 3, ch = idx & 7;
           if (r < cm.len) {
             uint4 val;
@@ -213,36 +271,33 @@ __global__ void __launch_bounds__(NTHREADS) scan_fwd_kernel(const b200gdn_chunk_
       }
     }
 
-    // S <- 2^gamma_last S + K^T v~     (rows rg*(DK/4) + mt*16.., columns cg*32..)
-    const float dec = exp2f(glast);
+    if (!failed && a.ht != nullptr) {
+      if (nc > 0) {
+        if (tc5::mbar_wait(s_ready, (nc - 1) & 1)) {
+          tc5::fence_after_sync();
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) S_[mt][nt][e] *= dec;
-      warp_mma_swz<4, BT / 16, AMajor::Trans, BMajor::KN>(S_[mt], k_tile, BT, rg * (DK / 4) + mt * 16, 0, vt_tile, BT, cg * 32,
-                                                          0, lane);
-    }
-    __syncwarp();
-    if (lane == 0) tc5::mbar_arrive(&empty[s]);   // this warp is done with stage s
-    if (failed) break;
-  }
-  if (failed && lane == 0) atomicExch(&g_scan_fwd_timeout, 1);
-
-  if (a.ht != nullptr) {
-    float* ht = a.ht + ((int64_t)n * a.HV + hv) * DK * DV;
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
-        int r = rg * (DK / 4) + mt * 16 + g;
-        int col = v0 + cg * 32 + nt * 8 + 2 * t;
-        *reinterpret_cast<float2*>(&ht[(int64_t)r * DV + col]) = make_float2(S_[mt][nt][0], S_[mt][nt][1]);
-        *reinterpret_cast<float2*>(&ht[(int64_t)(r + 8) * DV + col]) = make_float2(S_[mt][nt][2], S_[mt][nt][3]);
+          for (int hf = 0; hf < NH; ++hf) tc5::tmem_ld_16x256b_x4(TM_S + s_lane + ((uint32_t)(16 * hf) << 16) + 32 * hc, Sr[hf]);
+          tc5::tmem_ld_wait();
+        } else {
+          failed = true;
+        }
       }
+      float* ht = a.ht + ((int64_t)n * a.HV + hv) * DK * DV;
+#pragma unroll
+      for (int hf = 0; hf < NH; ++hf)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int r = srow0 + 16 * hf + g, col = v0 + 32 * hc + 8 * i + 2 * t;
+          *reinterpret_cast<float2*>(&ht[(int64_t)r * DV + col]) = make_float2(Sr[hf][4 * i], Sr[hf][4 * i + 1]);
+          *reinterpret_cast<float2*>(&ht[(int64_t)(r + 8) * DV + col]) = make_float2(Sr[hf][4 * i + 2], Sr[hf][4 * i + 3]);
+        }
+    }
   }
-  if (tid == 0) tma::store_wait_all<0>();   // shared tiles must outlive the stores that read them
+
+  if (failed && lane == 0) atomicExch(&g_scan_fwd_timeout, 1);
+  tc5::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc5::tmem_dealloc(tm, 128);
 }
 
 template <int DK, int DV, int NSTAGE>
