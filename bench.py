@@ -145,7 +145,7 @@ def time_stages(batch, steps):
     rows = B * T
     bf = dict(dtype=torch.bfloat16, device=dev)
     f32 = dict(dtype=torch.float32, device=dev)
-    buf = dict(o=torch.empty(rows, HV, V, **bf), ht=torch.empty(n_seq, HV, K, V, **f32), gamma=torch.empty(rows, HV, **f32),
+    buf = dict(o=torch.empty(rows, HV, V, **bf), ht=torch.empty(n_seq, HV, K, V, **f32), gamma=torch.empty(n_chunks, HV, 64, **f32),
                A=torch.empty(rows, HV, 64, **bf), w=torch.empty(rows, HV, K, **bf), u=torch.empty(rows, HV, V, **bf),
                h=torch.empty(n_chunks, HV, K, V, **bf), v_new=torch.empty(rows, HV, V, **bf),
                dq=torch.empty(rows, H, K, **bf), dk=torch.empty(rows, H, K, **bf), dv=torch.empty(rows, HV, V, **bf),

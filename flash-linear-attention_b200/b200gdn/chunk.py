@@ -71,7 +71,7 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             f32 = dict(dtype=torch.float32, device=dev)
             o = torch.empty(B, T, HV, V, **bf16)
             ht = torch.empty(n_seq, HV, K, V, **f32) if output_final_state else None
-            gamma = torch.empty(rows, HV, **f32)
+            gamma = torch.empty(n_chunks, HV, 64, **f32)
             A = torch.empty(rows, HV, 64, **bf16)
             w = torch.empty(rows, HV, K, **bf16)
             u = torch.empty(rows, HV, V, **bf16)

@@ -176,7 +176,7 @@ class ChunkGatedDeltaRuleCPFunction(torch.autograd.Function):
             bf16 = dict(dtype=torch.bfloat16, device=dev)
             f32 = dict(dtype=torch.float32, device=dev)
             o = torch.empty(B, T, HV, V, **bf16)
-            gamma = torch.empty(rows, HV, **f32)
+            gamma = torch.empty(n_chunks, HV, 64, **f32)
             A = torch.empty(rows, HV, 64, **bf16)
             w = torch.empty(rows, HV, K, **bf16)
             u = torch.empty(rows, HV, V, **bf16)

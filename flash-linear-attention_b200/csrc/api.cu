@@ -136,7 +136,7 @@ int b200gdn_affine_apply(const b200gdn_affine_args* a, void* stream) {
 int64_t b200gdn_saved_bytes(int32_t rows, int32_t H, int32_t HV, int32_t K, int32_t V, int32_t n_chunks) {
   (void)H;
   int64_t r = rows, hv = HV;
-  return r * hv * 4                      /* gamma */
+  return (int64_t)n_chunks * hv * 64 * 4  /* gamma */
          + r * hv * 64 * 2               /* A */
          + r * hv * K * 2                /* w */
          + r * hv * V * 2 * 2            /* u, v_new */

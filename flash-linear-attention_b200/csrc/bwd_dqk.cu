@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(NTHREADS) bwd_dqk_kernel(const b200gdn_chunk_a
     load_tile_swz<DK, 64, NTHREADS>(Hp, hg, DV, DK, tid);
     load_tile_swz<DK, 64, NTHREADS>(dHp, dhg, DV, DK, tid);
     cp_async_commit();
-    load_gamma(gs, a.gamma, cm.row, cm.len, a.HV, hv, tid);
+    load_gamma(gs, a.gamma, c, a.HV, hv, tid);
     cp_async_wait<0>();
     tc5::fence_async_smem();
     __syncthreads();

@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(NTHREADS) bwd_wy_kernel(const b200gdn_chunk_ar
     load_tile_swz<DK, DV, NTHREADS>(Hs, reinterpret_cast<const __nv_bfloat16*>(a.h) + ((int64_t)c * a.HV + hv) * DK * DV, DV, DK,
                                     tid);
     cp_async_commit();
-    load_gamma(gs, a.gamma, cm.row, cm.len, a.HV, hv, tid);
+    load_gamma(gs, a.gamma, c, a.HV, hv, tid);
     if (tid < BT) {
       const bool ok = tid < cm.len;
       bet[tid] = ok ? a.beta[(row0 + tid) * a.HV + hv] : 0.f;

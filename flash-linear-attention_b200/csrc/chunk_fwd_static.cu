@@ -74,7 +74,7 @@ extern "C" int b200gdn_chunk_fwd_static(const b200gdn_chunk_args* a, void* strea
 
   // carve the array: gamma | A | w | u | v_new | h, each region 256-byte aligned
   const size_t rh = (size_t)a->rows * a->HV;
-  const size_t sz_gamma = align256(rh * sizeof(float));
+  const size_t sz_gamma = align256((size_t)a->n_chunks * a->HV * B200GDN_CHUNK * sizeof(float));
   const size_t sz_A = align256(rh * B200GDN_CHUNK * 2);
   const size_t sz_w = align256(rh * a->K * 2);
   const size_t sz_u = align256(rh * a->V * 2);

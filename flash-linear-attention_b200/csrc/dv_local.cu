@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(NTHREADS) dv_local_kernel(const b200gdn_chunk_
   load_tile_async<DV, NTHREADS>(Ds, reinterpret_cast<const __nv_bfloat16*>(a.d_o) + (row0 * a.HV + hv) * DV,
                                 (int64_t)a.HV * DV, cm.len, tid);
   cp_async_commit();
-  load_gamma(gs, a.gamma, cm.row, cm.len, a.HV, hv, tid);
+  load_gamma(gs, a.gamma, c, a.HV, hv, tid);
   cp_async_wait<0>();
   __syncthreads();
 

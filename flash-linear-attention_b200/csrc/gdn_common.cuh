@@ -349,21 +349,18 @@ __device__ __forceinline__ void row_dot(float& r_lo, float& r_hi, const float (&
   r_hi = hi;
 }
 
-// gamma of a chunk into shared memory; rows past the valid length repeat the last valid value so
-// that 2^(gamma_last - gamma_i) is 1 there.
-__device__ __forceinline__ void load_gamma(float* gs, const float* gamma, int row0, int len, int HV, int hv, int tid) {
-  if (tid < BT) {
-    int r = tid < len ? tid : len - 1;
-    gs[tid] = gamma[(int64_t)(row0 + r) * HV + hv];
-  }
+// gamma is stored per chunk, [n_chunks][HV][64] fp32, entries past the chunk's valid length repeating the
+// last valid value (so 2^(gamma_last - gamma_i) is 1 there): a chunk's 64 values are 256 contiguous,
+// 256-byte aligned bytes that one bulk copy or one coalesced load brings in.
+__device__ __forceinline__ const float* gamma_ptr(const float* gamma, int c, int HV, int hv) {
+  return gamma + ((int64_t)c * HV + hv) * BT;
 }
-
+__device__ __forceinline__ void load_gamma(float* gs, const float* gamma, int c, int HV, int hv, int tid) {
+  if (tid < BT) gs[tid] = gamma_ptr(gamma, c, HV, hv)[tid];
+}
 // Same through the async-copy path, so that the loading threads do not stall on the global latency.
-__device__ __forceinline__ void load_gamma_async(float* gs, const float* gamma, int row0, int len, int HV, int hv, int tid) {
-  if (tid < BT) {
-    int r = tid < len ? tid : len - 1;
-    cp_async4(gs + tid, gamma + (int64_t)(row0 + r) * HV + hv);
-  }
+__device__ __forceinline__ void load_gamma_async(float* gs, const float* gamma, int c, int HV, int hv, int tid) {
+  if (tid < BT) cp_async4(gs + tid, gamma_ptr(gamma, c, HV, hv) + tid);
 }
 
 }  // namespace gdn

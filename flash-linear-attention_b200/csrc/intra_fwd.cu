@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(NTHREADS) intra_fwd_kernel(const b200gdn_chunk
     float gm = s * 1.4426950216f;
     gam[tid] = gm;
     bge[tid] = bet[tid] * exp2f(gm);
-    if (tid < cm.len) a.gamma[(row0 + tid) * a.HV + hv] = gm;
+    a.gamma[((int64_t)c * a.HV + hv) * BT + tid] = gm;   // padded rows carry the last valid value (their g is 0)
   }
   cp_async_wait<0>();
   __syncthreads();

@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(NTHREADS) out_fwd_kernel(const b200gdn_chunk_a
   load_rows_async<DK, DV, NTHREADS>(Hs, reinterpret_cast<const __nv_bfloat16*>(a.h) + ((int64_t)c * a.HV + hv) * DK * DV,
                                     DV, tid);
   cp_async_commit();
-  load_gamma(gs, a.gamma, cm.row, cm.len, a.HV, hv, tid);
+  load_gamma(gs, a.gamma, c, a.HV, hv, tid);
   cp_async_wait<0>();
   __syncthreads();
 

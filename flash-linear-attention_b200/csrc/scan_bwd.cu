@@ -45,7 +45,7 @@ __global__ void __launch_bounds__(128 * (BV / 32)) scan_bwd_kernel(const b200gdn
   const __nv_bfloat16* dobase = reinterpret_cast<const __nv_bfloat16*>(a.d_o);
   __nv_bfloat16* dv2base = reinterpret_cast<__nv_bfloat16*>(a.dv2);
 
-  auto issue_loads = [&](const ChunkMeta& cm, int s) {
+  auto issue_loads = [&](const ChunkMeta& cm, int c, int s) {
     unsigned char* base = smem + (size_t)s * S::stage_bytes;
     __nv_bfloat16* Qt = reinterpret_cast<__nv_bfloat16*>(base);
     __nv_bfloat16* Kt = reinterpret_cast<__nv_bfloat16*>(base + S::t_bytes);
@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(128 * (BV / 32)) scan_bwd_kernel(const b200gdn
     if (dobase != nullptr)
       load_tile_async<BV, NTHREADS>(Dt, dobase + ((int64_t)cm.row * a.HV + hv) * DV + v0, (int64_t)a.HV * DV, cm.len, tid);
     load_tile_async<BV, NTHREADS>(Lt, dv2base + ((int64_t)cm.row * a.HV + hv) * DV + v0, (int64_t)a.HV * DV, cm.len, tid);
-    load_gamma_async(gs, a.gamma, cm.row, cm.len, a.HV, hv, tid);
+    load_gamma_async(gs, a.gamma, c, a.HV, hv, tid);
   };
 
   float S_[MT][4][4];
@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(128 * (BV / 32)) scan_bwd_kernel(const b200gdn
   const int c_last = c_first + nc - 1;
   ChunkMeta cm_cur = load_chunk_meta(a.chunk_meta, nc > 0 ? c_last : c_first);
   ChunkMeta cm_nxt = load_chunk_meta(a.chunk_meta, nc > 1 ? c_last - 1 : c_first);
-  if (nc > 0) issue_loads(cm_cur, 0);
+  if (nc > 0) issue_loads(cm_cur, c_last, 0);
   cp_async_commit();
 
   for (int ic = 0; ic < nc; ++ic) {
@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(128 * (BV / 32)) scan_bwd_kernel(const b200gdn
 
     cp_async_wait<0>();
     __syncthreads();
-    if (ic + 1 < nc) issue_loads(cm_nxt, s ^ 1);
+    if (ic + 1 < nc) issue_loads(cm_nxt, c - 1, s ^ 1);
     cp_async_commit();
     cm_cur = cm_nxt;
     cm_nxt = cm_nn;

@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(NTHREADS) scan_fwd_kernel(const b200gdn_chunk_
   if (warp == 0) tc5::tmem_alloc(tmem_slot, 128);
   if (tid == 32) {
     for (int s = 0; s < NSTAGE; ++s) {
-      tc5::mbar_init(&full[s], 2);    // producer's expect_tx arrive + its gamma arrive
+      tc5::mbar_init(&full[s], 1);    // producer's expect_tx arrive; the copies complete the transaction count
       tc5::mbar_init(&empty[s], 1);   // tcgen05.commit of the step's second MMA
     }
     tc5::mbar_init(s_ready, 1);
@@ -99,57 +99,52 @@ __global__ void __launch_bounds__(NTHREADS) scan_fwd_kernel(const b200gdn_chunk_
       tma::prefetch_map(&maps.k);
       if (has_u) tma::prefetch_map(&maps.u);
     }
-    const uint32_t tx_bytes = (uint32_t)(2 * S::w_bytes + (has_u ? S::u_bytes : 0));
-    for (int ic = 0; ic < nc && !failed; ++ic) {
-      const int s = ic % NSTAGE;
-      const ChunkMeta cm = load_chunk_meta(a.chunk_meta, c_first + ic);
-      if (ic >= NSTAGE && !tc5::mbar_wait(&empty[s], ((ic / NSTAGE) - 1) & 1)) { failed = true; break; }
-      unsigned char* base = smem + (size_t)s * S::stage_bytes;
-      if (lane == 0) {
+    const uint32_t tx_bytes = (uint32_t)(2 * S::w_bytes + (has_u ? S::u_bytes : 0) + BT * 4);
+    if (lane == 0) {
+      int row_next = nc > 0 ? load_chunk_meta(a.chunk_meta, c_first).row : 0;
+      for (int ic = 0; ic < nc; ++ic) {
+        const int s = ic % NSTAGE;
+        const int row = row_next;
+        if (ic + 1 < nc) row_next = load_chunk_meta(a.chunk_meta, c_first + ic + 1).row;   // one step ahead of its use
+        if (ic >= NSTAGE && !tc5::mbar_wait(&empty[s], ((ic / NSTAGE) - 1) & 1)) { failed = true; break; }
+        unsigned char* base = smem + (size_t)s * S::stage_bytes;
         tc5::mbar_expect_tx(&full[s], tx_bytes);
-#pragma unroll
-        for (int p = 0; p < DK / 64; ++p) {
-          tma::load_2d(base + p * (BT * 128), &maps.w, hv * DK + p * 64, cm.row, &full[s]);
-          tma::load_2d(base + S::w_bytes + p * (BT * 128), &maps.k, hq * DK + p * 64, cm.row, &full[s]);
-        }
-        if (has_u) tma::load_2d(base + 2 * S::w_bytes, &maps.u, hv * DV + v0, cm.row, &full[s]);
+        tma::load_3d(base, &maps.w, row, (hv * DK) / 64, &full[s]);                 // W  [64 x K], all panels
+        tma::load_3d(base + S::w_bytes, &maps.k, row, (hq * DK) / 64, &full[s]);    // K  [64 x K]
+        if (has_u) tma::load_2d(base + 2 * S::w_bytes, &maps.u, hv * DV + v0, row, &full[s]);
+        tma::load_1d(gam_all + s * BT, gamma_ptr(a.gamma, c_first + ic, a.HV, hv), BT * 4, &full[s]);
       }
-      // gamma of the chunk (rows past the valid length repeat the last valid value)
-      float* gs = gam_all + s * BT;
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const int i = lane + 32 * j;
-        const int r = i < cm.len ? i : cm.len - 1;
-        gs[i] = a.gamma[(int64_t)(cm.row + r) * a.HV + hv];
-      }
-      __syncwarp();
-      if (lane == 0) tc5::mbar_arrive(&full[s]);
     }
   } else if (warp == WARP_MMA) {
     // ================= MMA warp: one thread issues the contractions and the TMA stores =================
     if (lane == 0) {
       const uint32_t vt_addr = tc5::smem_addr(smem + S::o_vt);
+      ChunkMeta cm_next = load_chunk_meta(a.chunk_meta, c_first);
       for (int ic = 0; ic < nc; ++ic) {
         const int c = c_first + ic, s = ic % NSTAGE, buf = ic & 1;
-        const ChunkMeta cm = load_chunk_meta(a.chunk_meta, c);
+        const ChunkMeta cm = cm_next;
+        if (ic + 1 < nc) cm_next = load_chunk_meta(a.chunk_meta, c + 1);
         const uint32_t w_addr = tc5::smem_addr(smem + (size_t)s * S::stage_bytes);
         const uint32_t k_addr = w_addr + (uint32_t)S::w_bytes;
         unsigned char* sb_ptr = smem + S::o_sb + buf * S::sb_bytes;
         if (!tc5::mbar_wait(&full[s], (ic / NSTAGE) & 1) || !tc5::mbar_wait(sb_ready, ic & 1)) { failed = true; break; }
         tc5::fence_after_sync();
         // V_acc = W S_bf16
-        issue_mma(TM_V, Operand{w_addr, BT, 0}, Operand{tc5::smem_addr(sb_ptr), DK, 1}, 64, BV, DK / 16, 0);
+        issue_mma_t<DK / 16>(TM_V, Operand{w_addr, BT, 0}, Operand{tc5::smem_addr(sb_ptr), DK, 1}, 64, BV, 0);
         tc5::mma_commit(v_ready);
         if (a.h != nullptr) {
           tma::store_2d(&maps.h, v0, (c * a.HV + hv) * DK, sb_ptr);
           tma::store_commit();
+          // every store older than this h_c has released its shared tile before the next step re-writes it;
+          // waiting here costs nothing, this thread would otherwise idle until the v_new tiles are ready
+          tma::store_wait_read<1>();
+        } else {
+          tma::store_wait_read<0>();
         }
         if (!tc5::mbar_wait(vt_ready, ic & 1)) { failed = true; break; }
-        // every store older than this step's h_c has released its shared tile (they are re-written next step)
-        if (a.h != nullptr) tma::store_wait_read<1>(); else tma::store_wait_read<0>();
         tc5::fence_after_sync();
         // S += K^T V~
-        issue_mma(TM_S, Operand{k_addr, BT, 1}, Operand{vt_addr, BT, 1}, DK, BV, BT / 16, 1);
+        issue_mma_t<BT / 16>(TM_S, Operand{k_addr, BT, 1}, Operand{vt_addr, BT, 1}, DK, BV, 1);
         tc5::mma_commit(s_ready);
         tc5::mma_commit(&empty[s]);
         if (a.v_new != nullptr && cm.len == BT) {
@@ -308,12 +303,14 @@ int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
   ScanFwdMaps m;
   const uint64_t pk = (uint64_t)a.H * DK, pw = (uint64_t)a.HV * DK, pv = (uint64_t)a.HV * DV;
   int rc = 0;
-  rc |= tma::encode_bf16_2d(&m.w, a.w, a.rows, pw, pw, BT);
-  rc |= tma::encode_bf16_2d(&m.k, a.k, a.rows, pk, pk, BT);
+  rc |= tma::encode_bf16_panels(&m.w, a.w, a.rows, pw, pw, BT, DK / 64);
+  rc |= tma::encode_bf16_panels(&m.k, a.k, a.rows, pk, pk, BT, DK / 64);
+  CUtensorMap dummy;
+  rc |= tma::encode_bf16_2d(&dummy, a.k, a.rows, pk, pk, BT);
   // an absent tensor gets a well-formed map over k; it is never used
-  if (a.u) rc |= tma::encode_bf16_2d(&m.u, a.u, a.rows, pv, pv, BT); else m.u = m.k;
-  if (a.h) rc |= tma::encode_bf16_2d(&m.h, a.h, (uint64_t)a.n_chunks * a.HV * DK, DV, DV, DK); else m.h = m.k;
-  if (a.v_new) rc |= tma::encode_bf16_2d(&m.vn, a.v_new, a.rows, pv, pv, BT); else m.vn = m.k;
+  if (a.u) rc |= tma::encode_bf16_2d(&m.u, a.u, a.rows, pv, pv, BT); else m.u = dummy;
+  if (a.h) rc |= tma::encode_bf16_2d(&m.h, a.h, (uint64_t)a.n_chunks * a.HV * DK, DV, DV, DK); else m.h = dummy;
+  if (a.v_new) rc |= tma::encode_bf16_2d(&m.vn, a.v_new, a.rows, pv, pv, BT); else m.vn = dummy;
   if (rc != 0) return set_error(B200GDN_ERR_CUDA, "scan_fwd: cuTensorMapEncodeTiled failed (%d)", rc);
   dim3 grid(DV / BV, a.HV, a.n_seq);
   scan_fwd_kernel<DK, DV, NSTAGE><<<grid, NTHREADS, S::bytes, st>>>(a, m);

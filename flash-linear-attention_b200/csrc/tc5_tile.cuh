@@ -60,15 +60,32 @@ struct Operand {
   int rows;         // rows of the stored tile (panel stride = rows * 128 bytes)
   int mn_major;     // 0: K-major, 1: MN-major
 };
-__device__ __forceinline__ uint64_t operand_desc(const Operand& o, int kstep) {
-  if (o.mn_major) return tc5::smem_desc(o.saddr + kstep * 2048, o.rows * 128, 1024);
-  return tc5::smem_desc(o.saddr + (kstep >> 2) * o.rows * 128 + (kstep & 3) * 32, 16, 1024);
+__device__ __forceinline__ uint64_t operand_desc0(const Operand& o) {
+  return o.mn_major ? tc5::smem_desc(o.saddr, o.rows * 128, 1024) : tc5::smem_desc(o.saddr, 16, 1024);
 }
-// D[tmem] (+)= A B over `ksteps` steps of 16.  `acc` = 0 starts a fresh accumulator.
+// byte offset of contraction step `kstep` (16 elements) from the operand's first descriptor
+__device__ __forceinline__ uint32_t operand_step_bytes(const Operand& o, int kstep) {
+  return o.mn_major ? (uint32_t)kstep * 2048u : (uint32_t)((kstep >> 2) * o.rows * 128 + (kstep & 3) * 32);
+}
+// D[tmem] (+)= A B over KSTEPS steps of 16.  `acc` = 0 starts a fresh accumulator.  The two base descriptors
+// are built once; every step only adds its byte offset (>> 4) to the address field.
+template <int KSTEPS>
+__device__ __forceinline__ void issue_mma_t(uint32_t d_tmem, const Operand& a, const Operand& b, int M, int N, int acc,
+                                            int neg_a = 0) {
+  const uint32_t idesc = tc5::idesc_bf16(M, N, a.mn_major, b.mn_major, neg_a);
+  const uint64_t da = operand_desc0(a), db = operand_desc0(b);
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks)
+    tc5::mma_ss(d_tmem, da + (operand_step_bytes(a, ks) >> 4), db + (operand_step_bytes(b, ks) >> 4), idesc,
+                (acc || ks > 0) ? 1u : 0u);
+}
 __device__ __forceinline__ void issue_mma(uint32_t d_tmem, const Operand& a, const Operand& b, int M, int N, int ksteps,
                                           int acc, int neg_a = 0) {
   const uint32_t idesc = tc5::idesc_bf16(M, N, a.mn_major, b.mn_major, neg_a);
-  for (int ks = 0; ks < ksteps; ++ks) tc5::mma_ss(d_tmem, operand_desc(a, ks), operand_desc(b, ks), idesc, (acc || ks > 0) ? 1u : 0u);
+  const uint64_t da = operand_desc0(a), db = operand_desc0(b);
+  for (int ks = 0; ks < ksteps; ++ks)
+    tc5::mma_ss(d_tmem, da + (operand_step_bytes(a, ks) >> 4), db + (operand_step_bytes(b, ks) >> 4), idesc,
+                (acc || ks > 0) ? 1u : 0u);
 }
 
 // ---- accumulator read-back -------------------------------------------------------------------------------

@@ -36,6 +36,32 @@ inline int encode_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uin
   return static_cast<int>(r);
 }
 
+// 3-D "panel" view of the same kind of matrix: dimension 0 = 64 columns of one panel, dimension 1 = rows,
+// dimension 2 = panel index (cols / 64, 128 bytes apart).  A box {64, box_rows, box_panels} lands in
+// shared memory panel after panel, i.e. a [box_rows][64 * box_panels] tile in the panel layout of
+// tc5.cuh arrives with ONE copy instruction.
+inline int encode_bf16_panels(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems,
+                              uint32_t box_rows, uint32_t box_panels) {
+  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || p == nullptr) return -1;
+    fn = reinterpret_cast<EncodeFn>(p);
+  }
+  cuuint64_t dims[3] = {64, rows, cols / 64};
+  cuuint64_t strides[2] = {pitch_elems * 2, 128};
+  cuuint32_t box[3] = {64, box_rows, box_panels};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return static_cast<int>(r);
+}
+
 // ---- device --------------------------------------------------------------------------------------------
 #ifdef __CUDACC__
 __device__ __forceinline__ uint32_t saddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -47,6 +73,26 @@ __device__ __forceinline__ void load_2d(void* dst, const CUtensorMap* map, int x
           saddr(dst)),
       "l"(reinterpret_cast<uint64_t>(map)), "r"(saddr(bar)), "r"(x), "r"(y)
       : "memory");
+}
+// panel view: row y, first panel z
+__device__ __forceinline__ void load_3d(void* dst, const CUtensorMap* map, int y, int z, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n" ::"r"(
+          saddr(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(saddr(bar)), "r"(0), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void store_3d(const CUtensorMap* map, int y, int z, const void* src) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];\n" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(saddr(src)), "r"(0), "r"(y), "r"(z)
+               : "memory");
+}
+// plain contiguous copy global -> shared (both 16-byte aligned, size a multiple of 16)
+__device__ __forceinline__ void load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(saddr(dst)),
+               "l"(src), "r"(bytes), "r"(saddr(bar))
+               : "memory");
 }
 // shared -> global box; joins the current bulk group of the issuing thread.
 __device__ __forceinline__ void store_2d(const CUtensorMap* map, int x, int y, const void* src) {

@@ -68,7 +68,8 @@ typedef struct b200gdn_chunk_args {
   void* o;                       /* bf16 [rows,HV,V] */
   float* ht;                     /* [n_seq,HV,K,V] or NULL */
   /* written by the forward pass, read by the backward pass */
-  float* gamma;                  /* [rows,HV]  chunk-local cumsum(g) * log2(e) */
+  float* gamma;                  /* [n_chunks,HV,64]  chunk-local cumsum(g) * log2(e); entries past a ragged
+                                    chunk's length repeat the last valid value */
   void* A;                       /* bf16 [rows,HV,64]  rows of (I + L)^-1 */
   void* w;                       /* bf16 [rows,HV,K] */
   void* u;                       /* bf16 [rows,HV,V] */
@@ -102,7 +103,7 @@ int b200gdn_chunk_fwd(const b200gdn_chunk_args* args, void* stream);
  * inside a foreign CUDA context, a C host that owns only inputs and outputs): the six intermediate tensors live
  * in one array built into the library, B200GDN_STATIC_SCRATCH_BYTES bytes per GPU that loads the library, held
  * until exit.  The gamma/A/w/u/h/v_new fields of `args` are ignored and nothing is saved for a backward pass.
- * Limit: align256(rows*HV*4) + align256(rows*HV*128) + align256(rows*HV*K*2) + 2*align256(rows*HV*V*2)
+ * Limit: align256(n_chunks*HV*256) + align256(rows*HV*128) + align256(rows*HV*K*2) + 2*align256(rows*HV*V*2)
  *        + align256(n_chunks*HV*K*V*2)  <=  B200GDN_STATIC_SCRATCH_BYTES
  * (e.g. 2048 tokens x 16 heads at K = V = 128); larger problems return B200GDN_ERR_TOO_LARGE and launch nothing.
  * Makes no allocating call.  The first call on each device looks up the array's address and should come before

@@ -32,6 +32,24 @@ def oracle_chain(d, dtype=torch.float32, emulate_bf16=False):
     return fwd, bwd
 
 
+def gamma_to_chunks(gamma_rows, bounds):
+    """[rows,HV] -> the kernels' per-chunk layout [n_chunks,HV,64] (tail repeats the last valid value)."""
+    out = []
+    for (_, s, L) in O.chunk_table(bounds):
+        g = gamma_rows[s:s + L]
+        if L < 64:
+            g = torch.cat([g, g[-1:].expand(64 - L, -1)], 0)
+        out.append(g.transpose(0, 1))
+    return torch.stack(out, 0).contiguous()
+
+
+def gamma_from_chunks(gamma_chunks, bounds, rows):
+    out = torch.zeros(rows, gamma_chunks.shape[1], dtype=gamma_chunks.dtype)
+    for c, (_, s, L) in enumerate(O.chunk_table(bounds)):
+        out[s:s + L] = gamma_chunks[c].transpose(0, 1)[:L]
+    return out
+
+
 def run_abi(d, dev='cuda', fwd_mask=0, bwd_mask=0, overrides=None, do_bwd=True):
     """Forward (and backward) through b200gdn_chunk_fwd / b200gdn_chunk_bwd.  ``overrides`` replaces
     saved tensors (by name) before the backward pass, e.g. with the oracle's, to isolate one stage."""
@@ -49,7 +67,7 @@ def run_abi(d, dev='cuda', fwd_mask=0, bwd_mask=0, overrides=None, do_bwd=True):
     nan = float('nan')
     t = dict(
         o=torch.full((rows, HV, V), nan, **bf), ht=torch.full((n_seq, HV, K, V), nan, **f32),
-        gamma=torch.full((rows, HV), nan, **f32), A=torch.full((rows, HV, 64), nan, **bf),
+        gamma=torch.full((n_chunks, HV, 64), nan, **f32), A=torch.full((rows, HV, 64), nan, **bf),
         w=torch.full((rows, HV, K), nan, **bf), u=torch.full((rows, HV, V), nan, **bf),
         h=torch.full((n_chunks, HV, K, V), nan, **bf), v_new=torch.full((rows, HV, V), nan, **bf),
         dq=torch.full((rows, H, K), nan, **bf), dk=torch.full((rows, H, K), nan, **bf),
@@ -64,6 +82,8 @@ def run_abi(d, dev='cuda', fwd_mask=0, bwd_mask=0, overrides=None, do_bwd=True):
     a.d_o, a.dht = do.data_ptr(), dht.data_ptr()
     if overrides:
         for name, val in overrides.items():
+            if name == 'gamma':
+                val = gamma_to_chunks(val, d['bounds'])
             t[name] = val.to(dev).to(t[name].dtype).contiguous()
     for name, val in t.items():
         setattr(a, name, val.data_ptr())
@@ -75,4 +95,6 @@ def run_abi(d, dev='cuda', fwd_mask=0, bwd_mask=0, overrides=None, do_bwd=True):
         a.stage_mask = bwd_mask
         _lib.call('b200gdn_chunk_bwd', a, st)
     torch.cuda.synchronize()
-    return {n_: x.float().cpu() for n_, x in t.items()}
+    out = {n_: x.float().cpu() for n_, x in t.items()}
+    out['gamma'] = gamma_from_chunks(out['gamma'], d['bounds'], rows)
+    return out
