@@ -268,7 +268,9 @@ class ChunkGatedDeltaRuleCPFunction(torch.autograd.Function):
             if not cp_context.is_first_rank:
                 first = seq_meta[0:1]
                 len0 = int(cp_context.cu_seqlens_cpu[1])
-                tmp = dv2[:len0].clone()            # the scan completes dv2 in place; keep dv_local intact
+                # the scan completes dv2 in place; keep dv_local intact.  Full-size copies: the kernels' tensor
+                # maps span all `rows` rows even though only the first sequence is scanned
+                tmp = dv2.clone()
                 dh_ext = torch.empty(1, HV, K, V, **f32)
                 p = new_chunk_args(qb, kb, vb, scale, (chunk_meta, first, (n_chunks, 1)))
                 p.gamma, p.w, p.d_o, p.dv2, p.dh0 = gamma.data_ptr(), w.data_ptr(), dob.data_ptr(), tmp.data_ptr(), \
@@ -276,7 +278,7 @@ class ChunkGatedDeltaRuleCPFunction(torch.autograd.Function):
                 p.stage_mask = _lib.BWD_SCAN
                 _lib.call('b200gdn_chunk_bwd', p, st)
                 eye = torch.eye(K, **f32).expand(1, HV, K, K).contiguous()
-                zeros = torch.zeros(len0, HV, K, **bf16)
+                zeros = torch.zeros(rows, HV, K, **bf16)
                 dM = torch.empty(1, HV, K, K, **f32)
                 p = new_chunk_args(qb, kb, vb, scale, (chunk_meta, first, (n_chunks, 1)))
                 p.V = K

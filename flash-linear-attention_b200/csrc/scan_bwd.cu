@@ -1,191 +1,322 @@
-// Reverse state-gradient scan: for every (sequence, value head) walk the chunks backwards with the
-// K x V gradient dS resident in registers:
+// Reverse state-gradient scan: for every (sequence, value head) walk the chunks backwards with the K x V
+// fp32 gradient dS resident in tensor memory (TMEM):
 //     dh_c = dS (bf16 snapshot, gradient w.r.t. the state at chunk END)
 //     dv2  = (K dS) 2^(gamma_last - gamma) + dv_local
-//     dS  <- 2^gamma_last dS + scale (Q 2^gamma)^T do - W^T dv2
+//     dS  <- 2^gamma_last dS + (Q)^T (do scale 2^gamma) - W^T dv2
 // Replaces chunk_gated_delta_rule_bwd_kernel_dhu_blockdim64 (fla/ops/common/chunk_delta_h.py:369-683).
-// Same CTA layout as the forward scan (a BV-wide column slice per CTA, warps 4 x BV/32).
+//
+// Same organisation as the forward scan: one CTA per 64-column slice of one state; a producer thread feeds
+// a ring of stages with TMA (Q, K, W tiles, the do and dv_local slices, gamma); one thread issues
+// tcgen05.mma  acc = K dS_bf16  and  dS += Q^T do_s - W^T dv2  with accumulators in TMEM and the TMA
+// stores of dh_c and dv2; eight epilogue warps move dS between TMEM and shared memory and form dv2.
+// Rows of a ragged last chunk that lie past its end are zeroed where dv2 and do_s are formed.
 //
 // With d_o == NULL (zeros), dv2 initialised to zeros, dht = identity and V := K the result in dh0 is the
 // backward transition matrix of a shard for context parallelism (fla/ops/cp/chunk_delta_h.py:478-744).
-#include "gdn_common.cuh"
+#include "tc5_tile.cuh"
+#include "tma.cuh"
 
 namespace gdn {
 namespace {
 
-template <int DK, int BV>
+constexpr int BV = 64;
+constexpr int NEPI = 256;
+constexpr int WARP_PROD = NEPI / 32, WARP_MMA = NEPI / 32 + 1;
+constexpr int NTHREADS = NEPI + 64;
+__device__ int g_scan_bwd_timeout = 0;
+
+template <int DK, int NSTAGE>
 struct ScanBwdSmem {
-  static constexpr int LDK = DK + PAD, LDB = BV + PAD;
-  static constexpr size_t t_bytes = sizeof(__nv_bfloat16) * BT * LDK;
-  static constexpr size_t s_bytes = sizeof(__nv_bfloat16) * BT * LDB;
-  static constexpr size_t stage_bytes = 3 * t_bytes + 2 * s_bytes + sizeof(float) * BT;  // Q, K, W, do, dv_local, gamma
-  static constexpr size_t sb_off = 2 * stage_bytes;
-  static constexpr size_t bytes = sb_off + sizeof(__nv_bfloat16) * DK * LDB;
+  static constexpr size_t t_bytes = BT * DK * 2;            // Q, K, W tiles
+  static constexpr size_t s_bytes = BT * BV * 2;            // do slice, dv_local slice
+  static constexpr size_t stage_bytes = 3 * t_bytes + 2 * s_bytes;
+  static constexpr size_t o_sb = NSTAGE * stage_bytes;      // 2 x dS snapshot [DK][64]
+  static constexpr size_t sb_bytes = DK * BV * 2;
+  static constexpr size_t o_d2 = o_sb + 2 * sb_bytes;       // 2 x dv2 slice [64][64]
+  static constexpr size_t o_gam = o_d2 + 2 * s_bytes;
+  static constexpr size_t o_bar = o_gam + NSTAGE * BT * 4;
+  static constexpr size_t bytes = o_bar + (2 * NSTAGE + 4) * 8 + 16 + 1024;
 };
 
-template <int DK, int DV, int BV>
-__global__ void __launch_bounds__(128 * (BV / 32)) scan_bwd_kernel(const b200gdn_chunk_args a) {
-  constexpr int NCG = BV / 32;
-  constexpr int NTHREADS = 128 * NCG;
-  constexpr int MT = DK / 64;
-  using S = ScanBwdSmem<DK, BV>;
-  extern __shared__ __align__(16) unsigned char smem[];
-  __nv_bfloat16* Sb = reinterpret_cast<__nv_bfloat16*>(smem + S::sb_off);
+struct ScanBwdMaps {
+  CUtensorMap q, k, w, d_o, dv2, dh;
+};
+
+__device__ __forceinline__ void bar_epi_b() { asm volatile("bar.sync 1, %0;\n" ::"n"(NEPI) : "memory"); }
+
+template <int DK, int DV, int NSTAGE>
+__global__ void __launch_bounds__(NTHREADS) scan_bwd_kernel(const b200gdn_chunk_args a, const __grid_constant__ ScanBwdMaps maps) {
+  using S = ScanBwdSmem<DK, NSTAGE>;
+  constexpr int NH = DK / 64;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* gam_all = reinterpret_cast<float*>(smem + S::o_gam);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::o_bar);
+  uint64_t* empty = full + NSTAGE;
+  uint64_t* s_ready = empty + NSTAGE;
+  uint64_t* sb_ready = s_ready + 1;
+  uint64_t* v_ready = sb_ready + 1;
+  uint64_t* vt_ready = v_ready + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(vt_ready + 1);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int rg = warp & 3, cg = warp >> 2;
-  const int g = lane >> 2, t = lane & 3;
   const int v0 = blockIdx.x * BV, hv = blockIdx.y, n = blockIdx.z;
   const int G = a.HV / a.H, hq = hv / G;
   const int c_first = a.seq_meta[2 * n], nc = a.seq_meta[2 * n + 1];
-
-  const __nv_bfloat16* qbase = reinterpret_cast<const __nv_bfloat16*>(a.q);
-  const __nv_bfloat16* kbase = reinterpret_cast<const __nv_bfloat16*>(a.k);
-  const __nv_bfloat16* wbase = reinterpret_cast<const __nv_bfloat16*>(a.w);
-  const __nv_bfloat16* dobase = reinterpret_cast<const __nv_bfloat16*>(a.d_o);
-  __nv_bfloat16* dv2base = reinterpret_cast<__nv_bfloat16*>(a.dv2);
-
-  auto issue_loads = [&](const ChunkMeta& cm, int c, int s) {
-    unsigned char* base = smem + (size_t)s * S::stage_bytes;
-    __nv_bfloat16* Qt = reinterpret_cast<__nv_bfloat16*>(base);
-    __nv_bfloat16* Kt = reinterpret_cast<__nv_bfloat16*>(base + S::t_bytes);
-    __nv_bfloat16* Wt = reinterpret_cast<__nv_bfloat16*>(base + 2 * S::t_bytes);
-    __nv_bfloat16* Dt = reinterpret_cast<__nv_bfloat16*>(base + 3 * S::t_bytes);
-    __nv_bfloat16* Lt = reinterpret_cast<__nv_bfloat16*>(base + 3 * S::t_bytes + S::s_bytes);
-    float* gs = reinterpret_cast<float*>(base + 3 * S::t_bytes + 2 * S::s_bytes);
-    load_tile_async<DK, NTHREADS>(Qt, qbase + ((int64_t)cm.row * a.H + hq) * DK, (int64_t)a.H * DK, cm.len, tid);
-    load_tile_async<DK, NTHREADS>(Kt, kbase + ((int64_t)cm.row * a.H + hq) * DK, (int64_t)a.H * DK, cm.len, tid);
-    load_tile_async<DK, NTHREADS>(Wt, wbase + ((int64_t)cm.row * a.HV + hv) * DK, (int64_t)a.HV * DK, cm.len, tid);
-    if (dobase != nullptr)
-      load_tile_async<BV, NTHREADS>(Dt, dobase + ((int64_t)cm.row * a.HV + hv) * DV + v0, (int64_t)a.HV * DV, cm.len, tid);
-    load_tile_async<BV, NTHREADS>(Lt, dv2base + ((int64_t)cm.row * a.HV + hv) * DV + v0, (int64_t)a.HV * DV, cm.len, tid);
-    load_gamma_async(gs, a.gamma, c, a.HV, hv, tid);
-  };
-
-  float S_[MT][4][4];
-  {
-    const float* dht = a.dht ? a.dht + ((int64_t)n * a.HV + hv) * DK * DV : nullptr;
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          int r = rg * (DK / 4) + mt * 16 + g + ((e >> 1) << 3);
-          int col = v0 + cg * 32 + nt * 8 + 2 * t + (e & 1);
-          S_[mt][nt][e] = dht ? dht[(int64_t)r * DV + col] : 0.f;
-        }
-  }
-
-  // chunk descriptors are fetched two iterations ahead so that no global-load latency sits on the chain
   const int c_last = c_first + nc - 1;
-  ChunkMeta cm_cur = load_chunk_meta(a.chunk_meta, nc > 0 ? c_last : c_first);
-  ChunkMeta cm_nxt = load_chunk_meta(a.chunk_meta, nc > 1 ? c_last - 1 : c_first);
-  if (nc > 0) issue_loads(cm_cur, c_last, 0);
-  cp_async_commit();
+  const bool has_do = a.d_o != nullptr;
 
-  for (int ic = 0; ic < nc; ++ic) {
-    const int c = c_last - ic, s = ic & 1;
-    const ChunkMeta cm = cm_cur;
-    const ChunkMeta cm_nn = load_chunk_meta(a.chunk_meta, ic + 2 < nc ? c - 2 : c);
-    unsigned char* base = smem + (size_t)s * S::stage_bytes;
-    const __nv_bfloat16* Qt = reinterpret_cast<const __nv_bfloat16*>(base);
-    const __nv_bfloat16* Kt = reinterpret_cast<const __nv_bfloat16*>(base + S::t_bytes);
-    const __nv_bfloat16* Wt = reinterpret_cast<const __nv_bfloat16*>(base + 2 * S::t_bytes);
-    __nv_bfloat16* Dt = reinterpret_cast<__nv_bfloat16*>(base + 3 * S::t_bytes);
-    __nv_bfloat16* Lt = reinterpret_cast<__nv_bfloat16*>(base + 3 * S::t_bytes + S::s_bytes);
-    const float* gs = reinterpret_cast<const float*>(base + 3 * S::t_bytes + 2 * S::s_bytes);
+  if (warp == 0) tc5::tmem_alloc(tmem_slot, 128);
+  if (tid == 32) {
+    for (int s = 0; s < NSTAGE; ++s) {
+      tc5::mbar_init(&full[s], 1);
+      tc5::mbar_init(&empty[s], 1);
+    }
+    tc5::mbar_init(s_ready, 1);
+    tc5::mbar_init(sb_ready, NEPI / 32);
+    tc5::mbar_init(v_ready, 1);
+    tc5::mbar_init(vt_ready, NEPI / 32);
+    tc5::fence_mbar_init();
+  }
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tm = *tmem_slot;
+  const uint32_t TM_S = tm, TM_V = tm + 64;
+  bool failed = false;
 
-    cp_async_wait<0>();
-    __syncthreads();
-    if (ic + 1 < nc) issue_loads(cm_nxt, c - 1, s ^ 1);
-    cp_async_commit();
-    cm_cur = cm_nxt;
-    cm_nxt = cm_nn;
+  if (warp == WARP_PROD) {
+    // ================= producer: TMA loads, chunks in reverse order =================
+    if (lane == 0) {
+      tma::prefetch_map(&maps.q);
+      tma::prefetch_map(&maps.k);
+      tma::prefetch_map(&maps.w);
+      const uint32_t tx_bytes = (uint32_t)((has_do ? 3 : 2) * S::t_bytes + (has_do ? 2 : 1) * S::s_bytes + BT * 4);
+      int row_next = nc > 0 ? load_chunk_meta(a.chunk_meta, c_last).row : 0;
+      for (int ic = 0; ic < nc; ++ic) {
+        const int s = ic % NSTAGE, c = c_last - ic;
+        const int row = row_next;
+        if (ic + 1 < nc) row_next = load_chunk_meta(a.chunk_meta, c - 1).row;
+        if (ic >= NSTAGE && !tc5::mbar_wait(&empty[s], ((ic / NSTAGE) - 1) & 1)) { failed = true; break; }
+        unsigned char* base = smem + (size_t)s * S::stage_bytes;
+        tc5::mbar_expect_tx(&full[s], tx_bytes);
+        tma::load_3d(base + S::t_bytes, &maps.k, row, (hq * DK) / 64, &full[s]);
+        tma::load_3d(base + 2 * S::t_bytes, &maps.w, row, (hv * DK) / 64, &full[s]);
+        tma::load_2d(base + 3 * S::t_bytes + S::s_bytes, &maps.dv2, hv * DV + v0, row, &full[s]);
+        if (has_do) {
+          tma::load_3d(base, &maps.q, row, (hq * DK) / 64, &full[s]);
+          tma::load_2d(base + 3 * S::t_bytes, &maps.d_o, hv * DV + v0, row, &full[s]);
+        }
+        tma::load_1d(gam_all + s * BT, gamma_ptr(a.gamma, c, a.HV, hv), BT * 4, &full[s]);
+      }
+    }
+  } else if (warp == WARP_MMA) {
+    // ================= MMA thread =================
+    if (lane == 0) {
+      ChunkMeta cm_next = load_chunk_meta(a.chunk_meta, nc > 0 ? c_last : c_first);
+      for (int ic = 0; ic < nc; ++ic) {
+        const int c = c_last - ic, s = ic % NSTAGE, buf = ic & 1;
+        const ChunkMeta cm = cm_next;
+        if (ic + 1 < nc) cm_next = load_chunk_meta(a.chunk_meta, c - 1);
+        const uint32_t q_addr = tc5::smem_addr(smem + (size_t)s * S::stage_bytes);
+        const uint32_t k_addr = q_addr + (uint32_t)S::t_bytes, w_addr = q_addr + 2 * (uint32_t)S::t_bytes;
+        const uint32_t do_addr = q_addr + 3 * (uint32_t)S::t_bytes;
+        unsigned char* sb_ptr = smem + S::o_sb + buf * S::sb_bytes;
+        unsigned char* d2_ptr = smem + S::o_d2 + buf * S::s_bytes;
+        if (!tc5::mbar_wait(&full[s], (ic / NSTAGE) & 1) || !tc5::mbar_wait(sb_ready, ic & 1)) { failed = true; break; }
+        tc5::fence_after_sync();
+        // acc = K dS_bf16
+        issue_mma_t<DK / 16>(TM_V, Operand{k_addr, BT, 0}, Operand{tc5::smem_addr(sb_ptr), DK, 1}, 64, BV, 0);
+        tc5::mma_commit(v_ready);
+        if (a.dh != nullptr) {
+          tma::store_2d(&maps.dh, v0, (c * a.HV + hv) * DK, sb_ptr);
+          tma::store_commit();
+          tma::store_wait_read<1>();   // older stores have released their tiles (re-written next step)
+        } else {
+          tma::store_wait_read<0>();
+        }
+        if (!tc5::mbar_wait(vt_ready, ic & 1)) { failed = true; break; }
+        tc5::fence_after_sync();
+        // dS += Q^T do_s - W^T dv2
+        if (has_do) issue_mma_t<BT / 16>(TM_S, Operand{q_addr, BT, 1}, Operand{do_addr, BT, 1}, DK, BV, 1);
+        issue_mma_t<BT / 16>(TM_S, Operand{w_addr, BT, 1}, Operand{tc5::smem_addr(d2_ptr), BT, 1}, DK, BV, 1, /*neg_a=*/1);
+        tc5::mma_commit(s_ready);
+        tc5::mma_commit(&empty[s]);
+        if (cm.len == BT) {
+          tma::store_2d(&maps.dv2, hv * DV + v0, cm.row, d2_ptr);
+          tma::store_commit();
+        }
+      }
+      tma::store_wait_all<0>();
+    }
+  } else {
+    // ================= epilogue warps =================
+    const int q = warp & 3, hc = warp >> 2;
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t sb_base = smem_u32(smem + S::o_sb);
+    const uint32_t d2_base = smem_u32(smem + S::o_d2);
+    const int srow0 = (DK / 4) * q;
+    const uint32_t s_lane = (uint32_t)(32 * q) << 16;
 
+    float Sr[NH][16];
+    {
+      const float* dht = a.dht ? a.dht + ((int64_t)n * a.HV + hv) * DK * DV : nullptr;
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-      acc_to_smem<4>(Sb + (rg * (DK / 4) + mt * 16) * S::LDB + cg * 32, S::LDB, S_[mt], lane);
-    __syncthreads();
-    if (a.dh != nullptr) {
-      __nv_bfloat16* hg = reinterpret_cast<__nv_bfloat16*>(a.dh) + ((int64_t)c * a.HV + hv) * DK * DV + v0;
-      store_tile<DK, BV, NTHREADS>(hg, DV, Sb, DK, tid);
+      for (int hf = 0; hf < NH; ++hf)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int r = srow0 + 16 * hf + g + ((e >> 1) << 3);
+            const int col = v0 + 32 * hc + 8 * i + 2 * t + (e & 1);
+            Sr[hf][4 * i + e] = dht ? dht[(int64_t)r * DV + col] : 0.f;
+          }
     }
 
-    // dv2 = (K dS) 2^(gamma_last - gamma) + dv_local ; in place over the dv_local slice.
-    // do <- do * scale * 2^gamma in place (the right-hand side of the Q^T product).
-    float acc[4][4];
-    zero_acc<4>(acc);
-    warp_mma<4, DK / 16, AMajor::Row, BMajor::KN>(acc, Kt + rg * 16 * S::LDK, S::LDK, Sb + cg * 32, S::LDB, lane);
-    const float glast = gs[BT - 1];
-    {
-      const int r_lo = rg * 16 + g, r_hi = r_lo + 8;
-      const float e_lo = exp2f(glast - gs[r_lo]), e_hi = exp2f(glast - gs[r_hi]);
-      const float q_lo = a.scale * exp2f(gs[r_lo]), q_hi = a.scale * exp2f(gs[r_hi]);
+    for (int ic = 0; ic < nc; ++ic) {
+      const int c = c_last - ic, s = ic % NSTAGE, buf = ic & 1;
+      const ChunkMeta cm = load_chunk_meta(a.chunk_meta, c);
+      const uint32_t stage0 = smem_u32(smem + (size_t)s * S::stage_bytes);
+      const uint32_t do_tile = stage0 + 3 * (uint32_t)S::t_bytes, dl_tile = do_tile + (uint32_t)S::s_bytes;
+      const float* gs = gam_all + s * BT;
+      const uint32_t sb_tile = sb_base + buf * (uint32_t)S::sb_bytes;
+      const uint32_t d2_tile = d2_base + buf * (uint32_t)S::s_bytes;
+
+      if (ic > 0) {
+        if (!tc5::mbar_wait(s_ready, (ic - 1) & 1)) { failed = true; break; }
+        tc5::fence_after_sync();
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
-        const int col = cg * 32 + nt * 8 + 2 * t;
-        uint32_t* pl_lo = reinterpret_cast<uint32_t*>(Lt + r_lo * S::LDB + col);
-        uint32_t* pl_hi = reinterpret_cast<uint32_t*>(Lt + r_hi * S::LDB + col);
-        float2 l_lo = unpack_bf16(*pl_lo), l_hi = unpack_bf16(*pl_hi);
-        *pl_lo = pack_bf16(acc[nt][0] * e_lo + l_lo.x, acc[nt][1] * e_lo + l_lo.y);
-        *pl_hi = pack_bf16(acc[nt][2] * e_hi + l_hi.x, acc[nt][3] * e_hi + l_hi.y);
-        uint32_t* pd_lo = reinterpret_cast<uint32_t*>(Dt + r_lo * S::LDB + col);
-        uint32_t* pd_hi = reinterpret_cast<uint32_t*>(Dt + r_hi * S::LDB + col);
-        if (dobase != nullptr) {
-          float2 d_lo = unpack_bf16(*pd_lo), d_hi = unpack_bf16(*pd_hi);
-          *pd_lo = pack_bf16(d_lo.x * q_lo, d_lo.y * q_lo);
-          *pd_hi = pack_bf16(d_hi.x * q_hi, d_hi.y * q_hi);
+        for (int hf = 0; hf < NH; ++hf) tc5::tmem_ld_16x256b_x4(TM_S + s_lane + ((uint32_t)(16 * hf) << 16) + 32 * hc, Sr[hf]);
+        tc5::tmem_ld_wait();
+      }
+#pragma unroll
+      for (int hf = 0; hf < NH; ++hf)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int col = 32 * hc + 8 * i + 2 * t, r = srow0 + 16 * hf + g;
+          sts32(swz_pair_addr(sb_tile, DK, r, col), pack_bf16(Sr[hf][4 * i], Sr[hf][4 * i + 1]));
+          sts32(swz_pair_addr(sb_tile, DK, r + 8, col), pack_bf16(Sr[hf][4 * i + 2], Sr[hf][4 * i + 3]));
+        }
+      if (!tc5::mbar_wait(&full[s], (ic / NSTAGE) & 1)) { failed = true; break; }
+      const float glast = gs[BT - 1];
+      const float dec = exp2f(glast);
+#pragma unroll
+      for (int hf = 0; hf < NH; ++hf) {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) Sr[hf][e] *= dec;
+        tc5::tmem_st_16x256b_x4(TM_S + s_lane + ((uint32_t)(16 * hf) << 16) + 32 * hc, Sr[hf]);
+      }
+      tc5::tmem_st_wait();
+      tc5::fence_async_smem();
+      tc5::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive(sb_ready);
+
+      // do_s = do scale 2^gamma (in place, rows past the chunk's end zeroed); dv_local into registers
+      const int r_lo = 16 * q + g, r_hi = r_lo + 8;
+      const bool ok_lo = r_lo < cm.len, ok_hi = r_hi < cm.len;
+      const float q_lo = ok_lo ? a.scale * exp2f(gs[r_lo]) : 0.f, q_hi = ok_hi ? a.scale * exp2f(gs[r_hi]) : 0.f;
+      const float e_lo = ok_lo ? exp2f(glast - gs[r_lo]) : 0.f, e_hi = ok_hi ? exp2f(glast - gs[r_hi]) : 0.f;
+      float2 l_lo[4], l_hi[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int col = 32 * hc + 8 * i + 2 * t;
+        l_lo[i] = unpack_bf16(lds32(swz_pair_addr(dl_tile, BT, r_lo, col)));
+        l_hi[i] = unpack_bf16(lds32(swz_pair_addr(dl_tile, BT, r_hi, col)));
+        if (has_do) {
+          const uint32_t a_lo = swz_pair_addr(do_tile, BT, r_lo, col), a_hi = swz_pair_addr(do_tile, BT, r_hi, col);
+          const float2 d_lo = unpack_bf16(lds32(a_lo)), d_hi = unpack_bf16(lds32(a_hi));
+          sts32(a_lo, pack_bf16(d_lo.x * q_lo, d_lo.y * q_lo));
+          sts32(a_hi, pack_bf16(d_hi.x * q_hi, d_hi.y * q_hi));
+        }
+      }
+      if (!tc5::mbar_wait(v_ready, ic & 1)) { failed = true; break; }
+      tc5::fence_after_sync();
+      float acc[16];
+      tc5::tmem_ld_16x256b_x4(TM_V + s_lane + 32 * hc, acc);
+      tc5::tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int col = 32 * hc + 8 * i + 2 * t;
+        const float v00 = ok_lo ? acc[4 * i] * e_lo + l_lo[i].x : 0.f, v01 = ok_lo ? acc[4 * i + 1] * e_lo + l_lo[i].y : 0.f;
+        const float v10 = ok_hi ? acc[4 * i + 2] * e_hi + l_hi[i].x : 0.f, v11 = ok_hi ? acc[4 * i + 3] * e_hi + l_hi[i].y : 0.f;
+        sts32(swz_pair_addr(d2_tile, BT, r_lo, col), pack_bf16(v00, v01));
+        sts32(swz_pair_addr(d2_tile, BT, r_hi, col), pack_bf16(v10, v11));
+      }
+      tc5::fence_async_smem();
+      tc5::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive(vt_ready);
+
+      if (cm.len < BT) {   // ragged chunk: predicated stores of the valid dv2 rows
+        bar_epi_b();
+        __nv_bfloat16* vg = reinterpret_cast<__nv_bfloat16*>(a.dv2) + ((int64_t)cm.row * a.HV + hv) * DV + v0;
+        for (int idx = tid; idx < BT * 8; idx += NEPI) {
+          const int r = idx >> 3, ch = idx & 7;
+          if (r < cm.len) {
+            uint4 val;
+            const uint32_t addr = swz_chunk_addr(d2_tile, BT, r, ch * 8);
+            asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];\n" : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w) : "r"(addr));
+            *reinterpret_cast<uint4*>(vg + (int64_t)r * a.HV * DV + ch * 8) = val;
+          }
         }
       }
     }
-    __syncthreads();
-    store_tile<BT, BV, NTHREADS>(dv2base + ((int64_t)cm.row * a.HV + hv) * DV + v0, (int64_t)a.HV * DV, Lt, cm.len, tid);
 
-    // dS <- 2^gamma_last dS + Q^T (do scale 2^gamma) - W^T dv2
-    const float dec = exp2f(glast);
+    if (!failed && a.dh0 != nullptr) {
+      if (nc > 0) {
+        if (tc5::mbar_wait(s_ready, (nc - 1) & 1)) {
+          tc5::fence_after_sync();
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
+          for (int hf = 0; hf < NH; ++hf) tc5::tmem_ld_16x256b_x4(TM_S + s_lane + ((uint32_t)(16 * hf) << 16) + 32 * hc, Sr[hf]);
+          tc5::tmem_ld_wait();
+        } else {
+          failed = true;
+        }
+      }
+      float* d0 = a.dh0 + ((int64_t)n * a.HV + hv) * DK * DV;
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
+      for (int hf = 0; hf < NH; ++hf)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) S_[mt][nt][e] *= dec;
-      if (dobase != nullptr)
-        warp_mma<4, BT / 16, AMajor::Trans, BMajor::KN>(S_[mt], Qt + rg * (DK / 4) + mt * 16, S::LDK, Dt + cg * 32,
-                                                        S::LDB, lane);
-      warp_mma<4, BT / 16, AMajor::Trans, BMajor::KN, true>(S_[mt], Wt + rg * (DK / 4) + mt * 16, S::LDK, Lt + cg * 32,
-                                                            S::LDB, lane);
+        for (int i = 0; i < 4; ++i) {
+          const int r = srow0 + 16 * hf + g, col = v0 + 32 * hc + 8 * i + 2 * t;
+          *reinterpret_cast<float2*>(&d0[(int64_t)r * DV + col]) = make_float2(Sr[hf][4 * i], Sr[hf][4 * i + 1]);
+          *reinterpret_cast<float2*>(&d0[(int64_t)(r + 8) * DV + col]) = make_float2(Sr[hf][4 * i + 2], Sr[hf][4 * i + 3]);
+        }
     }
   }
 
-  if (a.dh0 != nullptr) {
-    float* d0 = a.dh0 + ((int64_t)n * a.HV + hv) * DK * DV;
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
-        int r = rg * (DK / 4) + mt * 16 + g;
-        int col = v0 + cg * 32 + nt * 8 + 2 * t;
-        *reinterpret_cast<float2*>(&d0[(int64_t)r * DV + col]) = make_float2(S_[mt][nt][0], S_[mt][nt][1]);
-        *reinterpret_cast<float2*>(&d0[(int64_t)(r + 8) * DV + col]) = make_float2(S_[mt][nt][2], S_[mt][nt][3]);
-      }
-  }
+  if (failed && lane == 0) atomicExch(&g_scan_bwd_timeout, 1);
+  tc5::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc5::tmem_dealloc(tm, 128);
 }
 
-template <int DK, int DV, int BV>
+template <int DK, int DV, int NSTAGE>
 int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
-  using S = ScanBwdSmem<DK, BV>;
-  if (int e = ensure_smem(scan_bwd_kernel<DK, DV, BV>, S::bytes)) return e;
+  using S = ScanBwdSmem<DK, NSTAGE>;
+  static_assert(DV % BV == 0, "value dimension is processed in 64-column slices");
+  if (int e = ensure_smem(scan_bwd_kernel<DK, DV, NSTAGE>, S::bytes)) return e;
+  ScanBwdMaps m;
+  const uint64_t pk = (uint64_t)a.H * DK, pw = (uint64_t)a.HV * DK, pv = (uint64_t)a.HV * DV;
+  int rc = 0;
+  rc |= tma::encode_bf16_panels(&m.q, a.q, a.rows, pk, pk, BT, DK / 64);
+  rc |= tma::encode_bf16_panels(&m.k, a.k, a.rows, pk, pk, BT, DK / 64);
+  rc |= tma::encode_bf16_panels(&m.w, a.w, a.rows, pw, pw, BT, DK / 64);
+  rc |= tma::encode_bf16_2d(&m.dv2, a.dv2, a.rows, pv, pv, BT);
+  if (a.d_o) rc |= tma::encode_bf16_2d(&m.d_o, a.d_o, a.rows, pv, pv, BT); else m.d_o = m.dv2;
+  if (a.dh) rc |= tma::encode_bf16_2d(&m.dh, a.dh, (uint64_t)a.n_chunks * a.HV * DK, DV, DV, DK); else m.dh = m.dv2;
+  if (rc != 0) return set_error(B200GDN_ERR_CUDA, "scan_bwd: cuTensorMapEncodeTiled failed (%d)", rc);
   dim3 grid(DV / BV, a.HV, a.n_seq);
-  scan_bwd_kernel<DK, DV, BV><<<grid, 128 * (BV / 32), S::bytes, st>>>(a);
+  scan_bwd_kernel<DK, DV, NSTAGE><<<grid, NTHREADS, S::bytes, st>>>(a, m);
   return check_launch("scan_bwd");
 }
 
 }  // namespace
 
 int launch_scan_bwd(const b200gdn_chunk_args& a, cudaStream_t st) {
-  if (a.K == 128 && a.V == 128) return launch<128, 128, 64>(a, st);
-  if (a.K == 64 && a.V == 64) return launch<64, 64, 32>(a, st);
+  if (a.K == 128 && a.V == 128) return launch<128, 128, 2>(a, st);
+  if (a.K == 64 && a.V == 64) return launch<64, 64, 3>(a, st);
   return set_error(B200GDN_ERR_UNSUPPORTED, "scan_bwd: K=%d V=%d not built (64/64 and 128/128 are)", a.K, a.V);
 }
 
