@@ -1,107 +1,191 @@
 // Chunk output:  o = scale [ (Q h_c) 2^gamma + tril(Q K^T 2^(gamma_i - gamma_j)) v_new ].
-// Replaces chunk_fwd_kernel_o (fla/ops/common/chunk_o.py:56-153).  One CTA per (chunk, value head);
-// the masked score tile never leaves registers: the accumulator of Q K^T is re-packed as the A operand
-// of the product with v_new.
-#include "gdn_common.cuh"
+// Replaces chunk_fwd_kernel_o (fla/ops/common/chunk_o.py:56-153).  One CTA (4 warps) per (chunk, value
+// head), tcgen05 tensor cores with TMEM accumulators:
+//   load   : one thread issues five TMA copies (Q, K, v_new tiles, the 128 x 128 state snapshot, gamma);
+//   phase 1: P = Q K^T (64 columns of TMEM) and O = Q h (128 columns);
+//            epilogue: P masked and gated -> bf16 operand tile; O rows scaled by 2^gamma_i in place (tcgen05.st);
+//   phase 2: O += P v_new;  epilogue: scale, bf16, one TMA store (plain predicated stores for a ragged chunk).
+// 192 TMEM columns and ~90 KiB of shared memory per CTA: two CTAs per SM overlap each other's phases.
+#include "tc5_tile.cuh"
+#include "tma.cuh"
 
 namespace gdn {
 namespace {
 
 constexpr int NTHREADS = 128;
+__device__ int g_out_timeout = 0;
 
 template <int DK, int DV>
 struct OutSmem {
-  static constexpr int LDK = DK + PAD, LDV = DV + PAD;
-  static constexpr size_t q_off = 0;
-  static constexpr size_t k_off = q_off + sizeof(__nv_bfloat16) * BT * LDK;
-  static constexpr size_t v_off = k_off + sizeof(__nv_bfloat16) * BT * LDK;
-  static constexpr size_t h_off = v_off + sizeof(__nv_bfloat16) * BT * LDV;
-  static constexpr size_t g_off = h_off + sizeof(__nv_bfloat16) * DK * LDV;
-  static constexpr size_t bytes = g_off + sizeof(float) * BT;
-  static_assert(2 * BT * LDK >= BT * LDV, "output staging fits in the q/k tiles");
+  static constexpr size_t o_q = 0;                       // Q; later the output staging tile
+  static constexpr size_t o_k = o_q + (BT * DK * 2 > BT * DV * 2 ? BT * DK * 2 : BT * DV * 2);
+  static constexpr size_t o_v = o_k + BT * DK * 2;
+  static constexpr size_t o_h = o_v + BT * DV * 2;
+  static constexpr size_t o_p = o_h + DK * DV * 2;
+  static constexpr size_t o_vec = o_p + BT * 128;
+  static constexpr size_t bytes = o_vec + BT * 4 + 64 + 1024;
+};
+
+struct OutMaps {
+  CUtensorMap q, k, vn, h, o;
 };
 
 template <int DK, int DV>
-__global__ void __launch_bounds__(NTHREADS) out_fwd_kernel(const b200gdn_chunk_args a) {
+__global__ void __launch_bounds__(NTHREADS) out_fwd_kernel(const b200gdn_chunk_args a, const __grid_constant__ OutMaps maps) {
   using S = OutSmem<DK, DV>;
-  extern __shared__ __align__(16) unsigned char smem[];
-  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem + S::q_off);
-  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem + S::k_off);
-  __nv_bfloat16* Vn = reinterpret_cast<__nv_bfloat16*>(smem + S::v_off);
-  __nv_bfloat16* Hs = reinterpret_cast<__nv_bfloat16*>(smem + S::h_off);
-  float* gs = reinterpret_cast<float*>(smem + S::g_off);
-  __nv_bfloat16* stage = Qs;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* Qs = smem + S::o_q;
+  unsigned char* Ks = smem + S::o_k;
+  unsigned char* Vn = smem + S::o_v;
+  unsigned char* Hs = smem + S::o_h;
+  unsigned char* Ps = smem + S::o_p;
+  float* gs = reinterpret_cast<float*>(smem + S::o_vec);
+  uint64_t* bar_ld = reinterpret_cast<uint64_t*>(gs + BT);
+  uint64_t* bar_mma = bar_ld + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mma + 1);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int c = blockIdx.x, hv = blockIdx.y;
   const int G = a.HV / a.H, hq = hv / G;
   const ChunkMeta cm = load_chunk_meta(a.chunk_meta, c);
-  const int64_t row0 = cm.row;
-
-  load_tile_async<DK, NTHREADS>(Qs, reinterpret_cast<const __nv_bfloat16*>(a.q) + (row0 * a.H + hq) * DK,
-                                (int64_t)a.H * DK, cm.len, tid);
-  load_tile_async<DK, NTHREADS>(Ks, reinterpret_cast<const __nv_bfloat16*>(a.k) + (row0 * a.H + hq) * DK,
-                                (int64_t)a.H * DK, cm.len, tid);
-  load_tile_async<DV, NTHREADS>(Vn, reinterpret_cast<const __nv_bfloat16*>(a.v_new) + (row0 * a.HV + hv) * DV,
-                                (int64_t)a.HV * DV, cm.len, tid);
-  load_rows_async<DK, DV, NTHREADS>(Hs, reinterpret_cast<const __nv_bfloat16*>(a.h) + ((int64_t)c * a.HV + hv) * DK * DV,
-                                    DV, tid);
-  cp_async_commit();
-  load_gamma(gs, a.gamma, c, a.HV, hv, tid);
-  cp_async_wait<0>();
-  __syncthreads();
-
   const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
-  const float g_lo = gs[r_lo], g_hi = gs[r_hi];
 
-  // P = tril(Q K^T 2^(gamma_i - gamma_j)), kept as A fragments
-  uint32_t pfrag[4][4];
-  {
-    float acc[8][4];
-    zero_acc<8>(acc);
-    warp_mma<8, DK / 16, AMajor::Row, BMajor::NK>(acc, Qs + warp * 16 * S::LDK, S::LDK, Ks, S::LDK, lane);
+  if (warp == 0) tc5::tmem_alloc(tmem_slot, 256);
+  if (tid == 32) {
+    tc5::mbar_init(bar_ld, 1);
+    tc5::mbar_init(bar_mma, 1);
+    tc5::fence_mbar_init();
+  }
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tm = *tmem_slot;
+  const uint32_t TM_P = tm, TM_O = tm + 64;
+  PhaseBarrier ph{bar_mma, 0u, &g_out_timeout};
+  bool failed = false;
+
+  if (tid == 0) {
+    tc5::mbar_expect_tx(bar_ld, (uint32_t)(2 * BT * DK * 2 + BT * DV * 2 + DK * DV * 2 + BT * 4));
+    tma::load_3d(Qs, &maps.q, cm.row, (hq * DK) / 64, bar_ld);
+    tma::load_3d(Ks, &maps.k, cm.row, (hq * DK) / 64, bar_ld);
+    tma::load_3d(Hs, &maps.h, (c * a.HV + hv) * DK, 0, bar_ld);
+    tma::load_3d(Vn, &maps.vn, cm.row, (hv * DV) / 64, bar_ld);
+    tma::load_1d(gs, gamma_ptr(a.gamma, c, a.HV, hv), BT * 4, bar_ld);
+  }
+  if (!tc5::mbar_wait(bar_ld, 0)) failed = true;
+
+  // ---- phase 1: P = Q K^T ; O = Q h
+  if (tid == 0 && !failed) {
+    tc5::fence_after_sync();
+    issue_mma_t<DK / 16>(TM_P, Operand{tc5::smem_addr(Qs), BT, 0}, Operand{tc5::smem_addr(Ks), BT, 0}, 64, 64, 0);
+    issue_mma_t<DK / 16>(TM_O, Operand{tc5::smem_addr(Qs), BT, 0}, Operand{tc5::smem_addr(Hs), DK, 1}, 64, DV, 0);
+    ph.commit();
+  }
+  const float g_lo = gs[r_lo], g_hi = gs[r_hi];
+  if (__syncthreads_or(failed || !ph.wait())) {
+    failed = true;
+  } else {
+    // ---- epilogue 1: P -> bf16 operand tile; O rows scaled by 2^gamma_i in place
+    {
+      float r[2][16];
+      acc_ld32(TM_P, warp, 0, r[0]);
+      acc_ld32(TM_P, warp, 32, r[1]);
+      tc5::tmem_ld_wait();
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
+      for (int b = 0; b < 2; ++b)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        int i = (e & 2) ? r_hi : r_lo;
-        int j = nt * 8 + 2 * t + (e & 1);
-        float gi = (e & 2) ? g_hi : g_lo;
-        acc[nt][e] = (i >= j) ? acc[nt][e] * exp2f(gi - gs[j]) : 0.f;
+        for (int i = 0; i < 4; ++i) {
+          const int j0 = b * 32 + i * 8 + 2 * t;
+          float v[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int ii = (e & 2) ? r_hi : r_lo, jj = j0 + (e & 1);
+            v[e] = (ii >= jj) ? r[b][4 * i + e] * exp2f(((e & 2) ? g_hi : g_lo) - gs[jj]) : 0.f;
+          }
+          *swz_ptr32(Ps, r_lo, j0, BT) = pack_bf16(v[0], v[1]);
+          *swz_ptr32(Ps, r_hi, j0, BT) = pack_bf16(v[2], v[3]);
+        }
+    }
+    {
+      const float e_lo = exp2f(g_lo), e_hi = exp2f(g_hi);
+      float r[DV / 32][16];
+#pragma unroll
+      for (int b = 0; b < DV / 32; ++b) acc_ld32(TM_O, warp, b * 32, r[b]);
+      tc5::tmem_ld_wait();
+#pragma unroll
+      for (int b = 0; b < DV / 32; ++b) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          r[b][4 * i] *= e_lo; r[b][4 * i + 1] *= e_lo; r[b][4 * i + 2] *= e_hi; r[b][4 * i + 3] *= e_hi;
+        }
+        tc5::tmem_st_16x256b_x4(TM_O + ((uint32_t)(warp * 32) << 16) + b * 32, r[b]);
+      }
+      tc5::tmem_st_wait();
+    }
+    tc5::fence_async_smem();
+    tc5::fence_before_sync();
+    __syncthreads();
+
+    // ---- phase 2: O += P v_new
+    if (tid == 0) {
+      tc5::fence_after_sync();
+      issue_mma_t<BT / 16>(TM_O, Operand{tc5::smem_addr(Ps), BT, 0}, Operand{tc5::smem_addr(Vn), BT, 1}, 64, DV, 1);
+      ph.commit();
+    }
+    if (__syncthreads_or(!ph.wait())) {
+      failed = true;
+    } else {
+      // ---- epilogue 2: scale, bf16 -> staging tile (over Q) -> global
+      float r[DV / 32][16];
+#pragma unroll
+      for (int b = 0; b < DV / 32; ++b) acc_ld32(TM_O, warp, b * 32, r[b]);
+      tc5::tmem_ld_wait();
+#pragma unroll
+      for (int b = 0; b < DV / 32; ++b)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int col = b * 32 + i * 8 + 2 * t;
+          *swz_ptr32(Qs, r_lo, col, BT) = pack_bf16(r[b][4 * i] * a.scale, r[b][4 * i + 1] * a.scale);
+          *swz_ptr32(Qs, r_hi, col, BT) = pack_bf16(r[b][4 * i + 2] * a.scale, r[b][4 * i + 3] * a.scale);
+        }
+      tc5::fence_async_smem();
+      tc5::fence_before_sync();
+      __syncthreads();
+      if (cm.len == BT) {
+        if (tid == 0) {
+          tma::store_3d(&maps.o, cm.row, (hv * DV) / 64, Qs);
+          tma::store_commit();
+          tma::store_wait_all<0>();
+        }
+      } else {
+        store_tile_swz<BT, DV, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.o) + ((int64_t)cm.row * a.HV + hv) * DV,
+                                         (int64_t)a.HV * DV, Qs, cm.len, tid);
       }
     }
-    acc_to_afrag<8>(pfrag, acc);
   }
-
-  float o[DV / 8][4];
-  zero_acc<DV / 8>(o);
-  warp_mma<DV / 8, DK / 16, AMajor::Row, BMajor::KN>(o, Qs + warp * 16 * S::LDK, S::LDK, Hs, S::LDV, lane);
-  {
-    const float e_lo = exp2f(g_lo), e_hi = exp2f(g_hi);
-#pragma unroll
-    for (int nt = 0; nt < DV / 8; ++nt) {
-      o[nt][0] *= e_lo; o[nt][1] *= e_lo; o[nt][2] *= e_hi; o[nt][3] *= e_hi;
-    }
-  }
-  warp_mma_ra<DV / 8, 4, BMajor::KN>(o, pfrag, Vn, S::LDV, lane);
-#pragma unroll
-  for (int nt = 0; nt < DV / 8; ++nt) {
-    o[nt][0] *= a.scale; o[nt][1] *= a.scale; o[nt][2] *= a.scale; o[nt][3] *= a.scale;
-  }
-  __syncthreads();  // every warp is done reading Qs/Ks before they become the staging tile
-  acc_to_smem<DV / 8>(stage + warp * 16 * S::LDV, S::LDV, o, lane);
+  if (failed && tid == 0) atomicExch(&g_out_timeout, 1);
+  tc5::fence_before_sync();
   __syncthreads();
-  store_tile<BT, DV, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.o) + (row0 * a.HV + hv) * DV, (int64_t)a.HV * DV, stage,
-                               cm.len, tid);
+  if (warp == 0) tc5::tmem_dealloc(tm, 256);
 }
 
 template <int DK, int DV>
 int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
   using S = OutSmem<DK, DV>;
   if (int e = ensure_smem(out_fwd_kernel<DK, DV>, S::bytes)) return e;
+  OutMaps m;
+  const uint64_t pk = (uint64_t)a.H * DK, pv = (uint64_t)a.HV * DV;
+  int rc = 0;
+  rc |= tma::encode_bf16_panels(&m.q, a.q, a.rows, pk, pk, BT, DK / 64);
+  rc |= tma::encode_bf16_panels(&m.k, a.k, a.rows, pk, pk, BT, DK / 64);
+  rc |= tma::encode_bf16_panels(&m.vn, a.v_new, a.rows, pv, pv, BT, DV / 64);
+  rc |= tma::encode_bf16_panels(&m.h, a.h, (uint64_t)a.n_chunks * a.HV * DK, DV, DV, DK, DV / 64);
+  rc |= tma::encode_bf16_panels(&m.o, a.o, a.rows, pv, pv, BT, DV / 64);
+  if (rc != 0) return set_error(B200GDN_ERR_CUDA, "out_fwd: cuTensorMapEncodeTiled failed (%d)", rc);
   dim3 grid(a.n_chunks, a.HV);
-  out_fwd_kernel<DK, DV><<<grid, NTHREADS, S::bytes, st>>>(a);
+  out_fwd_kernel<DK, DV><<<grid, NTHREADS, S::bytes, st>>>(a, m);
   return check_launch("out_fwd");
 }
 
