@@ -1,93 +1,166 @@
 // Intra-chunk part of the value gradient:
 //     dv_local[j] = sum_{i >= j} scale <k_j, q_i> 2^(gamma_i - gamma_j) do_i
-// Replaces chunk_bwd_kernel_dv_local (fla/ops/common/chunk_o.py:465-540).  One CTA per (chunk, value
-// head); the result is written into the dv2 buffer, which the reverse scan then completes in place.
-#include "gdn_common.cuh"
+// Replaces chunk_bwd_kernel_dv_local (fla/ops/common/chunk_o.py:465-540).  One CTA (4 warps) per (chunk,
+// value head) on tcgen05 tensor cores: TMA brings Q, K, do and gamma; P = Q K^T in TMEM; the masked, gated
+// and scaled P goes to shared memory as bf16 and is used transposed (MN-major) for dv = P^T do; the result
+// leaves through one TMA store into the dv2 buffer, which the reverse scan then completes in place.
+#include "tc5_tile.cuh"
+#include "tma.cuh"
 
 namespace gdn {
 namespace {
 
 constexpr int NTHREADS = 128;
+__device__ int g_dvl_timeout = 0;
 
 template <int DK, int DV>
 struct DvSmem {
-  static constexpr int LDK = DK + PAD, LDV = DV + PAD, LDP = BT + PAD;
-  static constexpr size_t q_off = 0;
-  static constexpr size_t k_off = q_off + sizeof(__nv_bfloat16) * BT * LDK;
-  static constexpr size_t d_off = k_off + sizeof(__nv_bfloat16) * BT * LDK;
-  static constexpr size_t p_off = d_off + sizeof(__nv_bfloat16) * BT * LDV;
-  static constexpr size_t g_off = p_off + sizeof(__nv_bfloat16) * BT * LDP;
-  static constexpr size_t bytes = g_off + sizeof(float) * BT;
-  static_assert(2 * BT * LDK >= BT * LDV, "output staging fits in the q/k tiles");
+  static constexpr size_t o_q = 0;                       // Q; later the output staging tile
+  static constexpr size_t o_k = o_q + (BT * DK * 2 > BT * DV * 2 ? BT * DK * 2 : BT * DV * 2);
+  static constexpr size_t o_d = o_k + BT * DK * 2;
+  static constexpr size_t o_p = o_d + BT * DV * 2;
+  static constexpr size_t o_vec = o_p + BT * 128;
+  static constexpr size_t bytes = o_vec + BT * 4 + 64 + 1024;
+};
+
+struct DvMaps {
+  CUtensorMap q, k, d_o, dv2;
 };
 
 template <int DK, int DV>
-__global__ void __launch_bounds__(NTHREADS) dv_local_kernel(const b200gdn_chunk_args a) {
+__global__ void __launch_bounds__(NTHREADS) dv_local_kernel(const b200gdn_chunk_args a, const __grid_constant__ DvMaps maps) {
   using S = DvSmem<DK, DV>;
-  extern __shared__ __align__(16) unsigned char smem[];
-  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem + S::q_off);
-  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem + S::k_off);
-  __nv_bfloat16* Ds = reinterpret_cast<__nv_bfloat16*>(smem + S::d_off);
-  __nv_bfloat16* Ps = reinterpret_cast<__nv_bfloat16*>(smem + S::p_off);
-  float* gs = reinterpret_cast<float*>(smem + S::g_off);
-  __nv_bfloat16* stage = Qs;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* Qs = smem + S::o_q;
+  unsigned char* Ks = smem + S::o_k;
+  unsigned char* Ds = smem + S::o_d;
+  unsigned char* Ps = smem + S::o_p;
+  float* gs = reinterpret_cast<float*>(smem + S::o_vec);
+  uint64_t* bar_ld = reinterpret_cast<uint64_t*>(gs + BT);
+  uint64_t* bar_mma = bar_ld + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mma + 1);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int c = blockIdx.x, hv = blockIdx.y;
   const int G = a.HV / a.H, hq = hv / G;
   const ChunkMeta cm = load_chunk_meta(a.chunk_meta, c);
-  const int64_t row0 = cm.row;
+  const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
 
-  load_tile_async<DK, NTHREADS>(Qs, reinterpret_cast<const __nv_bfloat16*>(a.q) + (row0 * a.H + hq) * DK,
-                                (int64_t)a.H * DK, cm.len, tid);
-  load_tile_async<DK, NTHREADS>(Ks, reinterpret_cast<const __nv_bfloat16*>(a.k) + (row0 * a.H + hq) * DK,
-                                (int64_t)a.H * DK, cm.len, tid);
-  load_tile_async<DV, NTHREADS>(Ds, reinterpret_cast<const __nv_bfloat16*>(a.d_o) + (row0 * a.HV + hv) * DV,
-                                (int64_t)a.HV * DV, cm.len, tid);
-  cp_async_commit();
-  load_gamma(gs, a.gamma, c, a.HV, hv, tid);
-  cp_async_wait<0>();
+  if (warp == 0) tc5::tmem_alloc(tmem_slot, 256);
+  if (tid == 32) {
+    tc5::mbar_init(bar_ld, 1);
+    tc5::mbar_init(bar_mma, 1);
+    tc5::fence_mbar_init();
+  }
+  tc5::fence_before_sync();
   __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tm = *tmem_slot;
+  const uint32_t TM_P = tm, TM_D = tm + 64;
+  PhaseBarrier ph{bar_mma, 0u, &g_dvl_timeout};
+  bool failed = false;
 
-  // P[i][j] = scale (q_i . k_j) 2^(gamma_i - gamma_j) for i >= j, stored row-major in shared memory
-  {
-    float acc[8][4];
-    zero_acc<8>(acc);
-    warp_mma<8, DK / 16, AMajor::Row, BMajor::NK>(acc, Qs + warp * 16 * S::LDK, S::LDK, Ks, S::LDK, lane);
-    const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
-    const float g_lo = gs[r_lo], g_hi = gs[r_hi];
+  if (tid == 0) {
+    tc5::mbar_expect_tx(bar_ld, (uint32_t)(2 * BT * DK * 2 + BT * DV * 2 + BT * 4));
+    tma::load_3d(Qs, &maps.q, cm.row, (hq * DK) / 64, bar_ld);
+    tma::load_3d(Ks, &maps.k, cm.row, (hq * DK) / 64, bar_ld);
+    tma::load_3d(Ds, &maps.d_o, cm.row, (hv * DV) / 64, bar_ld);
+    tma::load_1d(gs, gamma_ptr(a.gamma, c, a.HV, hv), BT * 4, bar_ld);
+  }
+  if (!tc5::mbar_wait(bar_ld, 0)) failed = true;
+
+  if (tid == 0 && !failed) {
+    tc5::fence_after_sync();
+    issue_mma_t<DK / 16>(TM_P, Operand{tc5::smem_addr(Qs), BT, 0}, Operand{tc5::smem_addr(Ks), BT, 0}, 64, 64, 0);
+    ph.commit();
+  }
+  const float g_lo = gs[r_lo], g_hi = gs[r_hi];
+  if (__syncthreads_or(failed || !ph.wait())) {
+    failed = true;
+  } else {
+    // P[i][j] = scale (q_i . k_j) 2^(gamma_i - gamma_j) for j <= i < len (rows past a ragged chunk's end hold
+    // another sequence's data and must not leak into the columns of valid rows)
+    {
+      float r[2][16];
+      acc_ld32(TM_P, warp, 0, r[0]);
+      acc_ld32(TM_P, warp, 32, r[1]);
+      tc5::tmem_ld_wait();
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
+      for (int b = 0; b < 2; ++b)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        int i = (e & 2) ? r_hi : r_lo;
-        int j = nt * 8 + 2 * t + (e & 1);
-        float gi = (e & 2) ? g_hi : g_lo;
-        acc[nt][e] = (i >= j) ? acc[nt][e] * a.scale * exp2f(gi - gs[j]) : 0.f;
+        for (int i = 0; i < 4; ++i) {
+          const int j0 = b * 32 + i * 8 + 2 * t;
+          float v[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int ii = (e & 2) ? r_hi : r_lo, jj = j0 + (e & 1);
+            v[e] = (ii >= jj && ii < cm.len) ? r[b][4 * i + e] * a.scale * exp2f(((e & 2) ? g_hi : g_lo) - gs[jj]) : 0.f;
+          }
+          *swz_ptr32(Ps, r_lo, j0, BT) = pack_bf16(v[0], v[1]);
+          *swz_ptr32(Ps, r_hi, j0, BT) = pack_bf16(v[2], v[3]);
+        }
+    }
+    tc5::fence_async_smem();
+    tc5::fence_before_sync();
+    __syncthreads();
+    // dv_local = P^T do
+    if (tid == 0) {
+      tc5::fence_after_sync();
+      issue_mma_t<BT / 16>(TM_D, Operand{tc5::smem_addr(Ps), BT, 1}, Operand{tc5::smem_addr(Ds), BT, 1}, 64, DV, 0);
+      ph.commit();
+    }
+    if (__syncthreads_or(!ph.wait())) {
+      failed = true;
+    } else {
+      float r[DV / 32][16];
+#pragma unroll
+      for (int b = 0; b < DV / 32; ++b) acc_ld32(TM_D, warp, b * 32, r[b]);
+      tc5::tmem_ld_wait();
+#pragma unroll
+      for (int b = 0; b < DV / 32; ++b)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int col = b * 32 + i * 8 + 2 * t;
+          *swz_ptr32(Qs, r_lo, col, BT) = pack_bf16(r[b][4 * i], r[b][4 * i + 1]);
+          *swz_ptr32(Qs, r_hi, col, BT) = pack_bf16(r[b][4 * i + 2], r[b][4 * i + 3]);
+        }
+      tc5::fence_async_smem();
+      tc5::fence_before_sync();
+      __syncthreads();
+      if (cm.len == BT) {
+        if (tid == 0) {
+          tma::store_3d(&maps.dv2, cm.row, (hv * DV) / 64, Qs);
+          tma::store_commit();
+          tma::store_wait_all<0>();
+        }
+      } else {
+        store_tile_swz<BT, DV, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.dv2) + ((int64_t)cm.row * a.HV + hv) * DV,
+                                         (int64_t)a.HV * DV, Qs, cm.len, tid);
       }
     }
-    acc_to_smem<8>(Ps + warp * 16 * S::LDP, S::LDP, acc, lane);
   }
+  if (failed && tid == 0) atomicExch(&g_dvl_timeout, 1);
+  tc5::fence_before_sync();
   __syncthreads();
-
-  // dv_local = P^T do   (rows j = warp*16.., contraction over i)
-  float dv[DV / 8][4];
-  zero_acc<DV / 8>(dv);
-  warp_mma<DV / 8, BT / 16, AMajor::Trans, BMajor::KN>(dv, Ps + warp * 16, S::LDP, Ds, S::LDV, lane);
-  __syncthreads();
-  acc_to_smem<DV / 8>(stage + warp * 16 * S::LDV, S::LDV, dv, lane);
-  __syncthreads();
-  store_tile<BT, DV, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.dv2) + (row0 * a.HV + hv) * DV, (int64_t)a.HV * DV,
-                               stage, cm.len, tid);
+  if (warp == 0) tc5::tmem_dealloc(tm, 256);
 }
 
 template <int DK, int DV>
 int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
   using S = DvSmem<DK, DV>;
   if (int e = ensure_smem(dv_local_kernel<DK, DV>, S::bytes)) return e;
+  DvMaps m;
+  const uint64_t pk = (uint64_t)a.H * DK, pv = (uint64_t)a.HV * DV;
+  int rc = 0;
+  rc |= tma::encode_bf16_panels(&m.q, a.q, a.rows, pk, pk, BT, DK / 64);
+  rc |= tma::encode_bf16_panels(&m.k, a.k, a.rows, pk, pk, BT, DK / 64);
+  rc |= tma::encode_bf16_panels(&m.d_o, a.d_o, a.rows, pv, pv, BT, DV / 64);
+  rc |= tma::encode_bf16_panels(&m.dv2, a.dv2, a.rows, pv, pv, BT, DV / 64);
+  if (rc != 0) return set_error(B200GDN_ERR_CUDA, "dv_local: cuTensorMapEncodeTiled failed (%d)", rc);
   dim3 grid(a.n_chunks, a.HV);
-  dv_local_kernel<DK, DV><<<grid, NTHREADS, S::bytes, st>>>(a);
+  dv_local_kernel<DK, DV><<<grid, NTHREADS, S::bytes, st>>>(a, m);
   return check_launch("dv_local");
 }
 
