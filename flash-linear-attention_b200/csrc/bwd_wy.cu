@@ -13,13 +13,18 @@
 //     dg   = reverse cumsum of dG inside the chunk
 // All row scalings are folded into operands and all 128-wide row-dots are replaced by sums over 64x64
 // tiles that exist anyway (dW K^T, dU V^T, K K^T), so the three dk terms accumulate in one TMEM tile.
-// One CTA (4 warps) per (chunk, q/k head); 256 TMEM columns and ~99 KiB shared memory: two CTAs per SM.
+//
+// One CTA of eight warps per (chunk, q/k head).  The epilogues between the five dependent MMA phases are
+// CUDA-core work on 64-row tiles, so they are spread over eight warps (warps w and w+4 share TMEM
+// quadrant w&3 and split the columns); all tiles arrive by TMA issued from one thread.  256 TMEM columns
+// and ~100 KiB of shared memory: two CTAs per SM overlap each other's phases.
 #include "tc5_tile.cuh"
+#include "tma.cuh"
 
 namespace gdn {
 namespace {
 
-constexpr int NTHREADS = 128;
+constexpr int NTHREADS = 256;
 __device__ int g_wy_timeout = 0;
 
 template <int DK, int DV>
@@ -33,7 +38,11 @@ struct WyTcSmem {
   static constexpr size_t o_h = o_ab + BT * 128;       // h [DK][DV]; later dW (BT*DK*2) | dv staging / M2
   static constexpr size_t h_bytes = DK * DV * 2 > BT * DK * 2 + BT * DV * 2 ? DK * DV * 2 : BT * DK * 2 + BT * DV * 2;
   static constexpr size_t o_vec = o_h + h_bytes;
-  static constexpr size_t bytes = o_vec + 4096 + 1024;
+  static constexpr size_t bytes = o_vec + 6144 + 1024;
+};
+
+struct WyMaps {
+  CUtensorMap k, v, du, a, h;
 };
 
 // sum over the 8 row-lanes of a warp (lanes that differ in bits 2..4), result valid in lanes with g == 0
@@ -50,8 +59,9 @@ __device__ __forceinline__ float sum_over_t(float x) {
 }
 
 template <int DK, int DV>
-__global__ void __launch_bounds__(NTHREADS) bwd_wy_kernel(const b200gdn_chunk_args a) {
+__global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk_args a, const __grid_constant__ WyMaps maps) {
   using S = WyTcSmem<DK, DV>;
+  constexpr int KB = DK / 64, VB = DV / 64;   // 32-column blocks of a wide accumulator per warp
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* Ks = smem + S::o_k;
@@ -71,29 +81,32 @@ __global__ void __launch_bounds__(NTHREADS) bwd_wy_kernel(const b200gdn_chunk_ar
   float* eg = bge + BT;
   float* dGin = eg + BT;
   float* dGs = dGin + BT;
-  float* c_kbg = dGs + BT;   // colsum(A . dW K^T)
-  float* c_vb = c_kbg + BT;  // colsum(A . dU V^T)
-  float* c_m2 = c_vb + BT;   // colsum(M2 . K K^T)
-  float* r_mk = c_m2 + BT;   // rowsum(M . K K^T)
-  uint64_t* bar = reinterpret_cast<uint64_t*>(r_mk + BT);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
+  // column sums are reduced over rows: each of the four row-quadrant warps leaves its partial in its own
+  // slot and the consumer adds the four in a fixed order (no atomics: results are bit-reproducible)
+  float* c_kbg = dGs + BT;       // [4][64] colsum(A . dW K^T)
+  float* c_vb = c_kbg + 4 * BT;  // [4][64] colsum(A . dU V^T)
+  float* c_m2 = c_vb + 4 * BT;   // [4][64] colsum(M2 . K K^T)
+  float* r_mk = c_m2 + 4 * BT;   // rowsum(M . K K^T), two column halves
+  uint64_t* bar = reinterpret_cast<uint64_t*>(r_mk + 2 * BT);
+  uint64_t* bar_ld = bar + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_ld + 1);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int q = warp & 3, hc = warp >> 2;
   const int g = lane >> 2, t = lane & 3;
   const int c = blockIdx.x, hq = blockIdx.y;
   const int G = a.HV / a.H;
   const ChunkMeta cm = load_chunk_meta(a.chunk_meta, c);
   const int64_t row0 = cm.row;
-  const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
+  const int r_lo = q * 16 + g, r_hi = r_lo + 8;
+  const int cs = hc * 32;   // this warp's 32 columns of a 64-column tile
 
   if (warp == 0) tc5::tmem_alloc(tmem_slot, 256);
-  if (tid == 0) {
+  if (tid == 32) {
     tc5::mbar_init(bar, 1);
+    tc5::mbar_init(bar_ld, 1);
     tc5::fence_mbar_init();
   }
-  load_tile_swz<BT, DK, NTHREADS>(Ks, reinterpret_cast<const __nv_bfloat16*>(a.k) + (row0 * a.H + hq) * DK, (int64_t)a.H * DK,
-                                  cm.len, tid);
-  cp_async_commit();
   tc5::fence_before_sync();
   __syncthreads();
   tc5::fence_after_sync();
@@ -115,26 +128,29 @@ __global__ void __launch_bounds__(NTHREADS) bwd_wy_kernel(const b200gdn_chunk_ar
   for (int gi = 0; gi < G && !failed; ++gi) {
     const int hv = hq * G + gi;
     const bool last = gi == G - 1;
-    __syncthreads();
-    load_tile_swz<BT, DV, NTHREADS>(Vs, reinterpret_cast<const __nv_bfloat16*>(a.v) + (row0 * a.HV + hv) * DV,
-                                    (int64_t)a.HV * DV, cm.len, tid);
-    load_tile_swz<BT, DV, NTHREADS>(dUs, reinterpret_cast<const __nv_bfloat16*>(a.dv2) + (row0 * a.HV + hv) * DV,
-                                    (int64_t)a.HV * DV, cm.len, tid);
-    load_tile_swz<BT, BT, NTHREADS>(As, reinterpret_cast<const __nv_bfloat16*>(a.A) + (row0 * a.HV + hv) * BT,
-                                    (int64_t)a.HV * BT, cm.len, tid);
-    load_tile_swz<DK, DV, NTHREADS>(Hs, reinterpret_cast<const __nv_bfloat16*>(a.h) + ((int64_t)c * a.HV + hv) * DK * DV, DV, DK,
-                                    tid);
-    cp_async_commit();
-    load_gamma(gs, a.gamma, c, a.HV, hv, tid);
+    __syncthreads();   // previous head fully consumed
+    if (tid == 0) {
+      const uint32_t tx = (uint32_t)((gi == 0 ? BT * DK * 2 : 0) + 2 * BT * DV * 2 + BT * 128 + DK * DV * 2 + BT * 4);
+      tc5::mbar_expect_tx(bar_ld, tx);
+      if (gi == 0) tma::load_3d(Ks, &maps.k, cm.row, (hq * DK) / 64, bar_ld);
+      tma::load_3d(dUs, &maps.du, cm.row, (hv * DV) / 64, bar_ld);
+      tma::load_3d(Hs, &maps.h, (c * a.HV + hv) * DK, 0, bar_ld);
+      tma::load_3d(Vs, &maps.v, cm.row, (hv * DV) / 64, bar_ld);
+      tma::load_2d(As, &maps.a, hv * BT, cm.row, bar_ld);
+      tma::load_1d(gs, gamma_ptr(a.gamma, c, a.HV, hv), BT * 4, bar_ld);
+    }
     if (tid < BT) {
       const bool ok = tid < cm.len;
       bet[tid] = ok ? a.beta[(row0 + tid) * a.HV + hv] : 0.f;
       dGin[tid] = ok ? a.dG[(row0 + tid) * a.HV + hv] : 0.f;
-      c_kbg[tid] = 0.f;
-      c_vb[tid] = 0.f;
-      c_m2[tid] = 0.f;
     }
-    cp_async_wait<0>();
+    if (!tc5::mbar_wait(bar_ld, gi & 1)) failed = true;
+    if (cm.len < BT) {   // ragged chunk: the extra rows of the boxes belong to the next sequence
+      if (gi == 0) zero_tail_rows<BT, DK>(Ks, cm.len, tid, NTHREADS);
+      zero_tail_rows<BT, DV>(Vs, cm.len, tid, NTHREADS);
+      zero_tail_rows<BT, DV>(dUs, cm.len, tid, NTHREADS);
+      zero_tail_rows<BT, BT>(As, cm.len, tid, NTHREADS);
+    }
     __syncthreads();
     if (tid < BT) {
       const float e = exp2f(gs[tid]);
@@ -149,14 +165,14 @@ __global__ void __launch_bounds__(NTHREADS) bwd_wy_kernel(const b200gdn_chunk_ar
       *swz_ptr32(Abs, i, j, BT) = pack_bf16(x.x * bge[j], x.y * bge[j + 1]);
     }
     tc5::fence_async_smem();
-    __syncthreads();
+    if (__syncthreads_or(failed)) { failed = true; break; }
 
     // ---- phase 1: dW = -dU h^T | dA2 = dU V^T | KK = K K^T
     if (tid == 0) {
       tc5::fence_after_sync();
-      issue_mma(TM_BIG, opdU_k, Operand{tc5::smem_addr(Hs), DK, 0}, 64, DK, DV / 16, 0, /*neg_a=*/1);
-      issue_mma(TM_S1, opdU_k, Operand{tc5::smem_addr(Vs), BT, 0}, 64, 64, DV / 16, 0);
-      issue_mma(TM_KK, opK_k, opK_k, 64, 64, DK / 16, 0);
+      issue_mma_t<DV / 16>(TM_BIG, opdU_k, Operand{tc5::smem_addr(Hs), DK, 0}, 64, DK, 0, /*neg_a=*/1);
+      issue_mma_t<DV / 16>(TM_S1, opdU_k, Operand{tc5::smem_addr(Vs), BT, 0}, 64, 64, 0);
+      issue_mma_t<DK / 16>(TM_KK, opK_k, opK_k, 64, 64, 0);
       ph.commit();
     }
     const float g_lo = gs[r_lo], g_hi = gs[r_hi];
@@ -165,38 +181,31 @@ __global__ void __launch_bounds__(NTHREADS) bwd_wy_kernel(const b200gdn_chunk_ar
 
     // ---- epilogue 1: dW -> shared (over the h buffer); dA2 -> registers; colsum(A . dA2)
     {
-      float r[DK / 32][16];
+      float r[KB][16];
 #pragma unroll
-      for (int b = 0; b < DK / 32; ++b) acc_ld32(TM_BIG, warp, b * 32, r[b]);
+      for (int b = 0; b < KB; ++b) acc_ld32q(TM_BIG, q, hc * (DK / 2) + b * 32, r[b]);
       tc5::tmem_ld_wait();
 #pragma unroll
-      for (int b = 0; b < DK / 32; ++b) {
+      for (int b = 0; b < KB; ++b)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int col = b * 32 + i * 8 + 2 * t;
+          const int col = hc * (DK / 2) + b * 32 + i * 8 + 2 * t;
           *swz_ptr32(dWs, r_lo, col, BT) = pack_bf16(r[b][4 * i], r[b][4 * i + 1]);
           *swz_ptr32(dWs, r_hi, col, BT) = pack_bf16(r[b][4 * i + 2], r[b][4 * i + 3]);
         }
-      }
     }
-    float dA2[2][16];
-#pragma unroll
-    for (int b = 0; b < 2; ++b) {
-      acc_ld32(TM_S1, warp, b * 32, dA2[b]);
-    }
+    float dA2[16];
+    acc_ld32q(TM_S1, q, cs, dA2);
     tc5::tmem_ld_wait();
 #pragma unroll
-    for (int b = 0; b < 2; ++b) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int col = b * 32 + i * 8 + 2 * t;
-        const float2 al = swz_ld2(As, r_lo, col, BT), ah = swz_ld2(As, r_hi, col, BT);
-        float s0 = sum_over_g(al.x * dA2[b][4 * i] + ah.x * dA2[b][4 * i + 2]);
-        float s1 = sum_over_g(al.y * dA2[b][4 * i + 1] + ah.y * dA2[b][4 * i + 3]);
-        if (g == 0) {
-          atomicAdd(&c_vb[col], s0);
-          atomicAdd(&c_vb[col + 1], s1);
-        }
+    for (int i = 0; i < 4; ++i) {
+      const int col = cs + i * 8 + 2 * t;
+      const float2 al = swz_ld2(As, r_lo, col, BT), ah = swz_ld2(As, r_hi, col, BT);
+      const float s0 = sum_over_g(al.x * dA2[4 * i] + ah.x * dA2[4 * i + 2]);
+      const float s1 = sum_over_g(al.y * dA2[4 * i + 1] + ah.y * dA2[4 * i + 3]);
+      if (g == 0) {
+        c_vb[q * BT + col] = s0;
+        c_vb[q * BT + col + 1] = s1;
       }
     }
     tc5::fence_async_smem();
@@ -206,52 +215,47 @@ __global__ void __launch_bounds__(NTHREADS) bwd_wy_kernel(const b200gdn_chunk_ar
     // ---- phase 2: dA1 = dW K^T | dVb = A^T dU
     if (tid == 0) {
       tc5::fence_after_sync();
-      issue_mma(TM_S1, opdW_k, opK_k, 64, 64, DK / 16, 0);
-      issue_mma(TM_BIG, opA_mn, opdU_mn, 64, DV, 4, 0);
+      issue_mma_t<DK / 16>(TM_S1, opdW_k, opK_k, 64, 64, 0);
+      issue_mma_t<BT / 16>(TM_BIG, opA_mn, opdU_mn, 64, DV, 0);
       ph.commit();
     }
     if (__syncthreads_or(!ph.wait())) { failed = true; break; }
 
     // ---- epilogue 2: dA -> shared (over V); colsum(A . dA1); dv = dVb beta -> global
-#pragma unroll
-    for (int b = 0; b < 2; ++b) {
+    {
       float r[16];
-      acc_ld32(TM_S1, warp, b * 32, r);
+      acc_ld32q(TM_S1, q, cs, r);
+      float rv[VB][16];
+#pragma unroll
+      for (int b = 0; b < VB; ++b) acc_ld32q(TM_BIG, q, hc * (DV / 2) + b * 32, rv[b]);
       tc5::tmem_ld_wait();
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int col = b * 32 + i * 8 + 2 * t;
+        const int col = cs + i * 8 + 2 * t;
         const float2 al = swz_ld2(As, r_lo, col, BT), ah = swz_ld2(As, r_hi, col, BT);
-        float s0 = sum_over_g(al.x * r[4 * i] + ah.x * r[4 * i + 2]);
-        float s1 = sum_over_g(al.y * r[4 * i + 1] + ah.y * r[4 * i + 3]);
+        const float s0 = sum_over_g(al.x * r[4 * i] + ah.x * r[4 * i + 2]);
+        const float s1 = sum_over_g(al.y * r[4 * i + 1] + ah.y * r[4 * i + 3]);
         if (g == 0) {
-          atomicAdd(&c_kbg[col], s0);
-          atomicAdd(&c_kbg[col + 1], s1);
+          c_kbg[q * BT + col] = s0;
+          c_kbg[q * BT + col + 1] = s1;
         }
         float v[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int ii = (e & 2) ? r_hi : r_lo, jj = col + (e & 1);
-          v[e] = (ii > jj) ? r[4 * i + e] * bge[jj] + dA2[b][4 * i + e] * bet[jj] : 0.f;
+          v[e] = (ii > jj) ? r[4 * i + e] * bge[jj] + dA2[4 * i + e] * bet[jj] : 0.f;
         }
         *swz_ptr32(dAs, r_lo, col, BT) = pack_bf16(v[0], v[1]);
         *swz_ptr32(dAs, r_hi, col, BT) = pack_bf16(v[2], v[3]);
       }
-    }
-    {
-      float r[DV / 32][16];
 #pragma unroll
-      for (int b = 0; b < DV / 32; ++b) acc_ld32(TM_BIG, warp, b * 32, r[b]);
-      tc5::tmem_ld_wait();
-#pragma unroll
-      for (int b = 0; b < DV / 32; ++b) {
+      for (int b = 0; b < VB; ++b)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int col = b * 32 + i * 8 + 2 * t;
-          *swz_ptr32(Stg, r_lo, col, BT) = pack_bf16(r[b][4 * i] * b_lo, r[b][4 * i + 1] * b_lo);
-          *swz_ptr32(Stg, r_hi, col, BT) = pack_bf16(r[b][4 * i + 2] * b_hi, r[b][4 * i + 3] * b_hi);
+          const int col = hc * (DV / 2) + b * 32 + i * 8 + 2 * t;
+          *swz_ptr32(Stg, r_lo, col, BT) = pack_bf16(rv[b][4 * i] * b_lo, rv[b][4 * i + 1] * b_lo);
+          *swz_ptr32(Stg, r_hi, col, BT) = pack_bf16(rv[b][4 * i + 2] * b_hi, rv[b][4 * i + 3] * b_hi);
         }
-      }
     }
     tc5::fence_async_smem();
     tc5::fence_before_sync();
@@ -260,8 +264,8 @@ __global__ void __launch_bounds__(NTHREADS) bwd_wy_kernel(const b200gdn_chunk_ar
     // ---- phase 3: Y = dA A^T | dk = (A beta 2^gamma)^T dW
     if (tid == 0) {
       tc5::fence_after_sync();
-      issue_mma(TM_S1, Operand{tc5::smem_addr(dAs), BT, 0}, opA_k, 64, 64, 4, 0);
-      issue_mma(TM_BIG, opAb_mn, opdW_mn, 64, DK, 4, 0);
+      issue_mma_t<BT / 16>(TM_S1, Operand{tc5::smem_addr(dAs), BT, 0}, opA_k, 64, 64, 0);
+      issue_mma_t<BT / 16>(TM_BIG, opAb_mn, opdW_mn, 64, DK, 0);
       ph.commit();
     }
     store_tile_swz<BT, DV, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.dv) + (row0 * a.HV + hv) * DV, (int64_t)a.HV * DV, Stg,
@@ -269,14 +273,13 @@ __global__ void __launch_bounds__(NTHREADS) bwd_wy_kernel(const b200gdn_chunk_ar
     if (__syncthreads_or(!ph.wait())) { failed = true; break; }
 
     // ---- epilogue 3: Y -> shared
-#pragma unroll
-    for (int b = 0; b < 2; ++b) {
+    {
       float r[16];
-      acc_ld32(TM_S1, warp, b * 32, r);
+      acc_ld32q(TM_S1, q, cs, r);
       tc5::tmem_ld_wait();
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int col = b * 32 + i * 8 + 2 * t;
+        const int col = cs + i * 8 + 2 * t;
         *swz_ptr32(Ys, r_lo, col, BT) = pack_bf16(r[4 * i], r[4 * i + 1]);
         *swz_ptr32(Ys, r_hi, col, BT) = pack_bf16(r[4 * i + 2], r[4 * i + 3]);
       }
@@ -288,47 +291,45 @@ __global__ void __launch_bounds__(NTHREADS) bwd_wy_kernel(const b200gdn_chunk_ar
     // ---- phase 4: X = A^T Y
     if (tid == 0) {
       tc5::fence_after_sync();
-      issue_mma(TM_S1, opA_mn, Operand{tc5::smem_addr(Ys), BT, 1}, 64, 64, 4, 0);
+      issue_mma_t<BT / 16>(TM_S1, opA_mn, Operand{tc5::smem_addr(Ys), BT, 1}, 64, 64, 0);
       ph.commit();
     }
     if (__syncthreads_or(!ph.wait())) { failed = true; break; }
 
     // ---- epilogue 4: M, M2 = M beta_i -> shared; rowsum(M . KK), colsum(M2 . KK)
-    float rmk_lo = 0.f, rmk_hi = 0.f;
-#pragma unroll
-    for (int b = 0; b < 2; ++b) {
+    {
       float r[16], kk[16];
-      acc_ld32(TM_S1, warp, b * 32, r);
-      acc_ld32(TM_KK, warp, b * 32, kk);
+      acc_ld32q(TM_S1, q, cs, r);
+      acc_ld32q(TM_KK, q, cs, kk);
       tc5::tmem_ld_wait();
+      float rmk_lo = 0.f, rmk_hi = 0.f;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int col = b * 32 + i * 8 + 2 * t;
+        const int col = cs + i * 8 + 2 * t;
         float m[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int ii = (e & 2) ? r_hi : r_lo, jj = col + (e & 1);
-          const float gi_ = (e & 2) ? g_hi : g_lo;
-          m[e] = (ii > jj) ? -r[4 * i + e] * exp2f(gi_ - gs[jj]) : 0.f;
+          m[e] = (ii > jj) ? -r[4 * i + e] * exp2f(((e & 2) ? g_hi : g_lo) - gs[jj]) : 0.f;
         }
         rmk_lo += m[0] * kk[4 * i] + m[1] * kk[4 * i + 1];
         rmk_hi += m[2] * kk[4 * i + 2] + m[3] * kk[4 * i + 3];
         const float m20 = m[0] * b_lo, m21 = m[1] * b_lo, m22 = m[2] * b_hi, m23 = m[3] * b_hi;
-        float s0 = sum_over_g(m20 * kk[4 * i] + m22 * kk[4 * i + 2]);
-        float s1 = sum_over_g(m21 * kk[4 * i + 1] + m23 * kk[4 * i + 3]);
+        const float s0 = sum_over_g(m20 * kk[4 * i] + m22 * kk[4 * i + 2]);
+        const float s1 = sum_over_g(m21 * kk[4 * i + 1] + m23 * kk[4 * i + 3]);
         if (g == 0) {
-          atomicAdd(&c_m2[col], s0);
-          atomicAdd(&c_m2[col + 1], s1);
+          c_m2[q * BT + col] = s0;
+          c_m2[q * BT + col + 1] = s1;
         }
         *swz_ptr32(M2s, r_lo, col, BT) = pack_bf16(m20, m21);
         *swz_ptr32(M2s, r_hi, col, BT) = pack_bf16(m22, m23);
       }
-    }
-    rmk_lo = sum_over_t(rmk_lo);
-    rmk_hi = sum_over_t(rmk_hi);
-    if (t == 0) {
-      r_mk[r_lo] = rmk_lo;
-      r_mk[r_hi] = rmk_hi;
+      rmk_lo = sum_over_t(rmk_lo);
+      rmk_hi = sum_over_t(rmk_hi);
+      if (t == 0) {
+        r_mk[hc * BT + r_lo] = rmk_lo;
+        r_mk[hc * BT + r_hi] = rmk_hi;
+      }
     }
     tc5::fence_async_smem();
     tc5::fence_before_sync();
@@ -337,41 +338,47 @@ __global__ void __launch_bounds__(NTHREADS) bwd_wy_kernel(const b200gdn_chunk_ar
     // ---- phase 5: dk += M2 K + M2^T K
     if (tid == 0) {
       tc5::fence_after_sync();
-      issue_mma(TM_BIG, Operand{tc5::smem_addr(M2s), BT, 0}, opK_mn, 64, DK, 4, 1);
-      issue_mma(TM_BIG, Operand{tc5::smem_addr(M2s), BT, 1}, opK_mn, 64, DK, 4, 1);
+      issue_mma_t<BT / 16>(TM_BIG, Operand{tc5::smem_addr(M2s), BT, 0}, opK_mn, 64, DK, 1);
+      issue_mma_t<BT / 16>(TM_BIG, Operand{tc5::smem_addr(M2s), BT, 1}, opK_mn, 64, DK, 1);
       ph.commit();
     }
     // the dq/dk kernel's part of dk: fetched now so that its latency hides behind the MMAs
-    float* const dkbuf = a.dk_part + (row0 * a.H + hq) * DK;
+    float* const dkbuf = a.dk_part + (row0 * a.H + hq) * DK + hc * (DK / 2);
     const int64_t dkstride = (int64_t)a.H * DK;
-    float2 part[DK / 8][2];
+    float2 part[KB * 4][2];
 #pragma unroll
-    for (int n8 = 0; n8 < DK / 8; ++n8) {
+    for (int n8 = 0; n8 < KB * 4; ++n8) {
       const int col = n8 * 8 + 2 * t;
       part[n8][0] = r_lo < cm.len ? *reinterpret_cast<const float2*>(dkbuf + r_lo * dkstride + col) : make_float2(0.f, 0.f);
       part[n8][1] = r_hi < cm.len ? *reinterpret_cast<const float2*>(dkbuf + r_hi * dkstride + col) : make_float2(0.f, 0.f);
     }
-    // gate / beta gradients while the MMAs run
+    // gate / beta gradients while the MMAs run: dG per row, then the reverse cumsum as a two-warp suffix scan
     if (tid < BT) {
       const int i = tid;
-      dGs[i] = c_kbg[i] * bge[i] + bet[i] * r_mk[i] - c_m2[i] + dGin[i];
-      if (i < cm.len) a.dbeta[(row0 + i) * a.HV + hv] = c_kbg[i] * eg[i] + c_vb[i] + r_mk[i];
+      const float rmk = r_mk[i] + r_mk[BT + i];
+      const float ckbg = (c_kbg[i] + c_kbg[BT + i]) + (c_kbg[2 * BT + i] + c_kbg[3 * BT + i]);
+      const float cvb = (c_vb[i] + c_vb[BT + i]) + (c_vb[2 * BT + i] + c_vb[3 * BT + i]);
+      const float cm2 = (c_m2[i] + c_m2[BT + i]) + (c_m2[2 * BT + i] + c_m2[3 * BT + i]);
+      float x = ckbg * bge[i] + bet[i] * rmk - cm2 + dGin[i];
+      if (i < cm.len) a.dbeta[(row0 + i) * a.HV + hv] = ckbg * eg[i] + cvb + rmk;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float y = __shfl_down_sync(0xffffffffu, x, o);
+        if (lane + o < 32) x += y;
+      }
+      dGs[i] = x;   // suffix sum inside the warp
     }
     if (__syncthreads_or(!ph.wait())) { failed = true; break; }
-    if (tid < cm.len) {
-      float s = 0.f;
-      for (int j = BT - 1; j >= tid; --j) s += dGs[j];
-      a.dg[(row0 + tid) * a.HV + hv] = s;
-    }
+    if (tid < cm.len) a.dg[(row0 + tid) * a.HV + hv] = dGs[tid] + (tid < 32 ? dGs[32] : 0.f);
 
     // ---- epilogue 5: dk = accumulator + part from the dq/dk kernel (group-accumulated in fp32)
     {
-      float r[DK / 32][16];
+      float r[KB][16];
 #pragma unroll
-      for (int b = 0; b < DK / 32; ++b) acc_ld32(TM_BIG, warp, b * 32, r[b]);
+      for (int b = 0; b < KB; ++b) acc_ld32q(TM_BIG, q, hc * (DK / 2) + b * 32, r[b]);
       tc5::tmem_ld_wait();
 #pragma unroll
-      for (int b = 0; b < DK / 32; ++b) {
+      for (int b = 0; b < KB; ++b)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int n8 = b * 4 + i, col = n8 * 8 + 2 * t;
@@ -381,11 +388,10 @@ __global__ void __launch_bounds__(NTHREADS) bwd_wy_kernel(const b200gdn_chunk_ar
             if (r_lo < cm.len) *reinterpret_cast<float2*>(dkbuf + r_lo * dkstride + col) = make_float2(d0, d1);
             if (r_hi < cm.len) *reinterpret_cast<float2*>(dkbuf + r_hi * dkstride + col) = make_float2(d2, d3);
           } else {
-            *swz_ptr32(dWs, r_lo, col, BT) = pack_bf16(d0, d1);
-            *swz_ptr32(dWs, r_hi, col, BT) = pack_bf16(d2, d3);
+            *swz_ptr32(dWs, r_lo, hc * (DK / 2) + col, BT) = pack_bf16(d0, d1);
+            *swz_ptr32(dWs, r_hi, hc * (DK / 2) + col, BT) = pack_bf16(d2, d3);
           }
         }
-      }
     }
     tc5::fence_before_sync();
     __syncthreads();
@@ -404,8 +410,17 @@ template <int DK, int DV>
 int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
   using S = WyTcSmem<DK, DV>;
   if (int e = ensure_smem(bwd_wy_kernel<DK, DV>, S::bytes)) return e;
+  WyMaps m;
+  const uint64_t pk = (uint64_t)a.H * DK, pv = (uint64_t)a.HV * DV;
+  int rc = 0;
+  rc |= tma::encode_bf16_panels(&m.k, a.k, a.rows, pk, pk, BT, DK / 64);
+  rc |= tma::encode_bf16_panels(&m.v, a.v, a.rows, pv, pv, BT, DV / 64);
+  rc |= tma::encode_bf16_panels(&m.du, a.dv2, a.rows, pv, pv, BT, DV / 64);
+  rc |= tma::encode_bf16_2d(&m.a, a.A, a.rows, (uint64_t)a.HV * BT, (uint64_t)a.HV * BT, BT);
+  rc |= tma::encode_bf16_panels(&m.h, a.h, (uint64_t)a.n_chunks * a.HV * DK, DV, DV, DK, DV / 64);
+  if (rc != 0) return set_error(B200GDN_ERR_CUDA, "bwd_wy: cuTensorMapEncodeTiled failed (%d)", rc);
   dim3 grid(a.n_chunks, a.H);
-  bwd_wy_kernel<DK, DV><<<grid, NTHREADS, S::bytes, st>>>(a);
+  bwd_wy_kernel<DK, DV><<<grid, NTHREADS, S::bytes, st>>>(a, m);
   return check_launch("bwd_wy");
 }
 

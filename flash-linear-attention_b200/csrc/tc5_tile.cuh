@@ -51,6 +51,18 @@ __device__ __forceinline__ float2 swz_ld2(const unsigned char* tile, int row, in
   return unpack_bf16(*reinterpret_cast<const uint32_t*>(tile + tc5::swz_offset(row, col, rows)));
 }
 
+// Zero rows [valid, ROWS) of a swizzled [ROWS][COLS] tile (a ragged last chunk arrives by TMA as a full box
+// whose extra rows belong to the next sequence).  The caller fences and synchronises afterwards.
+template <int ROWS, int COLS>
+__device__ __forceinline__ void zero_tail_rows(unsigned char* tile, int valid, int tid, int nthreads) {
+  constexpr int CPR = COLS / 8;
+  const int total = (ROWS - valid) * CPR;
+  for (int idx = tid; idx < total; idx += nthreads) {
+    const int r = valid + idx / CPR, c = idx % CPR;
+    *reinterpret_cast<uint4*>(tile + (c >> 3) * (ROWS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+  }
+}
+
 // ---- MMA issue (one thread) -----------------------------------------------------------------------------
 // Operand descriptions.  A tile is stored [rows][cols]; as a K-major operand its MN index runs over rows
 // and the contraction over columns; as an MN-major operand the MN index runs over columns and the
@@ -93,6 +105,12 @@ __device__ __forceinline__ void issue_mma(uint32_t d_tmem, const Operand& a, con
 // n-tile i (columns c0 + 8i ..), e = {row g col 2t, row g col 2t+1, row g+8 col 2t, row g+8 col 2t+1}.
 __device__ __forceinline__ void acc_ld32(uint32_t tmem_acc, int warp, int c0, float (&r)[16]) {
   tc5::tmem_ld_16x256b_x4(tmem_acc + ((uint32_t)(warp * 32) << 16) + c0, r);
+}
+
+// The same block for a CTA of eight warps: warps w and w + 4 share TMEM quadrant w & 3 and split the
+// columns, `c0` is relative to the warp's own half.
+__device__ __forceinline__ void acc_ld32q(uint32_t tmem_acc, int quad, int c0, float (&r)[16]) {
+  tc5::tmem_ld_16x256b_x4(tmem_acc + ((uint32_t)(quad * 32) << 16) + c0, r);
 }
 
 // One phase boundary: the issuing thread commits, everybody waits for the MMAs (bounded).
