@@ -1,22 +1,24 @@
 // Chunk-local gradients of q and k and of the cumulative gate, on tcgen05 tensor cores with TMEM
 // accumulators (replaces chunk_bwd_kernel_dqkwg of fla/ops/common/chunk_o.py:172-342 except for dw,
-// which the WY-backward kernel now forms itself so that it never touches HBM):
+// which the WY-backward kernel forms itself so that it never touches HBM):
 //     dP   = tril(do v_new^T 2^(gamma_i - gamma_j)) scale
 //     dq   = (do scale 2^gamma) h^T + dP k
 //     dk   = dP^T q + (v_new 2^(gamma_last - gamma)) dh^T
 //     dG_i = <dq_i,q_i> - <dk_i,k_i>  (+ at the last valid row: 2^gamma_last <h,dh> + sum_i <dk_state_i,k_i>)
 //
-// One CTA (4 warps) per (chunk, q/k head), looping over the value heads of the group.  Operand tiles sit
-// in shared memory in the 128-byte-swizzled layout; one thread issues tcgen05.mma; the 64-row
-// accumulators (dq | dk_state, dP, dk_intra) share 256 TMEM columns, so two CTAs fit on an SM and one
-// CTA's epilogue overlaps the other's MMAs.  h and dh are streamed in 64-column panels through one
-// buffer pair, which keeps the CTA at ~106 KiB of shared memory.
+// One CTA of eight warps per (chunk, q/k head), looping over the value heads of the group.  All tiles
+// arrive by TMA (one issuing thread) in the 128-byte-swizzled layout; one thread issues tcgen05.mma; the
+// 64-row accumulators (dq | dk_state, dP, dk_intra) share 256 TMEM columns; the epilogues are spread over
+// eight warps (warps w and w+4 share TMEM quadrant w&3 and split the columns).  h and dh are streamed in
+// 64-column panels through one buffer pair, which keeps the CTA at ~106 KiB of shared memory, so two CTAs
+// per SM overlap each other's phases.
 #include "tc5_tile.cuh"
+#include "tma.cuh"
 
 namespace gdn {
 namespace {
 
-constexpr int NTHREADS = 128;
+constexpr int NTHREADS = 256;
 __device__ int g_dqk_timeout = 0;
 
 template <int DK, int DV>
@@ -29,14 +31,19 @@ struct DqkSmem {
   static constexpr size_t o_dhp = o_hp + DK * 128;       // dh panel [DK][64]
   static constexpr size_t o_p = o_dhp + DK * 128;        // dP~ [64][64]
   static constexpr size_t o_vec = o_p + BT * 128;
-  static constexpr size_t bytes = o_vec + 1024 + 1024;   // + vectors + alignment slack
+  static constexpr size_t bytes = o_vec + 2048 + 1024;   // + vectors + alignment slack
   static_assert(2 * DK * 128 >= BT * DK * 2, "staging fits in the panel buffers");
 };
 
+struct DqkMaps {
+  CUtensorMap q, k, d_o, vn, h, dh;
+};
+
 template <int DK, int DV>
-__global__ void __launch_bounds__(NTHREADS) bwd_dqk_kernel(const b200gdn_chunk_args a) {
+__global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chunk_args a, const __grid_constant__ DqkMaps maps) {
   using S = DqkSmem<DK, DV>;
-  constexpr int NP = DV / 64;  // value panels
+  constexpr int NP = DV / 64;   // value panels
+  constexpr int KB = DK / 64;   // 32-column blocks of a K-wide accumulator per warp
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* Do = smem + S::o_do;
@@ -47,35 +54,36 @@ __global__ void __launch_bounds__(NTHREADS) bwd_dqk_kernel(const b200gdn_chunk_a
   unsigned char* dHp = smem + S::o_dhp;
   unsigned char* Ps = smem + S::o_p;
   float* gs = reinterpret_cast<float*>(smem + S::o_vec);
-  float* dGs = gs + BT;
-  float* red = dGs + BT;                                   // [0..3] <h,dh>, [4..7] sum rs
+  float* rqs = gs + BT;          // [2][64] row-dot partials <dq, q> of the two column halves
+  float* rks = rqs + 2 * BT;     // [2][64] <dk, k>
+  float* red = rks + 2 * BT;     // [0..7] <h,dh> per warp, [8..15] sum of <dk_state, k> per warp
   uint64_t* bar = reinterpret_cast<uint64_t*>(red + 16);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
+  uint64_t* bar_ld = bar + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_ld + 1);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int q = warp & 3, hc = warp >> 2;
   const int g = lane >> 2, t = lane & 3;
   const int c = blockIdx.x, hq = blockIdx.y;
   const int G = a.HV / a.H;
   const ChunkMeta cm = load_chunk_meta(a.chunk_meta, c);
   const int64_t row0 = cm.row;
-  const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
+  const int r_lo = q * 16 + g, r_hi = r_lo + 8;
+  const int cs = hc * 32, ck = hc * (DK / 2);
 
   if (warp == 0) tc5::tmem_alloc(tmem_slot, 256);
-  if (tid == 0) {
+  if (tid == 32) {
     tc5::mbar_init(bar, 1);
+    tc5::mbar_init(bar_ld, 1);
     tc5::fence_mbar_init();
   }
-  load_tile_swz<BT, DK, NTHREADS>(Qs, reinterpret_cast<const __nv_bfloat16*>(a.q) + (row0 * a.H + hq) * DK, (int64_t)a.H * DK,
-                                  cm.len, tid);
-  load_tile_swz<BT, DK, NTHREADS>(Ks, reinterpret_cast<const __nv_bfloat16*>(a.k) + (row0 * a.H + hq) * DK, (int64_t)a.H * DK,
-                                  cm.len, tid);
-  cp_async_commit();
   tc5::fence_before_sync();
   __syncthreads();
   tc5::fence_after_sync();
   const uint32_t tm = *tmem_slot;
   const uint32_t TM_DQ = tm, TM_DKS = tm + 128, TM_DP = tm + 128, TM_DKI = tm;
   PhaseBarrier ph{bar, 0u, &g_dqk_timeout};
+  uint32_t ld_parity = 0;
   bool failed = false;
 
   const Operand opQ{tc5::smem_addr(Qs), BT, 1};   // B of dP~^T q : (k = token, n = key dim)
@@ -86,25 +94,37 @@ __global__ void __launch_bounds__(NTHREADS) bwd_dqk_kernel(const b200gdn_chunk_a
   for (int gi = 0; gi < G && !failed; ++gi) {
     const int hv = hq * G + gi;
     const bool first = gi == 0, last = gi == G - 1;
-    const __nv_bfloat16* hg = reinterpret_cast<const __nv_bfloat16*>(a.h) + ((int64_t)c * a.HV + hv) * DK * DV;
-    const __nv_bfloat16* dhg = reinterpret_cast<const __nv_bfloat16*>(a.dh) + ((int64_t)c * a.HV + hv) * DK * DV;
-    __syncthreads();  // previous head fully consumed (staging, gs, red)
-    load_tile_swz<BT, DV, NTHREADS>(Do, reinterpret_cast<const __nv_bfloat16*>(a.d_o) + (row0 * a.HV + hv) * DV,
-                                    (int64_t)a.HV * DV, cm.len, tid);
-    load_tile_swz<BT, DV, NTHREADS>(Vn, reinterpret_cast<const __nv_bfloat16*>(a.v_new) + (row0 * a.HV + hv) * DV,
-                                    (int64_t)a.HV * DV, cm.len, tid);
-    load_tile_swz<DK, 64, NTHREADS>(Hp, hg, DV, DK, tid);
-    load_tile_swz<DK, 64, NTHREADS>(dHp, dhg, DV, DK, tid);
-    cp_async_commit();
-    load_gamma(gs, a.gamma, c, a.HV, hv, tid);
-    cp_async_wait<0>();
-    tc5::fence_async_smem();
-    __syncthreads();
+    const int hrow = (c * a.HV + hv) * DK;   // first row of this head's state snapshot in the [.., V] view
+    __syncthreads();  // previous head fully consumed (staging, gs, partials)
+    if (tid == 0) {
+      tc5::mbar_expect_tx(bar_ld, (uint32_t)((first ? 2 * BT * DK * 2 : 0) + 2 * BT * DV * 2 + 2 * DK * 128 + BT * 4));
+      tma::load_3d(Do, &maps.d_o, cm.row, (hv * DV) / 64, bar_ld);
+      tma::load_3d(Vn, &maps.vn, cm.row, (hv * DV) / 64, bar_ld);
+      tma::load_2d(Hp, &maps.h, 0, hrow, bar_ld);
+      tma::load_2d(dHp, &maps.dh, 0, hrow, bar_ld);
+      if (first) {
+        tma::load_3d(Qs, &maps.q, cm.row, (hq * DK) / 64, bar_ld);
+        tma::load_3d(Ks, &maps.k, cm.row, (hq * DK) / 64, bar_ld);
+      }
+      tma::load_1d(gs, gamma_ptr(a.gamma, c, a.HV, hv), BT * 4, bar_ld);
+    }
+    if (!tc5::mbar_wait(bar_ld, ld_parity)) failed = true;
+    ld_parity ^= 1u;
+    if (cm.len < BT) {   // ragged chunk: the extra rows of the boxes belong to the next sequence
+      if (first) {
+        zero_tail_rows<BT, DK>(Qs, cm.len, tid, NTHREADS);
+        zero_tail_rows<BT, DK>(Ks, cm.len, tid, NTHREADS);
+      }
+      zero_tail_rows<BT, DV>(Do, cm.len, tid, NTHREADS);
+      zero_tail_rows<BT, DV>(Vn, cm.len, tid, NTHREADS);
+      tc5::fence_async_smem();
+    }
+    if (__syncthreads_or(failed)) { failed = true; break; }
 
     // ---- phase 1: dP = do v_new^T
     if (tid == 0) {
       tc5::fence_after_sync();
-      issue_mma(TM_DP, Operand{tc5::smem_addr(Do), BT, 0}, Operand{tc5::smem_addr(Vn), BT, 0}, 64, 64, DV / 16, 0);
+      issue_mma_t<DV / 16>(TM_DP, Operand{tc5::smem_addr(Do), BT, 0}, Operand{tc5::smem_addr(Vn), BT, 0}, 64, 64, 0);
       ph.commit();
     }
     const float g_lo = gs[r_lo], g_hi = gs[r_hi], glast = gs[BT - 1];
@@ -126,20 +146,18 @@ __global__ void __launch_bounds__(NTHREADS) bwd_dqk_kernel(const b200gdn_chunk_a
     if (__syncthreads_or(!ph.wait())) { failed = true; break; }
 
     // ---- epilogue 1: dP~ -> shared; rescale do and v_new rows in place
-#pragma unroll
-    for (int b = 0; b < 2; ++b) {
+    {
       float r[16];
-      acc_ld32(TM_DP, warp, b * 32, r);
+      acc_ld32q(TM_DP, q, cs, r);
       tc5::tmem_ld_wait();
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int j0 = b * 32 + i * 8 + 2 * t;
+        const int j0 = cs + i * 8 + 2 * t;
         float v[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int ii = (e & 2) ? r_hi : r_lo, jj = j0 + (e & 1);
-          const float gi_ = (e & 2) ? g_hi : g_lo;
-          v[e] = (ii >= jj) ? r[4 * i + e] * a.scale * exp2f(gi_ - gs[jj]) : 0.f;
+          v[e] = (ii >= jj) ? r[4 * i + e] * a.scale * exp2f(((e & 2) ? g_hi : g_lo) - gs[jj]) : 0.f;
         }
         *swz_ptr32(Ps, r_lo, j0, BT) = pack_bf16(v[0], v[1]);
         *swz_ptr32(Ps, r_hi, j0, BT) = pack_bf16(v[2], v[3]);
@@ -169,19 +187,21 @@ __global__ void __launch_bounds__(NTHREADS) bwd_dqk_kernel(const b200gdn_chunk_a
     // ---- phase 2: dq = do_s h^T + dP~ k ; dk_state = v~ dh^T   (h, dh streamed by 64-column panels)
     for (int p = 0; p < NP && !failed; ++p) {
       if (p > 0) {
-        load_tile_swz<DK, 64, NTHREADS>(Hp, hg + p * 64, DV, DK, tid);
-        load_tile_swz<DK, 64, NTHREADS>(dHp, dhg + p * 64, DV, DK, tid);
-        cp_async_commit();
-        cp_async_wait<0>();
-        tc5::fence_async_smem();
-        __syncthreads();
+        if (tid == 0) {
+          tc5::mbar_expect_tx(bar_ld, 2 * DK * 128);
+          tma::load_2d(Hp, &maps.h, p * 64, hrow, bar_ld);
+          tma::load_2d(dHp, &maps.dh, p * 64, hrow, bar_ld);
+        }
+        if (!tc5::mbar_wait(bar_ld, ld_parity)) failed = true;
+        ld_parity ^= 1u;
+        if (__syncthreads_or(failed)) { failed = true; break; }
       }
       if (tid == 0) {
         tc5::fence_after_sync();
-        issue_mma(TM_DQ, Operand{tc5::smem_addr(Do) + p * BT * 128, BT, 0}, Operand{tc5::smem_addr(Hp), DK, 0}, 64, DK, 4, p > 0);
-        issue_mma(TM_DKS, Operand{tc5::smem_addr(Vn) + p * BT * 128, BT, 0}, Operand{tc5::smem_addr(dHp), DK, 0}, 64, DK, 4,
-                  p > 0);
-        if (p == NP - 1) issue_mma(TM_DQ, opPk, opK, 64, DK, 4, 1);
+        issue_mma_t<4>(TM_DQ, Operand{tc5::smem_addr(Do) + p * BT * 128, BT, 0}, Operand{tc5::smem_addr(Hp), DK, 0}, 64, DK, p > 0);
+        issue_mma_t<4>(TM_DKS, Operand{tc5::smem_addr(Vn) + p * BT * 128, BT, 0}, Operand{tc5::smem_addr(dHp), DK, 0}, 64, DK,
+                       p > 0);
+        if (p == NP - 1) issue_mma_t<4>(TM_DQ, opPk, opK, 64, DK, 1);
         ph.commit();
       }
       if (p > 0) add_hd();
@@ -189,52 +209,58 @@ __global__ void __launch_bounds__(NTHREADS) bwd_dqk_kernel(const b200gdn_chunk_a
     }
     if (failed) break;
 
-    // ---- epilogue 2: dq
-    float rq_lo = 0.f, rq_hi = 0.f;
-    float racc[DK / 32][16];
+    // ---- epilogue 2: dq (this warp's half of the columns)
+    {
+      float racc[KB][16];
 #pragma unroll
-    for (int b = 0; b < DK / 32; ++b) acc_ld32(TM_DQ, warp, b * 32, racc[b]);
-    tc5::tmem_ld_wait();
+      for (int b = 0; b < KB; ++b) acc_ld32q(TM_DQ, q, ck + b * 32, racc[b]);
+      tc5::tmem_ld_wait();
+      float rq_lo = 0.f, rq_hi = 0.f;
 #pragma unroll
-    for (int b = 0; b < DK / 32; ++b) {
-      float (&r)[16] = racc[b];
+      for (int b = 0; b < KB; ++b) {
+        float (&r)[16] = racc[b];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int col = b * 32 + i * 8 + 2 * t;
-        const float2 qa = swz_ld2(Qs, r_lo, col, BT), qb = swz_ld2(Qs, r_hi, col, BT);
-        rq_lo += r[4 * i] * qa.x + r[4 * i + 1] * qa.y;
-        rq_hi += r[4 * i + 2] * qb.x + r[4 * i + 3] * qb.y;
-        if (G > 1) {
-          float* buf = a.dq_acc + (row0 * a.H + hq) * DK;
-          const int64_t stride = (int64_t)a.H * DK;
-          if (r_lo < cm.len) {
-            float2* pp = reinterpret_cast<float2*>(buf + r_lo * stride + col);
-            if (!first) { float2 o = *pp; r[4 * i] += o.x; r[4 * i + 1] += o.y; }
-            if (!last) *pp = make_float2(r[4 * i], r[4 * i + 1]);
+        for (int i = 0; i < 4; ++i) {
+          const int col = ck + b * 32 + i * 8 + 2 * t;
+          const float2 qa = swz_ld2(Qs, r_lo, col, BT), qb = swz_ld2(Qs, r_hi, col, BT);
+          rq_lo += r[4 * i] * qa.x + r[4 * i + 1] * qa.y;
+          rq_hi += r[4 * i + 2] * qb.x + r[4 * i + 3] * qb.y;
+          if (G > 1) {
+            float* buf = a.dq_acc + (row0 * a.H + hq) * DK;
+            const int64_t stride = (int64_t)a.H * DK;
+            if (r_lo < cm.len) {
+              float2* pp = reinterpret_cast<float2*>(buf + r_lo * stride + col);
+              if (!first) { float2 o = *pp; r[4 * i] += o.x; r[4 * i + 1] += o.y; }
+              if (!last) *pp = make_float2(r[4 * i], r[4 * i + 1]);
+            }
+            if (r_hi < cm.len) {
+              float2* pp = reinterpret_cast<float2*>(buf + r_hi * stride + col);
+              if (!first) { float2 o = *pp; r[4 * i + 2] += o.x; r[4 * i + 3] += o.y; }
+              if (!last) *pp = make_float2(r[4 * i + 2], r[4 * i + 3]);
+            }
           }
-          if (r_hi < cm.len) {
-            float2* pp = reinterpret_cast<float2*>(buf + r_hi * stride + col);
-            if (!first) { float2 o = *pp; r[4 * i + 2] += o.x; r[4 * i + 3] += o.y; }
-            if (!last) *pp = make_float2(r[4 * i + 2], r[4 * i + 3]);
+          if (last) {
+            *swz_ptr32(Hp, r_lo, col, BT) = pack_bf16(r[4 * i], r[4 * i + 1]);
+            *swz_ptr32(Hp, r_hi, col, BT) = pack_bf16(r[4 * i + 2], r[4 * i + 3]);
           }
-        }
-        if (last) {
-          *swz_ptr32(Hp, r_lo, col, BT) = pack_bf16(r[4 * i], r[4 * i + 1]);
-          *swz_ptr32(Hp, r_hi, col, BT) = pack_bf16(r[4 * i + 2], r[4 * i + 3]);
         }
       }
+      rq_lo += __shfl_xor_sync(0xffffffffu, rq_lo, 1);
+      rq_lo += __shfl_xor_sync(0xffffffffu, rq_lo, 2);
+      rq_hi += __shfl_xor_sync(0xffffffffu, rq_hi, 1);
+      rq_hi += __shfl_xor_sync(0xffffffffu, rq_hi, 2);
+      if (t == 0) {
+        rqs[hc * BT + r_lo] = rq_lo;
+        rqs[hc * BT + r_hi] = rq_hi;
+      }
     }
-    rq_lo += __shfl_xor_sync(0xffffffffu, rq_lo, 1);
-    rq_lo += __shfl_xor_sync(0xffffffffu, rq_lo, 2);
-    rq_hi += __shfl_xor_sync(0xffffffffu, rq_hi, 1);
-    rq_hi += __shfl_xor_sync(0xffffffffu, rq_hi, 2);
     tc5::fence_before_sync();
     __syncthreads();  // every warp has drained the dq columns; staging tile complete
 
     // ---- phase 3: dk_intra = dP~^T q (into the columns dq just left)
     if (tid == 0) {
       tc5::fence_after_sync();
-      issue_mma(TM_DKI, opPm, opQ, 64, DK, 4, 0);
+      issue_mma_t<4>(TM_DKI, opPm, opQ, 64, DK, 0);
       ph.commit();
     }
     if (last)
@@ -243,23 +269,26 @@ __global__ void __launch_bounds__(NTHREADS) bwd_dqk_kernel(const b200gdn_chunk_a
     if (__syncthreads_or(!ph.wait())) { failed = true; break; }
 
     // ---- epilogue 3: dk = dk_state + dk_intra, gate-gradient rows, tail
-    float rk_lo = 0.f, rk_hi = 0.f, rs = 0.f;
     {
+      float rk_lo = 0.f, rk_hi = 0.f, rs = 0.f;
       float* buf = a.dk_part + (row0 * a.H + hq) * DK;
       const int64_t stride = (int64_t)a.H * DK;
+      float r[KB][16], s[KB][16];
 #pragma unroll
-      for (int b = 0; b < DK / 32; ++b) {
-        float r[16], s[16];
-        acc_ld32(TM_DKS, warp, b * 32, s);
-        acc_ld32(TM_DKI, warp, b * 32, r);
-        tc5::tmem_ld_wait();
+      for (int b = 0; b < KB; ++b) {
+        acc_ld32q(TM_DKS, q, ck + b * 32, s[b]);
+        acc_ld32q(TM_DKI, q, ck + b * 32, r[b]);
+      }
+      tc5::tmem_ld_wait();
+#pragma unroll
+      for (int b = 0; b < KB; ++b)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int col = b * 32 + i * 8 + 2 * t;
+          const int col = ck + b * 32 + i * 8 + 2 * t;
           const float2 ka = swz_ld2(Ks, r_lo, col, BT), kb = swz_ld2(Ks, r_hi, col, BT);
-          rs += s[4 * i] * ka.x + s[4 * i + 1] * ka.y + s[4 * i + 2] * kb.x + s[4 * i + 3] * kb.y;
-          const float d0 = r[4 * i] + s[4 * i], d1 = r[4 * i + 1] + s[4 * i + 1];
-          const float d2 = r[4 * i + 2] + s[4 * i + 2], d3 = r[4 * i + 3] + s[4 * i + 3];
+          rs += s[b][4 * i] * ka.x + s[b][4 * i + 1] * ka.y + s[b][4 * i + 2] * kb.x + s[b][4 * i + 3] * kb.y;
+          const float d0 = r[b][4 * i] + s[b][4 * i], d1 = r[b][4 * i + 1] + s[b][4 * i + 1];
+          const float d2 = r[b][4 * i + 2] + s[b][4 * i + 2], d3 = r[b][4 * i + 3] + s[b][4 * i + 3];
           rk_lo += d0 * ka.x + d1 * ka.y;
           rk_hi += d2 * kb.x + d3 * kb.y;
           if (r_lo < cm.len) {
@@ -273,30 +302,36 @@ __global__ void __launch_bounds__(NTHREADS) bwd_dqk_kernel(const b200gdn_chunk_a
             *pp = make_float2(d2 + o.x, d3 + o.y);
           }
         }
-      }
-    }
-    rk_lo += __shfl_xor_sync(0xffffffffu, rk_lo, 1);
-    rk_lo += __shfl_xor_sync(0xffffffffu, rk_lo, 2);
-    rk_hi += __shfl_xor_sync(0xffffffffu, rk_hi, 1);
-    rk_hi += __shfl_xor_sync(0xffffffffu, rk_hi, 2);
+      rk_lo += __shfl_xor_sync(0xffffffffu, rk_lo, 1);
+      rk_lo += __shfl_xor_sync(0xffffffffu, rk_lo, 2);
+      rk_hi += __shfl_xor_sync(0xffffffffu, rk_hi, 1);
+      rk_hi += __shfl_xor_sync(0xffffffffu, rk_hi, 2);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      rs += __shfl_xor_sync(0xffffffffu, rs, o);
-      hd += __shfl_xor_sync(0xffffffffu, hd, o);
-    }
-    if (lane == 0) {
-      red[warp] = hd;
-      red[4 + warp] = rs;
-    }
-    if (t == 0) {
-      dGs[r_lo] = rq_lo - rk_lo;
-      dGs[r_hi] = rq_hi - rk_hi;
+      for (int o = 16; o > 0; o >>= 1) {
+        rs += __shfl_xor_sync(0xffffffffu, rs, o);
+        hd += __shfl_xor_sync(0xffffffffu, hd, o);
+      }
+      if (lane == 0) {
+        red[warp] = hd;
+        red[8 + warp] = rs;
+      }
+      if (t == 0) {
+        rks[hc * BT + r_lo] = rk_lo;
+        rks[hc * BT + r_hi] = rk_hi;
+      }
     }
     tc5::fence_before_sync();
     __syncthreads();
     if (tid < cm.len) {
-      const float tail = exp2f(glast) * (red[0] + red[1] + red[2] + red[3]) + (red[4] + red[5] + red[6] + red[7]);
-      a.dG[(row0 + tid) * a.HV + hv] = dGs[tid] + (tid == cm.len - 1 ? tail : 0.f);
+      float sh = 0.f, sr = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+        sh += red[w];
+        sr += red[8 + w];
+      }
+      const float tail = exp2f(glast) * sh + sr;
+      const float dGrow = (rqs[tid] + rqs[BT + tid]) - (rks[tid] + rks[BT + tid]);
+      a.dG[(row0 + tid) * a.HV + hv] = dGrow + (tid == cm.len - 1 ? tail : 0.f);
     }
   }
 
@@ -310,8 +345,19 @@ template <int DK, int DV>
 int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
   using S = DqkSmem<DK, DV>;
   if (int e = ensure_smem(bwd_dqk_kernel<DK, DV>, S::bytes)) return e;
+  DqkMaps m;
+  const uint64_t pk = (uint64_t)a.H * DK, pv = (uint64_t)a.HV * DV;
+  const uint64_t hrows = (uint64_t)a.n_chunks * a.HV * DK;
+  int rc = 0;
+  rc |= tma::encode_bf16_panels(&m.q, a.q, a.rows, pk, pk, BT, DK / 64);
+  rc |= tma::encode_bf16_panels(&m.k, a.k, a.rows, pk, pk, BT, DK / 64);
+  rc |= tma::encode_bf16_panels(&m.d_o, a.d_o, a.rows, pv, pv, BT, DV / 64);
+  rc |= tma::encode_bf16_panels(&m.vn, a.v_new, a.rows, pv, pv, BT, DV / 64);
+  rc |= tma::encode_bf16_2d(&m.h, a.h, hrows, DV, DV, DK);
+  rc |= tma::encode_bf16_2d(&m.dh, a.dh, hrows, DV, DV, DK);
+  if (rc != 0) return set_error(B200GDN_ERR_CUDA, "bwd_dqk: cuTensorMapEncodeTiled failed (%d)", rc);
   dim3 grid(a.n_chunks, a.H);
-  bwd_dqk_kernel<DK, DV><<<grid, NTHREADS, S::bytes, st>>>(a);
+  bwd_dqk_kernel<DK, DV><<<grid, NTHREADS, S::bytes, st>>>(a, m);
   return check_launch("bwd_dqk");
 }
 
