@@ -3,8 +3,10 @@
 //
 // Replaces chunk_local_cumsum (fla/ops/utils/cumsum.py:33-68), the fused K K^T + triangular solve
 // (fla/ops/gated_delta_rule/chunk_fwd.py:40-328) and recompute_w_u_fwd (gated_delta_rule/wy_fast.py:43-106).
-//   * K and V tiles arrive by TMA; K K^T, W and U run on tcgen05 with TMEM accumulators; A, W, U leave
-//     through TMA stores (plain predicated stores for a ragged chunk);
+//   * K and V tiles arrive by TMA; K K^T, W and U run on tcgen05 with TMEM accumulators (128 columns, used
+//     one product after the other); A, W, U leave through TMA stores (plain predicated stores for a ragged
+//     chunk); shared-memory regions are reused along the way so that three CTAs share an SM and hide each
+//     other's latencies;
 //   * the inverse is formed in exact fp32 on the CUDA cores: the four 16x16 diagonal blocks by
 //     right-looking forward substitution (one thread per column), then two levels of block merges
 //     A21 = -A22 (L21 A11) (16 -> 32 -> 64); the reference uses tf32 tensor-core merges;
@@ -18,22 +20,25 @@ namespace {
 
 constexpr int NTHREADS = 256;
 constexpr int LDF = 68;  // fp32 row stride of the 64x64 solve matrices
+constexpr int LDT = 36;  // fp32 row stride of the (at most 32x32) merge temporary
 __device__ int g_intra_timeout = 0;
 
 template <int DK, int DV>
 struct IntraSmem {
+  // Regions are reused as the kernel advances (each hand-over is separated by a CTA barrier):
+  //   K tile                      -> W staging
+  //   fp32 L                      -> V tile (loaded once L is dead) -> U staging
+  //   fp32 inverse                -> bf16 A (beta 2^gamma)_col | A beta_col
+  //   fp32 merge temporary (32x32)-> bf16 A
+  static constexpr size_t fmat = ((sizeof(float) * BT * LDF + 1023) / 1024) * 1024;
   static constexpr size_t o_k = 0;
-  static constexpr size_t o_v = o_k + BT * DK * 2;
-  static constexpr size_t o_l = o_v + BT * DV * 2;          // fp32 L ...
-  static constexpr size_t o_a = o_l + sizeof(float) * BT * LDF;   // ... fp32 inverse ...
-  static constexpr size_t o_t = o_a + sizeof(float) * BT * LDF;   // ... fp32 temp; the three become W | U staging
-  static constexpr size_t o_aw = ((o_t + sizeof(float) * BT * LDF + 1023) / 1024) * 1024;  // bf16 A (beta 2^gamma)_col
-  static constexpr size_t o_au = o_aw + BT * 128;           // bf16 A beta_col
-  static constexpr size_t o_ab = o_au + BT * 128;           // bf16 A
-  static constexpr size_t o_vec = o_ab + BT * 128;
+  static constexpr size_t o_l = o_k + BT * DK * 2;
+  static constexpr size_t o_a = o_l + (fmat > BT * DV * 2 ? fmat : BT * DV * 2);
+  static constexpr size_t o_t = o_a + fmat;
+  static constexpr size_t o_vec = o_t + BT * 128;
   static constexpr size_t bytes = o_vec + 4 * BT * 4 + 64 + 1024;
-  static constexpr size_t o_stg = ((o_l + 1023) / 1024) * 1024;   // staging for W then U (1024-aligned inside L/A/T)
-  static_assert(o_stg + BT * DK * 2 + BT * DV * 2 <= o_aw, "W and U staging fit in the fp32 solve buffers");
+  static_assert(fmat >= 2 * BT * 128, "two bf16 64x64 tiles fit in the fp32 inverse");
+  static_assert(sizeof(float) * 32 * LDT <= BT * 128, "merge temporary fits");
 };
 
 struct IntraMaps {
@@ -41,9 +46,10 @@ struct IntraMaps {
 };
 
 // T = L21 * A11 ;  A21 = -A22 * T   for an N x N off-diagonal block whose top-left corner is (r0, c0).
-// `nthr` threads with local index `t` cooperate (one row x four columns each).
+// T is kept in a compact temporary (row stride LDT).  `nthr` threads with local index `t` cooperate
+// (one row x four columns each).
 template <int N>
-__device__ __forceinline__ void merge_step1(const float* Lf, const float* Af, float* Tf, int r0, int c0, int t, int nthr) {
+__device__ __forceinline__ void merge_step1(const float* Lf, const float* Af, float* T, int r0, int c0, int t, int nthr) {
   for (int o = t; o < N * N / 4; o += nthr) {
     const int i = o / (N / 4), j0 = (o % (N / 4)) * 4;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -53,18 +59,18 @@ __device__ __forceinline__ void merge_step1(const float* Lf, const float* Af, fl
       const float4 x = *reinterpret_cast<const float4*>(&Af[(c0 + m) * LDF + c0 + j0]);
       acc[0] += l * x.x; acc[1] += l * x.y; acc[2] += l * x.z; acc[3] += l * x.w;
     }
-    *reinterpret_cast<float4*>(&Tf[(r0 + i) * LDF + c0 + j0]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4*>(&T[i * LDT + j0]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
   }
 }
 template <int N>
-__device__ __forceinline__ void merge_step2(const float* Tf, float* Af, int r0, int c0, int t, int nthr) {
+__device__ __forceinline__ void merge_step2(const float* T, float* Af, int r0, int c0, int t, int nthr) {
   for (int o = t; o < N * N / 4; o += nthr) {
     const int i = o / (N / 4), j0 = (o % (N / 4)) * 4;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int m = 0; m < N; ++m) {
       const float a22 = Af[(r0 + i) * LDF + r0 + m];
-      const float4 tv = *reinterpret_cast<const float4*>(&Tf[(r0 + m) * LDF + c0 + j0]);
+      const float4 tv = *reinterpret_cast<const float4*>(&T[m * LDT + j0]);
       acc[0] += a22 * tv.x; acc[1] += a22 * tv.y; acc[2] += a22 * tv.z; acc[3] += a22 * tv.w;
     }
     *reinterpret_cast<float4*>(&Af[(r0 + i) * LDF + c0 + j0]) = make_float4(-acc[0], -acc[1], -acc[2], -acc[3]);
@@ -72,27 +78,27 @@ __device__ __forceinline__ void merge_step2(const float* Tf, float* Af, int r0, 
 }
 
 template <int DK, int DV>
-__global__ void __launch_bounds__(NTHREADS, 2) intra_fwd_kernel(const b200gdn_chunk_args a, const __grid_constant__ IntraMaps maps) {
+__global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_chunk_args a, const __grid_constant__ IntraMaps maps) {
   using S = IntraSmem<DK, DV>;
+  constexpr int KB = DK / 64, VB = DV / 64;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned char* Ks = smem + S::o_k;
-  unsigned char* Vs = smem + S::o_v;
+  unsigned char* Ks = smem + S::o_k;      // later the W staging tile
+  unsigned char* Vs = smem + S::o_l;      // after L; later the U staging tile
   float* Lf = reinterpret_cast<float*>(smem + S::o_l);
   float* Af = reinterpret_cast<float*>(smem + S::o_a);
   float* Tf = reinterpret_cast<float*>(smem + S::o_t);
-  unsigned char* Aw = smem + S::o_aw;
-  unsigned char* Au = smem + S::o_au;
-  unsigned char* Ab = smem + S::o_ab;
-  unsigned char* StgW = smem + S::o_stg;
-  unsigned char* StgU = StgW + BT * DK * 2;
+  unsigned char* Aw = smem + S::o_a;      // after the fp32 inverse has been read into registers
+  unsigned char* Au = Aw + BT * 128;
+  unsigned char* Ab = smem + S::o_t;
   float* gam = reinterpret_cast<float*>(smem + S::o_vec);
   float* bet = gam + BT;
   float* bge = bet + BT;
   float* graw = bge + BT;
   uint64_t* bar = reinterpret_cast<uint64_t*>(graw + BT);
-  uint64_t* bar_ld = bar + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_ld + 1);
+  uint64_t* bar_k = bar + 1;
+  uint64_t* bar_v = bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 3);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int q = warp & 3, hc = warp >> 2;
@@ -104,34 +110,32 @@ __global__ void __launch_bounds__(NTHREADS, 2) intra_fwd_kernel(const b200gdn_ch
   const int r_lo = q * 16 + g, r_hi = r_lo + 8;
   const int cs = hc * 32;
 
-  if (warp == 0) tc5::tmem_alloc(tmem_slot, 256);
-  if (tid == 32) {
+  if (tid == 0) {
     tc5::mbar_init(bar, 1);
-    tc5::mbar_init(bar_ld, 1);
+    tc5::mbar_init(bar_k, 1);
+    tc5::mbar_init(bar_v, 1);
     tc5::fence_mbar_init();
+    tc5::mbar_expect_tx(bar_k, (uint32_t)(BT * DK * 2));
+    tma::load_3d(Ks, &maps.k, cm.row, (hq * DK) / 64, bar_k);
   }
-  if (tid < BT) {
-    const bool ok = tid < cm.len;
-    graw[tid] = ok ? a.g[(row0 + tid) * a.HV + hv] : 0.f;
-    bet[tid] = ok ? a.beta[(row0 + tid) * a.HV + hv] : 0.f;
+  if (warp == 1) tc5::tmem_alloc(tmem_slot, 128);
+  if (tid >= 64 && tid < 128) {
+    const int r = tid - 64;
+    const bool ok = r < cm.len;
+    graw[r] = ok ? a.g[(row0 + r) * a.HV + hv] : 0.f;
+    bet[r] = ok ? a.beta[(row0 + r) * a.HV + hv] : 0.f;
   }
-  // zero the fp32 inverse (upper triangles and off-diagonal blocks are read as zeros by the merges)
-  for (int i = tid; i < BT * LDF; i += NTHREADS) Af[i] = 0.f;
+  // zero the fp32 inverse (the merges and the final conversion read the untouched blocks as zeros)
+  for (int i = tid; i < BT * LDF / 4; i += NTHREADS) reinterpret_cast<float4*>(Af)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   tc5::fence_before_sync();
   __syncthreads();
   tc5::fence_after_sync();
   const uint32_t tm = *tmem_slot;
-  const uint32_t TM_KK = tm, TM_W = tm, TM_U = tm + 128;
   PhaseBarrier ph{bar, 0u, &g_intra_timeout};
   bool failed = false;
 
-  if (tid == 0) {
-    tc5::mbar_expect_tx(bar_ld, (uint32_t)(BT * DK * 2 + BT * DV * 2));
-    tma::load_3d(Ks, &maps.k, cm.row, (hq * DK) / 64, bar_ld);
-    tma::load_3d(Vs, &maps.v, cm.row, (hv * DV) / 64, bar_ld);
-  }
   if (tid < BT) {
-    // warp-shuffle inclusive scan of g over the chunk (two warps), then the cross-warp carry
+    // inclusive scan of g over the chunk: shuffle scan inside each of the two warps, carry added below
     float s = graw[tid];
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -140,10 +144,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) intra_fwd_kernel(const b200gdn_ch
     }
     gam[tid] = s;
   }
-  if (!tc5::mbar_wait(bar_ld, 0)) failed = true;
+  if (!tc5::mbar_wait(bar_k, 0)) failed = true;
   if (cm.len < BT) {
     zero_tail_rows<BT, DK>(Ks, cm.len, tid, NTHREADS);
-    zero_tail_rows<BT, DV>(Vs, cm.len, tid, NTHREADS);
     tc5::fence_async_smem();
   }
   if (__syncthreads_or(failed)) {
@@ -151,14 +154,10 @@ __global__ void __launch_bounds__(NTHREADS, 2) intra_fwd_kernel(const b200gdn_ch
   } else {
     if (tid == 0) {
       tc5::fence_after_sync();
-      issue_mma_t<DK / 16>(TM_KK, Operand{tc5::smem_addr(Ks), BT, 0}, Operand{tc5::smem_addr(Ks), BT, 0}, 64, 64, 0);
+      issue_mma_t<DK / 16>(tm, Operand{tc5::smem_addr(Ks), BT, 0}, Operand{tc5::smem_addr(Ks), BT, 0}, 64, 64, 0);
       ph.commit();
     }
-    if (tid < BT) {
-      const float gm = (gam[tid] + (tid >= 32 ? gam[31] : 0.f)) * 1.4426950216f;
-      // (the carry is read before anyone overwrites gam: see the barrier below)
-      graw[tid] = gm;
-    }
+    if (tid < BT) graw[tid] = (gam[tid] + (tid >= 32 ? gam[31] : 0.f)) * 1.4426950216f;
     __syncthreads();
     if (tid < BT) {
       const float gm = graw[tid];
@@ -173,7 +172,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) intra_fwd_kernel(const b200gdn_ch
     // ---- L = strict_tril(beta_i <k_i,k_j> 2^(gamma_i - gamma_j)) in fp32
     {
       float r[16];
-      acc_ld32q(TM_KK, q, cs, r);
+      acc_ld32q(tm, q, cs, r);
       tc5::tmem_ld_wait();
       const float g_lo = gam[r_lo], g_hi = gam[r_hi], b_lo = bet[r_lo], b_hi = bet[r_hi];
 #pragma unroll
@@ -193,7 +192,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) intra_fwd_kernel(const b200gdn_ch
     __syncthreads();
 
     // ---- four 16x16 diagonal inverses: thread (block b, column cc) solves (I + L_bb) x = e_cc right-looking,
-    //      so that the sixteen updates of a step are independent of each other
+    //      so that the updates of one step are independent of each other
     if (tid < BT) {
       const int b0 = (tid >> 4) * 16, cc = tid & 15;
       float s[16];
@@ -210,35 +209,49 @@ __global__ void __launch_bounds__(NTHREADS, 2) intra_fwd_kernel(const b200gdn_ch
     }
     __syncthreads();
     // ---- 16 -> 32: blocks (16,0) and (48,32), 64 threads each
-    if (tid < 128) merge_step1<16>(Lf, Af, Tf, (tid >> 6) ? 48 : 16, (tid >> 6) ? 32 : 0, tid & 63, 64);
+    if (tid < 128) merge_step1<16>(Lf, Af, Tf + (tid >> 6) * 16, (tid >> 6) ? 48 : 16, (tid >> 6) ? 32 : 0, tid & 63, 64);
     __syncthreads();
-    if (tid < 128) merge_step2<16>(Tf, Af, (tid >> 6) ? 48 : 16, (tid >> 6) ? 32 : 0, tid & 63, 64);
+    if (tid < 128) merge_step2<16>(Tf + (tid >> 6) * 16, Af, (tid >> 6) ? 48 : 16, (tid >> 6) ? 32 : 0, tid & 63, 64);
     __syncthreads();
     // ---- 32 -> 64: block (32,0), all threads
     merge_step1<32>(Lf, Af, Tf, 32, 0, tid, NTHREADS);
     __syncthreads();
+    // L is dead: its place takes the V tile while the last merge step and the conversion run
+    if (tid == 0) {
+      tc5::fence_async_smem();
+      tc5::mbar_expect_tx(bar_v, (uint32_t)(BT * DV * 2));
+      tma::load_3d(Vs, &maps.v, cm.row, (hv * DV) / 64, bar_v);
+    }
     merge_step2<32>(Tf, Af, 32, 0, tid, NTHREADS);
     __syncthreads();
 
-    // ---- bf16 operand tiles: A with its columns scaled for the W and U right-hand sides, and A itself
+    // ---- bf16 operand tiles (over the fp32 inverse and the merge temporary, hence through registers):
+    //      A with its columns scaled for the W and U right-hand sides, and A itself
+    {
+      float2 x[BT * BT / 2 / NTHREADS];
 #pragma unroll
-    for (int it = 0; it < BT * BT / 2 / NTHREADS; ++it) {
-      const int idx = it * NTHREADS + tid;
-      const int i = idx >> 5, j = (idx & 31) * 2;
-      const float2 x = *reinterpret_cast<const float2*>(&Af[i * LDF + j]);
-      *swz_ptr32(Aw, i, j, BT) = pack_bf16(x.x * bge[j], x.y * bge[j + 1]);
-      *swz_ptr32(Au, i, j, BT) = pack_bf16(x.x * bet[j], x.y * bet[j + 1]);
-      *swz_ptr32(Ab, i, j, BT) = pack_bf16(x.x, x.y);
+      for (int it = 0; it < BT * BT / 2 / NTHREADS; ++it) {
+        const int idx = it * NTHREADS + tid;
+        x[it] = *reinterpret_cast<const float2*>(&Af[(idx >> 5) * LDF + (idx & 31) * 2]);
+      }
+      __syncthreads();
+#pragma unroll
+      for (int it = 0; it < BT * BT / 2 / NTHREADS; ++it) {
+        const int idx = it * NTHREADS + tid;
+        const int i = idx >> 5, j = (idx & 31) * 2;
+        *swz_ptr32(Aw, i, j, BT) = pack_bf16(x[it].x * bge[j], x[it].y * bge[j + 1]);
+        *swz_ptr32(Au, i, j, BT) = pack_bf16(x[it].x * bet[j], x[it].y * bet[j + 1]);
+        *swz_ptr32(Ab, i, j, BT) = pack_bf16(x[it].x, x[it].y);
+      }
     }
     tc5::fence_async_smem();
     tc5::fence_before_sync();
     __syncthreads();
 
-    // ---- W = Aw K ; U = Au V   (K and V as MN-major B operands: contraction over the token rows)
+    // ---- W = Aw K   (K as an MN-major B operand: contraction over the token rows)
     if (tid == 0) {
       tc5::fence_after_sync();
-      issue_mma_t<BT / 16>(TM_W, Operand{tc5::smem_addr(Aw), BT, 0}, Operand{tc5::smem_addr(Ks), BT, 1}, 64, DK, 0);
-      issue_mma_t<BT / 16>(TM_U, Operand{tc5::smem_addr(Au), BT, 0}, Operand{tc5::smem_addr(Vs), BT, 1}, 64, DV, 0);
+      issue_mma_t<BT / 16>(tm, Operand{tc5::smem_addr(Aw), BT, 0}, Operand{tc5::smem_addr(Ks), BT, 1}, 64, DK, 0);
       ph.commit();
     }
     // A leaves while the tensor cores work
@@ -251,47 +264,72 @@ __global__ void __launch_bounds__(NTHREADS, 2) intra_fwd_kernel(const b200gdn_ch
       store_tile_swz<BT, BT, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.A) + (row0 * a.HV + hv) * BT, (int64_t)a.HV * BT, Ab,
                                        cm.len, tid);
     }
-    if (__syncthreads_or(!ph.wait())) {
+    if (!tc5::mbar_wait(bar_v, 0)) failed = true;
+    if (cm.len < BT) {
+      zero_tail_rows<BT, DV>(Vs, cm.len, tid, NTHREADS);
+      tc5::fence_async_smem();
+    }
+    if (__syncthreads_or(failed || !ph.wait())) {
       failed = true;
     } else {
-      constexpr int KB = DK / 64, VB = DV / 64;
       const int ck = hc * (DK / 2), cv = hc * (DV / 2);
-      float rw[KB][16], ru[VB][16];
+      float rw[KB][16];
 #pragma unroll
-      for (int b = 0; b < KB; ++b) acc_ld32q(TM_W, q, ck + b * 32, rw[b]);
-#pragma unroll
-      for (int b = 0; b < VB; ++b) acc_ld32q(TM_U, q, cv + b * 32, ru[b]);
+      for (int b = 0; b < KB; ++b) acc_ld32q(tm, q, ck + b * 32, rw[b]);
       tc5::tmem_ld_wait();
+      tc5::fence_before_sync();
+      __syncthreads();   // W has left tensor memory, K is no longer an operand
+      // ---- U = Au V into the same columns, while W is converted and staged over the K tile
+      if (tid == 0) {
+        tc5::fence_after_sync();
+        issue_mma_t<BT / 16>(tm, Operand{tc5::smem_addr(Au), BT, 0}, Operand{tc5::smem_addr(Vs), BT, 1}, 64, DV, 0);
+        ph.commit();
+      }
 #pragma unroll
       for (int b = 0; b < KB; ++b)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int col = ck + b * 32 + i * 8 + 2 * t;
-          *swz_ptr32(StgW, r_lo, col, BT) = pack_bf16(rw[b][4 * i], rw[b][4 * i + 1]);
-          *swz_ptr32(StgW, r_hi, col, BT) = pack_bf16(rw[b][4 * i + 2], rw[b][4 * i + 3]);
-        }
-#pragma unroll
-      for (int b = 0; b < VB; ++b)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int col = cv + b * 32 + i * 8 + 2 * t;
-          *swz_ptr32(StgU, r_lo, col, BT) = pack_bf16(ru[b][4 * i], ru[b][4 * i + 1]);
-          *swz_ptr32(StgU, r_hi, col, BT) = pack_bf16(ru[b][4 * i + 2], ru[b][4 * i + 3]);
+          *swz_ptr32(Ks, r_lo, col, BT) = pack_bf16(rw[b][4 * i], rw[b][4 * i + 1]);
+          *swz_ptr32(Ks, r_hi, col, BT) = pack_bf16(rw[b][4 * i + 2], rw[b][4 * i + 3]);
         }
       tc5::fence_async_smem();
-      tc5::fence_before_sync();
-      __syncthreads();
-      if (cm.len == BT) {
-        if (tid == 32) {
-          tma::store_3d(&maps.w, (int)cm.row, (hv * DK) / 64, StgW);
-          tma::store_3d(&maps.u, (int)cm.row, (hv * DV) / 64, StgU);
-          tma::store_commit();
-        }
+      if (__syncthreads_or(!ph.wait())) {
+        failed = true;
       } else {
-        store_tile_swz<BT, DK, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.w) + (row0 * a.HV + hv) * DK, (int64_t)a.HV * DK, StgW,
-                                         cm.len, tid);
-        store_tile_swz<BT, DV, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.u) + (row0 * a.HV + hv) * DV, (int64_t)a.HV * DV, StgU,
-                                         cm.len, tid);
+        if (cm.len == BT) {
+          if (tid == 32) {
+            tma::store_3d(&maps.w, (int)cm.row, (hv * DK) / 64, Ks);
+            tma::store_commit();
+          }
+        } else {
+          store_tile_swz<BT, DK, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.w) + (row0 * a.HV + hv) * DK, (int64_t)a.HV * DK,
+                                           Ks, cm.len, tid);
+        }
+        float ru[VB][16];
+#pragma unroll
+        for (int b = 0; b < VB; ++b) acc_ld32q(tm, q, cv + b * 32, ru[b]);
+        tc5::tmem_ld_wait();
+#pragma unroll
+        for (int b = 0; b < VB; ++b)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int col = cv + b * 32 + i * 8 + 2 * t;
+            *swz_ptr32(Vs, r_lo, col, BT) = pack_bf16(ru[b][4 * i], ru[b][4 * i + 1]);
+            *swz_ptr32(Vs, r_hi, col, BT) = pack_bf16(ru[b][4 * i + 2], ru[b][4 * i + 3]);
+          }
+        tc5::fence_async_smem();
+        tc5::fence_before_sync();
+        __syncthreads();
+        if (cm.len == BT) {
+          if (tid == 32) {
+            tma::store_3d(&maps.u, (int)cm.row, (hv * DV) / 64, Vs);
+            tma::store_commit();
+          }
+        } else {
+          store_tile_swz<BT, DV, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.u) + (row0 * a.HV + hv) * DV, (int64_t)a.HV * DV,
+                                           Vs, cm.len, tid);
+        }
       }
     }
   }
@@ -299,7 +337,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) intra_fwd_kernel(const b200gdn_ch
   if (failed && tid == 0) atomicExch(&g_intra_timeout, 1);
   tc5::fence_before_sync();
   __syncthreads();
-  if (warp == 0) tc5::tmem_dealloc(tm, 256);
+  if (warp == 1) tc5::tmem_dealloc(tm, 128);
 }
 
 template <int DK, int DV>
