@@ -42,7 +42,7 @@ struct WyTcSmem {
 };
 
 struct WyMaps {
-  CUtensorMap k, v, du, a, h;
+  CUtensorMap k, v, du, a, h, dv;
 };
 
 // sum over the 8 row-lanes of a warp (lanes that differ in bits 2..4), result valid in lanes with g == 0
@@ -101,11 +101,31 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
   const int r_lo = q * 16 + g, r_hi = r_lo + 8;
   const int cs = hc * 32;   // this warp's 32 columns of a 64-column tile
 
-  if (warp == 0) tc5::tmem_alloc(tmem_slot, 256);
-  if (tid == 32) {
+  auto issue_loads = [&](int gi) {   // one thread
+    const int hv = hq * G + gi;
+    const uint32_t tx = (uint32_t)((gi == 0 ? BT * DK * 2 : 0) + 2 * BT * DV * 2 + BT * 128 + DK * DV * 2 + BT * 4);
+    tc5::mbar_expect_tx(bar_ld, tx);
+    tma::load_3d(dUs, &maps.du, cm.row, (hv * DV) / 64, bar_ld);
+    tma::load_3d(Hs, &maps.h, (c * a.HV + hv) * DK, 0, bar_ld);
+    if (gi == 0) tma::load_3d(Ks, &maps.k, cm.row, (hq * DK) / 64, bar_ld);
+    tma::load_3d(Vs, &maps.v, cm.row, (hv * DV) / 64, bar_ld);
+    tma::load_2d(As, &maps.a, hv * BT, cm.row, bar_ld);
+    tma::load_1d(gs, gamma_ptr(a.gamma, c, a.HV, hv), BT * 4, bar_ld);
+  };
+  if (tid == 0) {
     tc5::mbar_init(bar, 1);
     tc5::mbar_init(bar_ld, 1);
     tc5::fence_mbar_init();
+    issue_loads(0);   // the first head's tiles are on their way while the CTA sets itself up
+  }
+  if (warp == 1) tc5::tmem_alloc(tmem_slot, 256);
+  {
+    // the dq/dk kernel's part of dk is read at the very end: pull it into L2 now (one 128-byte line per thread)
+    const int r = tid >> 2, seg = tid & 3;
+    if (r < cm.len && seg * 32 < DK) {
+      const float* p = a.dk_part + ((row0 + r) * a.H + hq) * DK + seg * 32;
+      asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p));
+    }
   }
   tc5::fence_before_sync();
   __syncthreads();
@@ -128,16 +148,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
   for (int gi = 0; gi < G && !failed; ++gi) {
     const int hv = hq * G + gi;
     const bool last = gi == G - 1;
-    __syncthreads();   // previous head fully consumed
-    if (tid == 0) {
-      const uint32_t tx = (uint32_t)((gi == 0 ? BT * DK * 2 : 0) + 2 * BT * DV * 2 + BT * 128 + DK * DV * 2 + BT * 4);
-      tc5::mbar_expect_tx(bar_ld, tx);
-      if (gi == 0) tma::load_3d(Ks, &maps.k, cm.row, (hq * DK) / 64, bar_ld);
-      tma::load_3d(dUs, &maps.du, cm.row, (hv * DV) / 64, bar_ld);
-      tma::load_3d(Hs, &maps.h, (c * a.HV + hv) * DK, 0, bar_ld);
-      tma::load_3d(Vs, &maps.v, cm.row, (hv * DV) / 64, bar_ld);
-      tma::load_2d(As, &maps.a, hv * BT, cm.row, bar_ld);
-      tma::load_1d(gs, gamma_ptr(a.gamma, c, a.HV, hv), BT * 4, bar_ld);
+    if (gi > 0) {
+      __syncthreads();   // previous head fully consumed
+      if (tid == 0) issue_loads(gi);
     }
     if (tid < BT) {
       const bool ok = tid < cm.len;
@@ -151,18 +164,10 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
       zero_tail_rows<BT, DV>(dUs, cm.len, tid, NTHREADS);
       zero_tail_rows<BT, BT>(As, cm.len, tid, NTHREADS);
     }
-    __syncthreads();
-    if (tid < BT) {
+    if (tid < BT) {   // bet[tid] was written by this very thread
       const float e = exp2f(gs[tid]);
       eg[tid] = e;
       bge[tid] = bet[tid] * e;
-    }
-    __syncthreads();
-    // A with its columns scaled by beta 2^gamma
-    for (int idx = tid; idx < BT * BT / 2; idx += NTHREADS) {
-      const int i = idx / (BT / 2), j = (idx % (BT / 2)) * 2;
-      const float2 x = swz_ld2(As, i, j, BT);
-      *swz_ptr32(Abs, i, j, BT) = pack_bf16(x.x * bge[j], x.y * bge[j + 1]);
     }
     tc5::fence_async_smem();
     if (__syncthreads_or(failed)) { failed = true; break; }
@@ -174,6 +179,12 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
       issue_mma_t<DV / 16>(TM_S1, opdU_k, Operand{tc5::smem_addr(Vs), BT, 0}, 64, 64, 0);
       issue_mma_t<DK / 16>(TM_KK, opK_k, opK_k, 64, 64, 0);
       ph.commit();
+    }
+    // A with its columns scaled by beta 2^gamma (an operand of phase 3), while phase 1 runs
+    for (int idx = tid; idx < BT * BT / 2; idx += NTHREADS) {
+      const int i = idx / (BT / 2), j = (idx % (BT / 2)) * 2;
+      const float2 x = swz_ld2(As, i, j, BT);
+      *swz_ptr32(Abs, i, j, BT) = pack_bf16(x.x * bge[j], x.y * bge[j + 1]);
     }
     const float g_lo = gs[r_lo], g_hi = gs[r_hi];
     const float b_lo = bet[r_lo], b_hi = bet[r_hi];
@@ -197,17 +208,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
     float dA2[16];
     acc_ld32q(TM_S1, q, cs, dA2);
     tc5::tmem_ld_wait();
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int col = cs + i * 8 + 2 * t;
-      const float2 al = swz_ld2(As, r_lo, col, BT), ah = swz_ld2(As, r_hi, col, BT);
-      const float s0 = sum_over_g(al.x * dA2[4 * i] + ah.x * dA2[4 * i + 2]);
-      const float s1 = sum_over_g(al.y * dA2[4 * i + 1] + ah.y * dA2[4 * i + 3]);
-      if (g == 0) {
-        c_vb[q * BT + col] = s0;
-        c_vb[q * BT + col + 1] = s1;
-      }
-    }
     tc5::fence_async_smem();
     tc5::fence_before_sync();
     __syncthreads();
@@ -219,9 +219,21 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
       issue_mma_t<BT / 16>(TM_BIG, opA_mn, opdU_mn, 64, DV, 0);
       ph.commit();
     }
+    // colsum(A . dA2), off the critical path
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int col = cs + i * 8 + 2 * t;
+      const float2 al = swz_ld2(As, r_lo, col, BT), ah = swz_ld2(As, r_hi, col, BT);
+      const float s0 = sum_over_g(al.x * dA2[4 * i] + ah.x * dA2[4 * i + 2]);
+      const float s1 = sum_over_g(al.y * dA2[4 * i + 1] + ah.y * dA2[4 * i + 3]);
+      if (g == 0) {
+        c_vb[q * BT + col] = s0;
+        c_vb[q * BT + col + 1] = s1;
+      }
+    }
     if (__syncthreads_or(!ph.wait())) { failed = true; break; }
 
-    // ---- epilogue 2: dA -> shared (over V); colsum(A . dA1); dv = dVb beta -> global
+    // ---- epilogue 2: dA -> shared (over V) is all phase 3 waits for; colsum(A . dA1) and dv = dVb beta follow
     {
       float r[16];
       acc_ld32q(TM_S1, q, cs, r);
@@ -232,13 +244,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int col = cs + i * 8 + 2 * t;
-        const float2 al = swz_ld2(As, r_lo, col, BT), ah = swz_ld2(As, r_hi, col, BT);
-        const float s0 = sum_over_g(al.x * r[4 * i] + ah.x * r[4 * i + 2]);
-        const float s1 = sum_over_g(al.y * r[4 * i + 1] + ah.y * r[4 * i + 3]);
-        if (g == 0) {
-          c_kbg[q * BT + col] = s0;
-          c_kbg[q * BT + col + 1] = s1;
-        }
         float v[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -247,6 +252,28 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
         }
         *swz_ptr32(dAs, r_lo, col, BT) = pack_bf16(v[0], v[1]);
         *swz_ptr32(dAs, r_hi, col, BT) = pack_bf16(v[2], v[3]);
+      }
+      tc5::fence_async_smem();
+      tc5::fence_before_sync();
+      __syncthreads();
+
+      // ---- phase 3: Y = dA A^T | dk = (A beta 2^gamma)^T dW
+      if (tid == 0) {
+        tc5::fence_after_sync();
+        issue_mma_t<BT / 16>(TM_S1, Operand{tc5::smem_addr(dAs), BT, 0}, opA_k, 64, 64, 0);
+        issue_mma_t<BT / 16>(TM_BIG, opAb_mn, opdW_mn, 64, DK, 0);
+        ph.commit();
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int col = cs + i * 8 + 2 * t;
+        const float2 al = swz_ld2(As, r_lo, col, BT), ah = swz_ld2(As, r_hi, col, BT);
+        const float s0 = sum_over_g(al.x * r[4 * i] + ah.x * r[4 * i + 2]);
+        const float s1 = sum_over_g(al.y * r[4 * i + 1] + ah.y * r[4 * i + 3]);
+        if (g == 0) {
+          c_kbg[q * BT + col] = s0;
+          c_kbg[q * BT + col + 1] = s1;
+        }
       }
 #pragma unroll
       for (int b = 0; b < VB; ++b)
@@ -258,18 +285,16 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
         }
     }
     tc5::fence_async_smem();
-    tc5::fence_before_sync();
     __syncthreads();
-
-    // ---- phase 3: Y = dA A^T | dk = (A beta 2^gamma)^T dW
-    if (tid == 0) {
-      tc5::fence_after_sync();
-      issue_mma_t<BT / 16>(TM_S1, Operand{tc5::smem_addr(dAs), BT, 0}, opA_k, 64, 64, 0);
-      issue_mma_t<BT / 16>(TM_BIG, opAb_mn, opdW_mn, 64, DK, 0);
-      ph.commit();
+    if (cm.len == BT) {
+      if (tid == 32) {
+        tma::store_3d(&maps.dv, (int)cm.row, (hv * DV) / 64, Stg);
+        tma::store_commit();
+      }
+    } else {
+      store_tile_swz<BT, DV, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.dv) + (row0 * a.HV + hv) * DV, (int64_t)a.HV * DV,
+                                       Stg, cm.len, tid);
     }
-    store_tile_swz<BT, DV, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.dv) + (row0 * a.HV + hv) * DV, (int64_t)a.HV * DV, Stg,
-                                     cm.len, tid);
     if (__syncthreads_or(!ph.wait())) { failed = true; break; }
 
     // ---- epilogue 3: Y -> shared
@@ -284,6 +309,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
         *swz_ptr32(Ys, r_hi, col, BT) = pack_bf16(r[4 * i + 2], r[4 * i + 3]);
       }
     }
+    if (tid == 32) tma::store_wait_read<0>();   // the dv staging tile is rewritten (as M2) after the next barrier
     tc5::fence_async_smem();
     tc5::fence_before_sync();
     __syncthreads();
@@ -296,39 +322,23 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
     }
     if (__syncthreads_or(!ph.wait())) { failed = true; break; }
 
-    // ---- epilogue 4: M, M2 = M beta_i -> shared; rowsum(M . KK), colsum(M2 . KK)
+    // ---- epilogue 4: M2 = M beta_i -> shared is all phase 5 waits for; the sums over M . KK follow
+    float m[16], kk[16];
     {
-      float r[16], kk[16];
+      float r[16];
       acc_ld32q(TM_S1, q, cs, r);
       acc_ld32q(TM_KK, q, cs, kk);
       tc5::tmem_ld_wait();
-      float rmk_lo = 0.f, rmk_hi = 0.f;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int col = cs + i * 8 + 2 * t;
-        float m[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int ii = (e & 2) ? r_hi : r_lo, jj = col + (e & 1);
-          m[e] = (ii > jj) ? -r[4 * i + e] * exp2f(((e & 2) ? g_hi : g_lo) - gs[jj]) : 0.f;
+          m[4 * i + e] = (ii > jj) ? -r[4 * i + e] * exp2f(((e & 2) ? g_hi : g_lo) - gs[jj]) : 0.f;
         }
-        rmk_lo += m[0] * kk[4 * i] + m[1] * kk[4 * i + 1];
-        rmk_hi += m[2] * kk[4 * i + 2] + m[3] * kk[4 * i + 3];
-        const float m20 = m[0] * b_lo, m21 = m[1] * b_lo, m22 = m[2] * b_hi, m23 = m[3] * b_hi;
-        const float s0 = sum_over_g(m20 * kk[4 * i] + m22 * kk[4 * i + 2]);
-        const float s1 = sum_over_g(m21 * kk[4 * i + 1] + m23 * kk[4 * i + 3]);
-        if (g == 0) {
-          c_m2[q * BT + col] = s0;
-          c_m2[q * BT + col + 1] = s1;
-        }
-        *swz_ptr32(M2s, r_lo, col, BT) = pack_bf16(m20, m21);
-        *swz_ptr32(M2s, r_hi, col, BT) = pack_bf16(m22, m23);
-      }
-      rmk_lo = sum_over_t(rmk_lo);
-      rmk_hi = sum_over_t(rmk_hi);
-      if (t == 0) {
-        r_mk[hc * BT + r_lo] = rmk_lo;
-        r_mk[hc * BT + r_hi] = rmk_hi;
+        *swz_ptr32(M2s, r_lo, col, BT) = pack_bf16(m[4 * i] * b_lo, m[4 * i + 1] * b_lo);
+        *swz_ptr32(M2s, r_hi, col, BT) = pack_bf16(m[4 * i + 2] * b_hi, m[4 * i + 3] * b_hi);
       }
     }
     tc5::fence_async_smem();
@@ -342,6 +352,27 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
       issue_mma_t<BT / 16>(TM_BIG, Operand{tc5::smem_addr(M2s), BT, 1}, opK_mn, 64, DK, 1);
       ph.commit();
     }
+    {
+      float rmk_lo = 0.f, rmk_hi = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int col = cs + i * 8 + 2 * t;
+        rmk_lo += m[4 * i] * kk[4 * i] + m[4 * i + 1] * kk[4 * i + 1];
+        rmk_hi += m[4 * i + 2] * kk[4 * i + 2] + m[4 * i + 3] * kk[4 * i + 3];
+        const float s0 = sum_over_g(m[4 * i] * b_lo * kk[4 * i] + m[4 * i + 2] * b_hi * kk[4 * i + 2]);
+        const float s1 = sum_over_g(m[4 * i + 1] * b_lo * kk[4 * i + 1] + m[4 * i + 3] * b_hi * kk[4 * i + 3]);
+        if (g == 0) {
+          c_m2[q * BT + col] = s0;
+          c_m2[q * BT + col + 1] = s1;
+        }
+      }
+      rmk_lo = sum_over_t(rmk_lo);
+      rmk_hi = sum_over_t(rmk_hi);
+      if (t == 0) {
+        r_mk[hc * BT + r_lo] = rmk_lo;
+        r_mk[hc * BT + r_hi] = rmk_hi;
+      }
+    }
     // the dq/dk kernel's part of dk: fetched now so that its latency hides behind the MMAs
     float* const dkbuf = a.dk_part + (row0 * a.H + hq) * DK + hc * (DK / 2);
     const int64_t dkstride = (int64_t)a.H * DK;
@@ -352,6 +383,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
       part[n8][0] = r_lo < cm.len ? *reinterpret_cast<const float2*>(dkbuf + r_lo * dkstride + col) : make_float2(0.f, 0.f);
       part[n8][1] = r_hi < cm.len ? *reinterpret_cast<const float2*>(dkbuf + r_hi * dkstride + col) : make_float2(0.f, 0.f);
     }
+    __syncthreads();   // column / row sums of every warp are in place
     // gate / beta gradients while the MMAs run: dG per row, then the reverse cumsum as a two-warp suffix scan
     if (tid < BT) {
       const int i = tid;
@@ -400,10 +432,11 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
                                        cm.len, tid);
   }
 
+  if (tid == 32) tma::store_wait_all<0>();
   if (failed && tid == 0) atomicExch(&g_wy_timeout, 1);
   tc5::fence_before_sync();
   __syncthreads();
-  if (warp == 0) tc5::tmem_dealloc(tm, 256);
+  if (warp == 1) tc5::tmem_dealloc(tm, 256);
 }
 
 template <int DK, int DV>
@@ -417,6 +450,7 @@ int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
   rc |= tma::encode_bf16_panels(&m.v, a.v, a.rows, pv, pv, BT, DV / 64);
   rc |= tma::encode_bf16_panels(&m.du, a.dv2, a.rows, pv, pv, BT, DV / 64);
   rc |= tma::encode_bf16_2d(&m.a, a.A, a.rows, (uint64_t)a.HV * BT, (uint64_t)a.HV * BT, BT);
+  rc |= tma::encode_bf16_panels(&m.dv, a.dv, a.rows, pv, pv, BT, DV / 64);
   rc |= tma::encode_bf16_panels(&m.h, a.h, (uint64_t)a.n_chunks * a.HV * DK, DV, DV, DK, DV / 64);
   if (rc != 0) return set_error(B200GDN_ERR_CUDA, "bwd_wy: cuTensorMapEncodeTiled failed (%d)", rc);
   dim3 grid(a.n_chunks, a.H);
