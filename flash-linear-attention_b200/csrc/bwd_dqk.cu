@@ -58,8 +58,10 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
   float* rks = rqs + 2 * BT;     // [2][64] <dk, k>
   float* red = rks + 2 * BT;     // [0..7] <h,dh> per warp, [8..15] sum of <dk_state, k> per warp
   uint64_t* bar = reinterpret_cast<uint64_t*>(red + 16);
-  uint64_t* bar_ld = bar + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_ld + 1);
+  uint64_t* bar_a = bar + 1;   // do, v_new, gamma of one head
+  uint64_t* bar_b = bar + 2;   // one h / dh panel pair
+  uint64_t* bar_c = bar + 3;   // q, k (once)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 4);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int q = warp & 3, hc = warp >> 2;
@@ -71,19 +73,45 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
   const int r_lo = q * 16 + g, r_hi = r_lo + 8;
   const int cs = hc * 32, ck = hc * (DK / 2);
 
-  if (warp == 0) tc5::tmem_alloc(tmem_slot, 256);
-  if (tid == 32) {
+  // Loads of one head, in the order the phases need them, each group on its own barrier so that phase 1
+  // starts as soon as do and v_new are in.  The second h / dh panel pair is only pulled into L2 here; it
+  // takes the place of the first pair once phase 2 has consumed that.
+  auto issue_loads = [&](int gi) {   // one thread
+    const int hv = hq * G + gi;
+    const int hrow = (c * a.HV + hv) * DK;
+    tc5::mbar_expect_tx(bar_a, (uint32_t)(2 * BT * DV * 2 + BT * 4));
+    tma::load_3d(Do, &maps.d_o, cm.row, (hv * DV) / 64, bar_a);
+    tma::load_3d(Vn, &maps.vn, cm.row, (hv * DV) / 64, bar_a);
+    tma::load_1d(gs, gamma_ptr(a.gamma, c, a.HV, hv), BT * 4, bar_a);
+    tc5::mbar_expect_tx(bar_b, 2 * DK * 128);
+    tma::load_2d(Hp, &maps.h, 0, hrow, bar_b);
+    tma::load_2d(dHp, &maps.dh, 0, hrow, bar_b);
+    if (gi == 0) {
+      tc5::mbar_expect_tx(bar_c, 2 * BT * DK * 2);
+      tma::load_3d(Qs, &maps.q, cm.row, (hq * DK) / 64, bar_c);
+      tma::load_3d(Ks, &maps.k, cm.row, (hq * DK) / 64, bar_c);
+    }
+    for (int p = 1; p < NP; ++p) {
+      tma::prefetch_2d(&maps.h, p * 64, hrow);
+      tma::prefetch_2d(&maps.dh, p * 64, hrow);
+    }
+  };
+  if (tid == 0) {
     tc5::mbar_init(bar, 1);
-    tc5::mbar_init(bar_ld, 1);
+    tc5::mbar_init(bar_a, 1);
+    tc5::mbar_init(bar_b, 1);
+    tc5::mbar_init(bar_c, 1);
     tc5::fence_mbar_init();
+    issue_loads(0);   // the first head's tiles are on their way while the CTA sets itself up
   }
+  if (warp == 1) tc5::tmem_alloc(tmem_slot, 256);
   tc5::fence_before_sync();
   __syncthreads();
   tc5::fence_after_sync();
   const uint32_t tm = *tmem_slot;
   const uint32_t TM_DQ = tm, TM_DKS = tm + 128, TM_DP = tm + 128, TM_DKI = tm;
   PhaseBarrier ph{bar, 0u, &g_dqk_timeout};
-  uint32_t ld_parity = 0;
+  uint32_t par_b = 0;
   bool failed = false;
 
   const Operand opQ{tc5::smem_addr(Qs), BT, 1};   // B of dP~^T q : (k = token, n = key dim)
@@ -95,26 +123,12 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
     const int hv = hq * G + gi;
     const bool first = gi == 0, last = gi == G - 1;
     const int hrow = (c * a.HV + hv) * DK;   // first row of this head's state snapshot in the [.., V] view
-    __syncthreads();  // previous head fully consumed (staging, gs, partials)
-    if (tid == 0) {
-      tc5::mbar_expect_tx(bar_ld, (uint32_t)((first ? 2 * BT * DK * 2 : 0) + 2 * BT * DV * 2 + 2 * DK * 128 + BT * 4));
-      tma::load_3d(Do, &maps.d_o, cm.row, (hv * DV) / 64, bar_ld);
-      tma::load_3d(Vn, &maps.vn, cm.row, (hv * DV) / 64, bar_ld);
-      tma::load_2d(Hp, &maps.h, 0, hrow, bar_ld);
-      tma::load_2d(dHp, &maps.dh, 0, hrow, bar_ld);
-      if (first) {
-        tma::load_3d(Qs, &maps.q, cm.row, (hq * DK) / 64, bar_ld);
-        tma::load_3d(Ks, &maps.k, cm.row, (hq * DK) / 64, bar_ld);
-      }
-      tma::load_1d(gs, gamma_ptr(a.gamma, c, a.HV, hv), BT * 4, bar_ld);
+    if (gi > 0) {
+      __syncthreads();  // previous head fully consumed (staging, gs, partials)
+      if (tid == 0) issue_loads(gi);
     }
-    if (!tc5::mbar_wait(bar_ld, ld_parity)) failed = true;
-    ld_parity ^= 1u;
+    if (!tc5::mbar_wait(bar_a, gi & 1)) failed = true;
     if (cm.len < BT) {   // ragged chunk: the extra rows of the boxes belong to the next sequence
-      if (first) {
-        zero_tail_rows<BT, DK>(Qs, cm.len, tid, NTHREADS);
-        zero_tail_rows<BT, DK>(Ks, cm.len, tid, NTHREADS);
-      }
       zero_tail_rows<BT, DV>(Do, cm.len, tid, NTHREADS);
       zero_tail_rows<BT, DV>(Vn, cm.len, tid, NTHREADS);
       tc5::fence_async_smem();
@@ -142,10 +156,20 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
         }
       }
     };
+    if (!tc5::mbar_wait(bar_b, par_b)) failed = true;
+    par_b ^= 1u;
     add_hd();
-    if (__syncthreads_or(!ph.wait())) { failed = true; break; }
+    if (first) {
+      if (!tc5::mbar_wait(bar_c, 0)) failed = true;
+      if (cm.len < BT) {
+        zero_tail_rows<BT, DK>(Qs, cm.len, tid, NTHREADS);
+        zero_tail_rows<BT, DK>(Ks, cm.len, tid, NTHREADS);
+      }
+    }
+    if (__syncthreads_or(failed || !ph.wait())) { failed = true; break; }
 
-    // ---- epilogue 1: dP~ -> shared; rescale do and v_new rows in place
+    // ---- epilogue 1: dP~ -> shared; rescale the rows of do in place (v_new stays as loaded: its row factor
+    //      2^(gamma_last - gamma_j) multiplies the rows of dk_state in the last epilogue instead)
     {
       float r[16];
       acc_ld32q(TM_DP, q, cs, r);
@@ -165,35 +189,31 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
     }
     for (int idx = tid; idx < BT * DV / 8; idx += NTHREADS) {
       const int row = (idx % (BT * 8)) / 8;
-      const float fo = a.scale * exp2f(gs[row]), fv = exp2f(glast - gs[row]);
+      const float fo = a.scale * exp2f(gs[row]);
       uint4* po = reinterpret_cast<uint4*>(Do + idx * 16);
-      uint4* pv = reinterpret_cast<uint4*>(Vn + idx * 16);
-      uint4 x = *po, y = *pv;
+      uint4 x = *po;
       uint32_t* xu = reinterpret_cast<uint32_t*>(&x);
-      uint32_t* yu = reinterpret_cast<uint32_t*>(&y);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        float2 p = unpack_bf16(xu[e]), q2 = unpack_bf16(yu[e]);
+        float2 p = unpack_bf16(xu[e]);
         xu[e] = pack_bf16(p.x * fo, p.y * fo);
-        yu[e] = pack_bf16(q2.x * fv, q2.y * fv);
       }
       *po = x;
-      *pv = y;
     }
     tc5::fence_async_smem();
     tc5::fence_before_sync();
     __syncthreads();
 
-    // ---- phase 2: dq = do_s h^T + dP~ k ; dk_state = v~ dh^T   (h, dh streamed by 64-column panels)
+    // ---- phase 2: dq = do_s h^T + dP~ k ; dk_state = v_new dh^T (row factor later); h, dh streamed by 64-column panels
     for (int p = 0; p < NP && !failed; ++p) {
       if (p > 0) {
         if (tid == 0) {
-          tc5::mbar_expect_tx(bar_ld, 2 * DK * 128);
-          tma::load_2d(Hp, &maps.h, p * 64, hrow, bar_ld);
-          tma::load_2d(dHp, &maps.dh, p * 64, hrow, bar_ld);
+          tc5::mbar_expect_tx(bar_b, 2 * DK * 128);
+          tma::load_2d(Hp, &maps.h, p * 64, hrow, bar_b);
+          tma::load_2d(dHp, &maps.dh, p * 64, hrow, bar_b);
         }
-        if (!tc5::mbar_wait(bar_ld, ld_parity)) failed = true;
-        ld_parity ^= 1u;
+        if (!tc5::mbar_wait(bar_b, par_b)) failed = true;
+        par_b ^= 1u;
         if (__syncthreads_or(failed)) { failed = true; break; }
       }
       if (tid == 0) {
@@ -280,6 +300,13 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
         acc_ld32q(TM_DKI, q, ck + b * 32, r[b]);
       }
       tc5::tmem_ld_wait();
+      const float e_lo = exp2f(glast - g_lo), e_hi = exp2f(glast - g_hi);
+#pragma unroll
+      for (int b = 0; b < KB; ++b)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          s[b][4 * i] *= e_lo; s[b][4 * i + 1] *= e_lo; s[b][4 * i + 2] *= e_hi; s[b][4 * i + 3] *= e_hi;
+        }
 #pragma unroll
       for (int b = 0; b < KB; ++b)
 #pragma unroll
@@ -338,7 +365,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
   if (failed && tid == 0) atomicExch(&g_dqk_timeout, 1);
   tc5::fence_before_sync();
   __syncthreads();
-  if (warp == 0) tc5::tmem_dealloc(tm, 256);
+  if (warp == 1) tc5::tmem_dealloc(tm, 256);
 }
 
 template <int DK, int DV>

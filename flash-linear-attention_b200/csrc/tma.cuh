@@ -111,6 +111,12 @@ template <int N>
 __device__ __forceinline__ void store_wait_all() {
   asm volatile("cp.async.bulk.wait_group %0;\n" ::"n"(N) : "memory");
 }
+// pull a box into L2 only (no shared-memory destination, no completion): a later load of the same box is short
+__device__ __forceinline__ void prefetch_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];\n" ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x),
+               "r"(y)
+               : "memory");
+}
 __device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
