@@ -40,7 +40,8 @@ struct DqkMaps {
 };
 
 template <int DK, int DV>
-__global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chunk_args a, const __grid_constant__ DqkMaps maps) {
+__global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chunk_args a, const __grid_constant__ DqkMaps maps,
+                                                              const int pf_dist) {
   using S = DqkSmem<DK, DV>;
   constexpr int NP = DV / 64;   // value panels
   constexpr int KB = DK / 64;   // 32-column blocks of a K-wide accumulator per warp
@@ -126,6 +127,18 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
     if (gi > 0) {
       __syncthreads();  // previous head fully consumed (staging, gs, partials)
       if (tid == 0) issue_loads(gi);
+    }
+    if (first && tid == 32) {   // while everybody waits for the first tiles
+      int c2, h2;
+      // L2 look-ahead for the CTA that will follow this one: only what its first phase waits for (a look-ahead
+      // over all of its tiles costs more in L2 evictions than it saves)
+      if (successor_cta(pf_dist, c2, h2)) {
+        const int row2 = load_chunk_meta(a.chunk_meta, c2).row, hv2 = h2 * G;
+        tma::prefetch_3d(&maps.d_o, row2, (hv2 * DV) / 64);
+        tma::prefetch_3d(&maps.vn, row2, (hv2 * DV) / 64);
+        tma::prefetch_line(gamma_ptr(a.gamma, c2, a.HV, hv2));
+        tma::prefetch_line(gamma_ptr(a.gamma, c2, a.HV, hv2) + 32);
+      }
     }
     if (!tc5::mbar_wait(bar_a, gi & 1)) failed = true;
     if (cm.len < BT) {   // ragged chunk: the extra rows of the boxes belong to the next sequence
@@ -384,7 +397,7 @@ int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
   rc |= tma::encode_bf16_2d(&m.dh, a.dh, hrows, DV, DV, DK);
   if (rc != 0) return set_error(B200GDN_ERR_CUDA, "bwd_dqk: cuTensorMapEncodeTiled failed (%d)", rc);
   dim3 grid(a.n_chunks, a.H);
-  bwd_dqk_kernel<DK, DV><<<grid, NTHREADS, S::bytes, st>>>(a, m);
+  bwd_dqk_kernel<DK, DV><<<grid, NTHREADS, S::bytes, st>>>(a, m, resident_ctas(bwd_dqk_kernel<DK, DV>, NTHREADS, S::bytes));
   return check_launch("bwd_dqk");
 }
 

@@ -118,14 +118,13 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
     tc5::fence_mbar_init();
     issue_loads(0);   // the first head's tiles are on their way while the CTA sets itself up
   }
+
   if (warp == 1) tc5::tmem_alloc(tmem_slot, 256);
   {
     // the dq/dk kernel's part of dk is read at the very end: pull it into L2 now (one 128-byte line per thread)
     const int r = tid >> 2, seg = tid & 3;
-    if (r < cm.len && seg * 32 < DK) {
-      const float* p = a.dk_part + ((row0 + r) * a.H + hq) * DK + seg * 32;
-      asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p));
-    }
+    if (r < cm.len && seg * 32 < DK) tma::prefetch_line(a.dk_part + ((row0 + r) * a.H + hq) * DK + seg * 32);
+
   }
   tc5::fence_before_sync();
   __syncthreads();

@@ -15,11 +15,10 @@ __device__ int g_dvl_timeout = 0;
 
 template <int DK, int DV>
 struct DvSmem {
-  static constexpr size_t o_q = 0;                       // Q; later the output staging tile
-  static constexpr size_t o_k = o_q + (BT * DK * 2 > BT * DV * 2 ? BT * DK * 2 : BT * DV * 2);
-  static constexpr size_t o_d = o_k + BT * DK * 2;
-  static constexpr size_t o_p = o_d + BT * DV * 2;
-  static constexpr size_t o_vec = o_p + BT * 128;
+  static constexpr size_t o_q = 0;                       // Q; once P = Q K^T is done, the bf16 P operand
+  static constexpr size_t o_k = o_q + (BT * DK * 2 > BT * 128 ? BT * DK * 2 : BT * 128);   // K; later the output staging
+  static constexpr size_t o_d = o_k + (BT * DK * 2 > BT * DV * 2 ? BT * DK * 2 : BT * DV * 2);
+  static constexpr size_t o_vec = o_d + BT * DV * 2;
   static constexpr size_t bytes = o_vec + BT * 4 + 64 + 1024;
 };
 
@@ -28,14 +27,16 @@ struct DvMaps {
 };
 
 template <int DK, int DV>
-__global__ void __launch_bounds__(NTHREADS) dv_local_kernel(const b200gdn_chunk_args a, const __grid_constant__ DvMaps maps) {
+__global__ void __launch_bounds__(NTHREADS, 4) dv_local_kernel(const b200gdn_chunk_args a, const __grid_constant__ DvMaps maps,
+                                                            const int pf_dist) {
   using S = DvSmem<DK, DV>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* Qs = smem + S::o_q;
   unsigned char* Ks = smem + S::o_k;
   unsigned char* Ds = smem + S::o_d;
-  unsigned char* Ps = smem + S::o_p;
+  unsigned char* Ps = Qs;    // Q is dead once phase 1 has completed
+  unsigned char* Stg = Ks;   // and so is K
   float* gs = reinterpret_cast<float*>(smem + S::o_vec);
   uint64_t* bar_ld = reinterpret_cast<uint64_t*>(gs + BT);
   uint64_t* bar_mma = bar_ld + 1;
@@ -48,26 +49,36 @@ __global__ void __launch_bounds__(NTHREADS) dv_local_kernel(const b200gdn_chunk_
   const ChunkMeta cm = load_chunk_meta(a.chunk_meta, c);
   const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
 
-  if (warp == 0) tc5::tmem_alloc(tmem_slot, 256);
-  if (tid == 32) {
+  if (tid == 0) {
     tc5::mbar_init(bar_ld, 1);
     tc5::mbar_init(bar_mma, 1);
     tc5::fence_mbar_init();
-  }
-  tc5::fence_before_sync();
-  __syncthreads();
-  tc5::fence_after_sync();
-  const uint32_t tm = *tmem_slot;
-  const uint32_t TM_P = tm, TM_D = tm + 64;
-  PhaseBarrier ph{bar_mma, 0u, &g_dvl_timeout};
-  bool failed = false;
-
-  if (tid == 0) {
+    // the tiles are on their way while the CTA sets itself up
     tc5::mbar_expect_tx(bar_ld, (uint32_t)(2 * BT * DK * 2 + BT * DV * 2 + BT * 4));
     tma::load_3d(Qs, &maps.q, cm.row, (hq * DK) / 64, bar_ld);
     tma::load_3d(Ks, &maps.k, cm.row, (hq * DK) / 64, bar_ld);
     tma::load_3d(Ds, &maps.d_o, cm.row, (hv * DV) / 64, bar_ld);
     tma::load_1d(gs, gamma_ptr(a.gamma, c, a.HV, hv), BT * 4, bar_ld);
+  }
+  if (warp == 1) tc5::tmem_alloc(tmem_slot, 128);
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tm = *tmem_slot;
+  const uint32_t TM_P = tm, TM_D = tm;   // P has left tensor memory before dv is accumulated
+  PhaseBarrier ph{bar_mma, 0u, &g_dvl_timeout};
+  bool failed = false;
+
+  if (tid == 32) {   // while everybody waits for the tiles
+    int c2, h2;
+    if (successor_cta(pf_dist, c2, h2)) {   // L2 look-ahead for the CTA that will follow this one
+      const int row2 = load_chunk_meta(a.chunk_meta, c2).row, hq2 = h2 / G;
+      tma::prefetch_3d(&maps.q, row2, (hq2 * DK) / 64);
+      tma::prefetch_3d(&maps.k, row2, (hq2 * DK) / 64);
+      tma::prefetch_3d(&maps.d_o, row2, (h2 * DV) / 64);
+      tma::prefetch_line(gamma_ptr(a.gamma, c2, a.HV, h2));
+      tma::prefetch_line(gamma_ptr(a.gamma, c2, a.HV, h2) + 32);
+    }
   }
   if (!tc5::mbar_wait(bar_ld, 0)) failed = true;
 
@@ -123,28 +134,28 @@ __global__ void __launch_bounds__(NTHREADS) dv_local_kernel(const b200gdn_chunk_
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int col = b * 32 + i * 8 + 2 * t;
-          *swz_ptr32(Qs, r_lo, col, BT) = pack_bf16(r[b][4 * i], r[b][4 * i + 1]);
-          *swz_ptr32(Qs, r_hi, col, BT) = pack_bf16(r[b][4 * i + 2], r[b][4 * i + 3]);
+          *swz_ptr32(Stg, r_lo, col, BT) = pack_bf16(r[b][4 * i], r[b][4 * i + 1]);
+          *swz_ptr32(Stg, r_hi, col, BT) = pack_bf16(r[b][4 * i + 2], r[b][4 * i + 3]);
         }
       tc5::fence_async_smem();
       tc5::fence_before_sync();
       __syncthreads();
       if (cm.len == BT) {
         if (tid == 0) {
-          tma::store_3d(&maps.dv2, cm.row, (hv * DV) / 64, Qs);
+          tma::store_3d(&maps.dv2, cm.row, (hv * DV) / 64, Stg);
           tma::store_commit();
           tma::store_wait_all<0>();
         }
       } else {
         store_tile_swz<BT, DV, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.dv2) + ((int64_t)cm.row * a.HV + hv) * DV,
-                                         (int64_t)a.HV * DV, Qs, cm.len, tid);
+                                         (int64_t)a.HV * DV, Stg, cm.len, tid);
       }
     }
   }
   if (failed && tid == 0) atomicExch(&g_dvl_timeout, 1);
   tc5::fence_before_sync();
   __syncthreads();
-  if (warp == 0) tc5::tmem_dealloc(tm, 256);
+  if (warp == 1) tc5::tmem_dealloc(tm, 128);
 }
 
 template <int DK, int DV>
@@ -160,7 +171,7 @@ int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
   rc |= tma::encode_bf16_panels(&m.dv2, a.dv2, a.rows, pv, pv, BT, DV / 64);
   if (rc != 0) return set_error(B200GDN_ERR_CUDA, "dv_local: cuTensorMapEncodeTiled failed (%d)", rc);
   dim3 grid(a.n_chunks, a.HV);
-  dv_local_kernel<DK, DV><<<grid, NTHREADS, S::bytes, st>>>(a, m);
+  dv_local_kernel<DK, DV><<<grid, NTHREADS, S::bytes, st>>>(a, m, resident_ctas(dv_local_kernel<DK, DV>, NTHREADS, S::bytes));
   return check_launch("dv_local");
 }
 

@@ -363,6 +363,18 @@ __device__ __forceinline__ void load_gamma_async(float* gs, const float* gamma, 
   if (tid < BT) cp_async4(gs + tid, gamma_ptr(gamma, c, HV, hv) + tid);
 }
 
+// Look-ahead for the one-CTA-per-(chunk, head) kernels.  CTAs are dispatched in launch order (x fastest), so the
+// CTA that will take this one's place on the device is `dist` CTAs further on (dist = CTAs resident at once).
+// A CTA pulls that successor's tiles into L2 as it starts; the successor's own loads then see L2 latency
+// instead of DRAM latency.  Returns false when there is no successor.
+__device__ __forceinline__ bool successor_cta(int dist, int& c2, int& h2) {
+  const int nxt = blockIdx.y * gridDim.x + blockIdx.x + dist;
+  if (nxt >= (int)(gridDim.x * gridDim.y)) return false;
+  c2 = nxt % gridDim.x;
+  h2 = nxt / gridDim.x;
+  return true;
+}
+
 }  // namespace gdn
 
 // ---- host-side launch plumbing (one translation unit per kernel, collected by api.cu) ---------------
@@ -384,5 +396,19 @@ int ensure_smem(Kern kern, size_t bytes) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
   if (e != cudaSuccess) return set_error(B200GDN_ERR_CUDA, "cudaFuncSetAttribute(%zu B): %s", bytes, cudaGetErrorString(e));
   return 0;
+}
+
+// CTAs of `kern` resident on the whole device at once (SMs x CTAs per SM); cached per instantiation and device.
+template <typename Kern>
+int resident_ctas(Kern kern, int threads, size_t smem) {
+  static int cached[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+  int per_sm = 1, sms = 148;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 148;
+  if (dev >= 0 && dev < 64) cached[dev] = per_sm * sms;
+  return per_sm * sms;
 }
 }  // namespace gdn

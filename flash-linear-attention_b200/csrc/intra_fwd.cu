@@ -78,7 +78,8 @@ __device__ __forceinline__ void merge_step2(const float* T, float* Af, int r0, i
 }
 
 template <int DK, int DV>
-__global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_chunk_args a, const __grid_constant__ IntraMaps maps) {
+__global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_chunk_args a, const __grid_constant__ IntraMaps maps,
+                                                                const int pf_dist) {
   using S = IntraSmem<DK, DV>;
   constexpr int KB = DK / 64, VB = DV / 64;
   extern __shared__ unsigned char smem_raw[];
@@ -117,6 +118,7 @@ __global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_ch
     tc5::fence_mbar_init();
     tc5::mbar_expect_tx(bar_k, (uint32_t)(BT * DK * 2));
     tma::load_3d(Ks, &maps.k, cm.row, (hq * DK) / 64, bar_k);
+    tma::prefetch_3d(&maps.v, cm.row, (hv * DV) / 64);   // V is loaded late (it reuses L's place): have it in L2 by then
   }
   if (warp == 1) tc5::tmem_alloc(tmem_slot, 128);
   if (tid >= 64 && tid < 128) {
@@ -143,6 +145,13 @@ __global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_ch
       if (lane >= o) s += y;
     }
     gam[tid] = s;
+  }
+  if (tid == 128) {   // while everybody waits for the K tile
+    int c2, h2;
+    if (successor_cta(pf_dist, c2, h2)) {   // L2 look-ahead for the CTA that will follow this one
+      const int row2 = load_chunk_meta(a.chunk_meta, c2).row;
+      tma::prefetch_3d(&maps.k, row2, ((h2 / G) * DK) / 64);
+    }
   }
   if (!tc5::mbar_wait(bar_k, 0)) failed = true;
   if (cm.len < BT) {
@@ -354,7 +363,7 @@ int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
   rc |= tma::encode_bf16_panels(&m.u, a.u, a.rows, pv, pv, BT, DV / 64);
   if (rc != 0) return set_error(B200GDN_ERR_CUDA, "intra_fwd: cuTensorMapEncodeTiled failed (%d)", rc);
   dim3 grid(a.n_chunks, a.HV);
-  intra_fwd_kernel<DK, DV><<<grid, NTHREADS, S::bytes, st>>>(a, m);
+  intra_fwd_kernel<DK, DV><<<grid, NTHREADS, S::bytes, st>>>(a, m, resident_ctas(intra_fwd_kernel<DK, DV>, NTHREADS, S::bytes));
   return check_launch("intra_fwd");
 }
 

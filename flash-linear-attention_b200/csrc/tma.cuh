@@ -117,6 +117,14 @@ __device__ __forceinline__ void prefetch_2d(const CUtensorMap* map, int x, int y
                "r"(y)
                : "memory");
 }
+// the same for a box of the panel view (row y, first panel z)
+__device__ __forceinline__ void prefetch_3d(const CUtensorMap* map, int y, int z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];\n" ::"l"(reinterpret_cast<uint64_t>(map)),
+               "r"(0), "r"(y), "r"(z)
+               : "memory");
+}
+// one 128-byte line of plain global memory into L2
+__device__ __forceinline__ void prefetch_line(const void* p) { asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p)); }
 __device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
