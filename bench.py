@@ -43,6 +43,33 @@ STAGE_FLOPS = {
     'bwd_dqk': 4 * K * V + 2 * BT * (V + 2 * K),                       # dP, do h^T, v dh^T, dP k, dP^T q
     'bwd_wy': 2 * K * V + 2 * BT * (5 * K + 2 * V + 2 * BT),           # dv2 h^T + WY backward
 }
+
+
+def stage_bytes(R, C, NS):
+    """Algorithmic HBM bytes of every kernel of one fwd+bwd step: each operand read once, each result written
+    once (R token rows, C chunks, NS sequences; bf16 tiles, fp32 gates / row vectors / dk partials)."""
+    qk, wv = R * H * K * 2, R * HV * V * 2           # q or k ; v, u, v_new, do, dv2, o, dv
+    w = R * HV * K * 2
+    a_ = R * HV * BT * 2
+    snap = C * HV * K * V * 2                         # h or dh snapshots
+    st32 = NS * HV * K * V * 4                        # h0, ht, dht, dh0
+    gam, vec = C * HV * BT * 4, R * HV * 4
+    dkp = R * H * K * 4
+    return {
+        'intra_fwd': qk + wv + 2 * vec + a_ + w + wv + gam,
+        'scan_fwd': w + qk + wv + gam + st32 + snap + wv + st32,
+        'out_fwd': 2 * qk + wv + snap + gam + wv,
+        'dv_local': 2 * qk + wv + gam + wv,
+        'scan_bwd': 2 * qk + w + 2 * wv + gam + st32 + wv + snap + st32,
+        'bwd_dqk': 2 * qk + 2 * wv + 2 * snap + gam + qk + dkp + vec,
+        'bwd_wy': qk + 2 * wv + a_ + snap + gam + 2 * vec + dkp + qk + wv + 2 * vec,
+    }
+
+
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the headline workload, from the
+# ncu capture summarised in profiles/chunk_fwd_bwd_B4_T4096_H16_D128_tcgen05.md; None = not captured.
+NCU_TRAFFIC_BYTES = {}
+
 F_FWD = sum(STAGE_FLOPS[s] for s in ('intra_fwd', 'scan_fwd', 'out_fwd'))
 F_BWD = sum(STAGE_FLOPS[s] for s in ('dv_local', 'scan_bwd', 'bwd_dqk', 'bwd_wy'))
 assert F_FWD == 180224 and F_BWD == 409600
@@ -316,7 +343,16 @@ def main():
         e2e_value = tokens * args.steps / (ms_e2e * 1e-3)
         tok_heads = B * T * HV
         top = max(stages, key=lambda n: stages[n])
-        achieved = tok_heads * STAGE_FLOPS[top] / (stages[top] * 1e-3) / 1e12
+        n_chunks = B * (T // BT)
+        sbytes = stage_bytes(B * T, n_chunks, B)
+        per_stage = {}
+        for n, t_ms in stages.items():
+            gbs = sbytes[n] / (t_ms * 1e-3) / 1e9
+            tfs = tok_heads * STAGE_FLOPS[n] / (t_ms * 1e-3) / 1e12
+            per_stage[n] = {'ms': t_ms, 'GB/s': gbs, 'hbm_frac': gbs / peaks['hbm'], 'TFLOP/s': tfs,
+                            'tensor_frac': tfs / peaks['bf16']}
+        # every kernel of this path moves ~0.3-0.7 GB for 20-45 GFLOP: the HBM floor is 3-4x the tensor floor
+        top_gbs = per_stage[top]['GB/s']
         step_tflops = tok_heads * (F_FWD + F_BWD) * args.steps / (ms * 1e-3) / 1e12
         line = {
             'metric': METRIC, 'value': value, 'unit': 'tokens/s', 'n_gpus': world, 'steps': args.steps,
@@ -327,9 +363,11 @@ def main():
                        'parallelism': f'dp{world} (batch/head shard, no collective)'},
             'pct_tensor_peak': 100.0 * step_tflops / world / peaks['bf16'],
             'step_tflops_per_gpu': step_tflops / world,
-            'roofline': {'kernel': top, 'bound': 'tensor', 'achieved': achieved, 'peak': peaks['bf16'], 'unit': 'TFLOP/s',
-                         'frac': achieved / peaks['bf16'], 'traffic': None, 'peak_source': peaks['source'],
-                         'stage_ms': stages},
+            'roofline': {'kernel': top, 'bound': 'hbm', 'achieved': top_gbs, 'peak': peaks['hbm'], 'unit': 'GB/s',
+                         'frac': top_gbs / peaks['hbm'], 'traffic': NCU_TRAFFIC_BYTES.get(top),
+                         'algorithmic_bytes': sbytes[top], 'peak_source': peaks['source'],
+                         'step_hbm_frac': sum(sbytes.values()) / (sum(stages.values()) * 1e-3) / 1e9 / peaks['hbm'],
+                         'stage_ms': stages, 'stages': per_stage},
             'e2e': {'value': e2e_value, 'unit': 'tokens/s', 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
                     'ms_per_step': ms_e2e / args.steps},
             'gpu_launches': launches,

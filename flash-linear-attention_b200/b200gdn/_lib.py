@@ -57,7 +57,7 @@ class AffineArgs(C.Structure):
 EXPORTS = (
     'b200gdn_chunk_fwd', 'b200gdn_chunk_bwd', 'b200gdn_recurrent_fwd', 'b200gdn_affine_apply',
     'b200gdn_saved_bytes', 'b200gdn_bwd_workspace_bytes', 'b200gdn_last_launch_count',
-    'b200gdn_abi_version', 'b200gdn_last_error',
+    'b200gdn_abi_version', 'b200gdn_last_error', 'b200gdn_device_status',
 )
 
 _lib = None
@@ -90,6 +90,8 @@ def load():
             fn.restype = C.c_int64
             fn.argtypes = [C.c_int32] * 6
         lib.b200gdn_last_launch_count.restype = C.c_int
+        lib.b200gdn_device_status.restype = C.c_int
+        lib.b200gdn_device_status.argtypes = []
         lib.b200gdn_abi_version.restype = C.c_int
         lib.b200gdn_last_error.restype = C.c_char_p
         if lib.b200gdn_abi_version() != ABI_VERSION:
@@ -114,6 +116,15 @@ def call(name: str, args: C.Structure, stream: int) -> None:
     if rc != 0:
         raise B200GDNError(f'{name} failed ({rc}): {lib.b200gdn_last_error().decode()}')
     _launches += lib.b200gdn_last_launch_count()
+
+
+def device_status() -> None:
+    """Synchronise the current device and raise if a bounded wait inside one of the kernels expired since the
+    last check (the flagged kernel's results are invalid)."""
+    lib = load()
+    rc = lib.b200gdn_device_status()
+    if rc != 0:
+        raise B200GDNError(f'b200gdn_device_status ({rc}): {lib.b200gdn_last_error().decode()}')
 
 
 def ptr(t):

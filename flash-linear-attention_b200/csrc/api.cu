@@ -153,6 +153,19 @@ int64_t b200gdn_bwd_workspace_bytes(int32_t rows, int32_t H, int32_t HV, int32_t
          + (HV > H ? r * H * K * 4 : 0);     /* dq_acc */
 }
 
+int b200gdn_device_status(void) {
+  struct { const char* name; int (*flag)(); } k[] = {
+      {"intra_fwd", gdn::intra_fwd_timeout_flag}, {"scan_fwd", gdn::scan_fwd_timeout_flag}, {"out_fwd", gdn::out_fwd_timeout_flag},
+      {"dv_local", gdn::dv_local_timeout_flag},   {"scan_bwd", gdn::scan_bwd_timeout_flag}, {"bwd_dqk", gdn::bwd_dqk_timeout_flag},
+      {"bwd_wy", gdn::bwd_wy_timeout_flag}};
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return gdn::set_error(B200GDN_ERR_CUDA, "device_status: %s", cudaGetErrorString(e));
+  int rc = B200GDN_OK;
+  for (auto& x : k)
+    if (x.flag()) rc = gdn::set_error(B200GDN_ERR_TIMEOUT, "%s: a bounded device wait expired; its results are invalid", x.name);
+  return rc;
+}
+
 int b200gdn_last_launch_count(void) { return gdn::g_launches; }
 int b200gdn_abi_version(void) { return B200GDN_ABI_VERSION; }
 const char* b200gdn_last_error(void) { return gdn::g_err; }

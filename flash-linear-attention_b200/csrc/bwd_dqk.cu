@@ -410,9 +410,11 @@ int launch_bwd_dqk(const b200gdn_chunk_args& a, cudaStream_t st) {
   return set_error(B200GDN_ERR_UNSUPPORTED, "bwd_dqk: K=%d V=%d not built (64/64 and 128/128 are)", a.K, a.V);
 }
 
+// Reads and clears the flag a bounded device wait raises when it expires (synchronises with the device).
 int bwd_dqk_timeout_flag() {
-  int v = 0;
+  int v = 0, zero = 0;
   cudaMemcpyFromSymbol(&v, g_dqk_timeout, sizeof(int));
+  if (v) cudaMemcpyToSymbol(g_dqk_timeout, &zero, sizeof(int));
   return v;
 }
 

@@ -465,9 +465,11 @@ int launch_bwd_wy(const b200gdn_chunk_args& a, cudaStream_t st) {
   return set_error(B200GDN_ERR_UNSUPPORTED, "bwd_wy: K=%d V=%d not built (64/64 and 128/128 are)", a.K, a.V);
 }
 
+// Reads and clears the flag a bounded device wait raises when it expires (synchronises with the device).
 int bwd_wy_timeout_flag() {
-  int v = 0;
+  int v = 0, zero = 0;
   cudaMemcpyFromSymbol(&v, g_wy_timeout, sizeof(int));
+  if (v) cudaMemcpyToSymbol(g_wy_timeout, &zero, sizeof(int));
   return v;
 }
 

@@ -183,4 +183,12 @@ int launch_dv_local(const b200gdn_chunk_args& a, cudaStream_t st) {
   return set_error(B200GDN_ERR_UNSUPPORTED, "dv_local: K=%d V=%d not built (64/64 and 128/128 are)", a.K, a.V);
 }
 
+// Reads and clears the flag a bounded device wait raises when it expires (synchronises with the device).
+int dv_local_timeout_flag() {
+  int v = 0, zero = 0;
+  cudaMemcpyFromSymbol(&v, g_dvl_timeout, sizeof(int));
+  if (v) cudaMemcpyToSymbol(g_dvl_timeout, &zero, sizeof(int));
+  return v;
+}
+
 }  // namespace gdn

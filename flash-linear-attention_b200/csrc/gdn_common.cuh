@@ -388,6 +388,13 @@ int launch_bwd_dqk(const b200gdn_chunk_args& a, cudaStream_t st);
 int launch_bwd_wy(const b200gdn_chunk_args& a, cudaStream_t st);
 int launch_recurrent(const b200gdn_recurrent_args& a, cudaStream_t st);
 int launch_affine(const b200gdn_affine_args& a, cudaStream_t st);
+int intra_fwd_timeout_flag();
+int scan_fwd_timeout_flag();
+int out_fwd_timeout_flag();
+int dv_local_timeout_flag();
+int scan_bwd_timeout_flag();
+int bwd_dqk_timeout_flag();
+int bwd_wy_timeout_flag();
 int set_error(int code, const char* fmt, ...);
 int check_launch(const char* what);
 

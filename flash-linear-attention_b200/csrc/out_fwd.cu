@@ -232,4 +232,12 @@ int launch_out_fwd(const b200gdn_chunk_args& a, cudaStream_t st) {
   return set_error(B200GDN_ERR_UNSUPPORTED, "out_fwd: K=%d V=%d not built (64/64 and 128/128 are)", a.K, a.V);
 }
 
+// Reads and clears the flag a bounded device wait raises when it expires (synchronises with the device).
+int out_fwd_timeout_flag() {
+  int v = 0, zero = 0;
+  cudaMemcpyFromSymbol(&v, g_out_timeout, sizeof(int));
+  if (v) cudaMemcpyToSymbol(g_out_timeout, &zero, sizeof(int));
+  return v;
+}
+
 }  // namespace gdn

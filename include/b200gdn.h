@@ -37,7 +37,8 @@ typedef enum b200gdn_status {
   B200GDN_ERR_BAD_ARGUMENT = -1,   /* null pointer, wrong struct size, zero size */
   B200GDN_ERR_UNSUPPORTED = -2,    /* head dimension / option not built */
   B200GDN_ERR_CUDA = -3,           /* a CUDA runtime call failed; see b200gdn_last_error() */
-  B200GDN_ERR_TOO_LARGE = -4       /* size exceeds a fixed capacity (static-scratch entry point) */
+  B200GDN_ERR_TOO_LARGE = -4,      /* size exceeds a fixed capacity (static-scratch entry point) */
+  B200GDN_ERR_TIMEOUT = -5         /* a bounded wait inside a kernel expired (b200gdn_device_status) */
 } b200gdn_status;
 
 /* stage masks: run only some kernels of a pass (unit tests and profiling); 0 means all */
@@ -163,6 +164,13 @@ int b200gdn_affine_apply(const b200gdn_affine_args* args, void* stream);
 /* Bytes of forward-saved tensors and of backward workspace for a problem (what the caller allocates). */
 int64_t b200gdn_saved_bytes(int32_t rows, int32_t H, int32_t HV, int32_t K, int32_t V, int32_t n_chunks);
 int64_t b200gdn_bwd_workspace_bytes(int32_t rows, int32_t H, int32_t HV, int32_t K, int32_t V, int32_t n_chunks);
+
+/* No counterpart in the reference (Triton kernels have no bounded waits).  Every wait inside the kernels of this
+ * library (on an mbarrier that a TMA copy or a tensor-core commit completes) gives up after a fixed number of
+ * polls, raises a flag in device memory and lets the CTA return, so that a lost completion cannot hang the GPU.
+ * This call synchronises the device, reads and clears the flags of the current device and returns B200GDN_OK or
+ * B200GDN_ERR_TIMEOUT (the results of the flagged kernel are then invalid; b200gdn_last_error() names it). */
+int b200gdn_device_status(void);
 
 /* Number of kernels the last call on this thread enqueued (bench bookkeeping). */
 int b200gdn_last_launch_count(void);

@@ -153,6 +153,9 @@ def test_determinism_and_no_uninitialised_reads():
     for n in ('o', 'ht', 'dq', 'dk', 'dv', 'dg', 'dbeta', 'dh0'):
         assert not torch.isnan(a[n]).any(), n
         assert torch.equal(a[n], b[n]), n
+    # none of the bounded device waits (mbarriers of TMA copies and tensor-core commits) expired
+    import b200gdn
+    b200gdn.device_status()
 
 
 def test_full_size_properties():
