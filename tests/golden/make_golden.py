@@ -34,7 +34,7 @@ CASES = {
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('--reference', default='/root/reference')
+    ap.add_argument('--reference', required=True, help='checkout of fla-org/flash-linear-attention (0.5.2) to import')
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     from fla.ops.cp.context import get_cp_cu_seqlens
