@@ -121,11 +121,15 @@ __global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_ch
     tma::prefetch_3d(&maps.v, cm.row, (hv * DV) / 64);   // V is loaded late (it reuses L's place): have it in L2 by then
   }
   if (warp == 1) tc5::tmem_alloc(tmem_slot, 128);
-  if (tid >= 64 && tid < 128) {
-    const int r = tid - 64;
-    const bool ok = r < cm.len;
-    graw[r] = ok ? a.g[(row0 + r) * a.HV + hv] : 0.f;
-    bet[r] = ok ? a.beta[(row0 + r) * a.HV + hv] : 0.f;
+  if (tid < BT) {   // asynchronous copies: nobody stalls on the DRAM latency of the gates before the first barrier
+    if (tid < cm.len) {
+      cp_async4(graw + tid, a.g + (row0 + tid) * a.HV + hv);
+      cp_async4(bet + tid, a.beta + (row0 + tid) * a.HV + hv);
+    } else {
+      graw[tid] = 0.f;
+      bet[tid] = 0.f;
+    }
+    cp_async_commit();
   }
   // zero the fp32 inverse (the merges and the final conversion read the untouched blocks as zeros)
   for (int i = tid; i < BT * LDF / 4; i += NTHREADS) reinterpret_cast<float4*>(Af)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -138,6 +142,7 @@ __global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_ch
 
   if (tid < BT) {
     // inclusive scan of g over the chunk: shuffle scan inside each of the two warps, carry added below
+    cp_async_wait<0>();   // this thread's own g and beta
     float s = graw[tid];
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -151,6 +156,12 @@ __global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_ch
     if (successor_cta(pf_dist, c2, h2)) {   // L2 look-ahead for the CTA that will follow this one
       const int row2 = load_chunk_meta(a.chunk_meta, c2).row;
       tma::prefetch_3d(&maps.k, row2, ((h2 / G) * DK) / 64);
+      // g and beta of a chunk are [64][HV] fp32 blocks: the HV CTAs of a chunk pull two lines each
+      const int lines = BT * a.HV * 4 / 128;
+      for (int l = h2 * 2; l < h2 * 2 + 2 && l < lines; ++l) {
+        tma::prefetch_line(a.g + (int64_t)row2 * a.HV + l * 32);
+        tma::prefetch_line(a.beta + (int64_t)row2 * a.HV + l * 32);
+      }
     }
   }
   if (!tc5::mbar_wait(bar_k, 0)) failed = true;
@@ -174,12 +185,12 @@ __global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_ch
       bge[tid] = bet[tid] * exp2f(gm);
       a.gamma[((int64_t)c * a.HV + hv) * BT + tid] = gm;   // padded rows carry the last valid value (their g is 0)
     }
-    if (__syncthreads_or(!ph.wait())) failed = true;
+    if (!ph.sync_wait()) failed = true;
   }
 
   if (!failed) {
     // ---- L = strict_tril(beta_i <k_i,k_j> 2^(gamma_i - gamma_j)) in fp32
-    {
+    if (q * 16 + 15 > cs) {   // a block entirely above the diagonal is never read by the solve
       float r[16];
       acc_ld32q(tm, q, cs, r);
       tc5::tmem_ld_wait();
@@ -278,7 +289,7 @@ __global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_ch
       zero_tail_rows<BT, DV>(Vs, cm.len, tid, NTHREADS);
       tc5::fence_async_smem();
     }
-    if (__syncthreads_or(failed || !ph.wait())) {
+    if (!ph.sync_wait(failed)) {
       failed = true;
     } else {
       const int ck = hc * (DK / 2), cv = hc * (DV / 2);
@@ -303,7 +314,7 @@ __global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_ch
           *swz_ptr32(Ks, r_hi, col, BT) = pack_bf16(rw[b][4 * i + 2], rw[b][4 * i + 3]);
         }
       tc5::fence_async_smem();
-      if (__syncthreads_or(!ph.wait())) {
+      if (!ph.sync_wait()) {
         failed = true;
       } else {
         if (cm.len == BT) {

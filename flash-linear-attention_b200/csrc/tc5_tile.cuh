@@ -125,6 +125,16 @@ struct PhaseBarrier {
     tc5::fence_after_sync();
     return ok;
   }
+  // CTA-wide form: the first warp polls the barrier, the others sleep in the hardware barrier instead of
+  // spending issue slots on the poll; returns false if the wait expired or any thread passed `bad`.
+  // (Pays in kernels whose other resident CTAs are issue-bound; measured slower in the two big backward kernels.)
+  __device__ __forceinline__ bool sync_wait(bool bad = false) {
+    if (threadIdx.x < 32 && !bad) bad = !tc5::mbar_wait(bar, parity);
+    parity ^= 1u;
+    const int any_bad = __syncthreads_or(bad);
+    tc5::fence_after_sync();
+    return !any_bad;
+  }
 };
 
 }  // namespace gdn
