@@ -216,7 +216,7 @@ def cpu_baseline(seconds_budget=20.0, threads=None):
     from oracle.gdn_oracle import make_inputs, naive_recurrent
     threads = threads or os.cpu_count() or 1
     torch.set_num_threads(threads)
-    Bs, Ts, Hs = 1, 256, 2
+    Bs, Ts, Hs = 1, 1024, 4
     d = make_inputs(Bs, Ts, Hs, Hs, K, V, seed=0)
 
     def one():
