@@ -90,3 +90,33 @@ def test_recurrent_errors():
     o, _ = fused_recurrent_gated_delta_rule(q.requires_grad_(True), q, q, g)
     with pytest.raises(NotImplementedError):
         o.sum().backward()
+
+
+@pytest.mark.parametrize('B', [1, 16, 256])
+def test_decode_sweep_single_token_steps(B):
+    """Decode sweep of the long-context configuration: single-token steps at batch 1..256 with a
+    [B,16,128,128] fp32 state, three consecutive steps with the state carried in place; checked against
+    the delta-rule update written out in plain fp32 torch on the same device."""
+    from b200gdn import fused_recurrent_gated_delta_rule
+    dev = 'cuda'
+    H, K, V = 16, 128, 128
+    gen = torch.Generator(device=dev).manual_seed(B)
+    state = torch.randn(B, H, K, V, device=dev, generator=gen) * 0.1
+    ref = state.clone()
+    scale = K ** -0.5
+    for step in range(3):
+        q = torch.nn.functional.normalize(torch.randn(B, 1, H, K, device=dev, generator=gen), dim=-1)
+        k = torch.nn.functional.normalize(torch.randn(B, 1, H, K, device=dev, generator=gen), dim=-1)
+        v = torch.randn(B, 1, H, V, device=dev, generator=gen)
+        g = torch.nn.functional.logsigmoid(torch.randn(B, 1, H, device=dev, generator=gen))
+        beta = torch.sigmoid(torch.randn(B, 1, H, device=dev, generator=gen))
+        o, ht = fused_recurrent_gated_delta_rule(q, k, v, g, beta=beta, initial_state=state, output_final_state=True,
+                                                 inplace_state=True)
+        assert ht.data_ptr() == state.data_ptr()
+        # S <- S e^g ; u = beta (v - S^T k) ; S <- S + k u^T ; o = scale S^T q      (fla/ops/gated_delta_rule/naive.py:41-60)
+        ref = ref * g[:, 0, :, None, None].exp()
+        u = (v[:, 0] - torch.einsum('bhkv,bhk->bhv', ref, k[:, 0])) * beta[:, 0, :, None]
+        ref = ref + torch.einsum('bhk,bhv->bhkv', k[:, 0], u)
+        o_ref = torch.einsum('bhkv,bhk->bhv', ref, q[:, 0]) * scale
+        O.assert_close(f'o step {step}', o_ref.cpu(), o[:, 0].cpu(), 1e-5)
+        O.assert_close(f'state step {step}', ref.cpu(), state.cpu(), 1e-5)
