@@ -309,29 +309,56 @@ def main():
     ms = e0.elapsed_time(e1)
     launches = b200gdn.launch_count() - launches0
 
-    # end to end: pinned host buffers in, all results back to the host, every step
-    out_host = {n: torch.empty_like(host[n]).pin_memory() for n in ('q', 'k', 'v', 'g', 'beta')}
-    o_host = torch.empty(B, T, HV, V, dtype=torch.bfloat16).pin_memory()
+    # end to end: every step copies its inputs from pinned host memory and all of its results (o and the five
+    # gradients) back to pinned host memory.  The three legs run on three streams over three buffer slots, so the copy
+    # of step i+1 and the read-back of step i-1 overlap the kernels of step i (PCIe is full duplex); a step's kernels
+    # still wait for its own inputs and its read-back for its own results.
+    NSLOT = 3
+    out_host = [{n: torch.empty_like(host[n]).pin_memory() for n in ('q', 'k', 'v', 'g', 'beta')} for _ in range(NSLOT)]
+    o_host = [torch.empty(B, T, HV, V, dtype=torch.bfloat16).pin_memory() for _ in range(NSLOT)]
+    dev_in = [{n: torch.empty_like(x, device=dev) for n, x in host.items()} for _ in range(NSLOT)]
     h2d = sum(x.numel() * x.element_size() for x in host.values())
-    d2h = sum(x.numel() * x.element_size() for x in out_host.values()) + o_host.numel() * 2
+    d2h = sum(x.numel() * x.element_size() for x in out_host[0].values()) + o_host[0].numel() * 2
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
 
-    def step_e2e():
-        dbatch = {n: x.to(dev, non_blocking=True) for n, x in host.items()}
-        o, leaves = step_device(dbatch, chunk_gated_delta_rule)
-        o_host.copy_(o, non_blocking=True)
-        for n, leaf in zip(('q', 'k', 'v', 'g', 'beta'), leaves):
-            out_host[n].copy_(leaf.grad, non_blocking=True)
+    def run_e2e(n_steps):
+        """Returns device milliseconds from the first copy-in to the last copy-out."""
         torch.cuda.synchronize(dev)
-    for _ in range(3):
-        step_e2e()
+        ev_in = [None] * n_steps
+        ev_comp = [None] * n_steps
+        ev_out = [None] * n_steps
+        keep = [None] * NSLOT
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(s_in)
+        for i in range(n_steps):
+            slot = i % NSLOT
+            if i >= NSLOT:
+                s_in.wait_event(ev_comp[i - NSLOT])     # the slot's previous inputs have been consumed
+                ev_out[i - NSLOT].synchronize()         # and its previous results are on the host: drop them
+            with torch.cuda.stream(s_in):
+                for n, x in host.items():
+                    dev_in[slot][n].copy_(x, non_blocking=True)
+                ev_in[i] = torch.cuda.Event()
+                ev_in[i].record(s_in)
+            stream.wait_event(ev_in[i])
+            o, leaves = step_device(dev_in[slot], chunk_gated_delta_rule)
+            ev_comp[i] = torch.cuda.Event()
+            ev_comp[i].record(stream)
+            keep[slot] = (o, leaves)                    # alive until the read-back below has finished
+            s_out.wait_event(ev_comp[i])
+            with torch.cuda.stream(s_out):
+                o_host[slot].copy_(o, non_blocking=True)
+                for n, leaf in zip(('q', 'k', 'v', 'g', 'beta'), leaves):
+                    out_host[slot][n].copy_(leaf.grad, non_blocking=True)
+                ev_out[i] = torch.cuda.Event()
+                ev_out[i].record(s_out)
+        t1.record(s_out)
+        torch.cuda.synchronize(dev)
+        return t0.elapsed_time(t1)
+    run_e2e(3)
     barrier()
-    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2.record(stream)
-    for _ in range(args.steps):
-        step_e2e()
-    e3.record(stream)
+    ms_e2e = run_e2e(args.steps)
     barrier()
-    ms_e2e = e2.elapsed_time(e3)
     clocks = sampler.stop() if rank == 0 else None
 
     if world > 1:
@@ -372,7 +399,8 @@ def main():
                          'step_hbm_frac': sum(sbytes.values()) / (sum(stages.values()) * 1e-3) / 1e9 / peaks['hbm'],
                          'stage_ms': stages, 'stages': per_stage},
             'e2e': {'value': e2e_value, 'unit': 'tokens/s', 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
-                    'ms_per_step': ms_e2e / args.steps},
+                    'ms_per_step': ms_e2e / args.steps,
+                    'pipeline': 'copy-in, kernels and copy-out of consecutive steps overlap on three streams (3 buffer slots)'},
             'gpu_launches': launches,
             'clocks': clocks,
         }
