@@ -46,6 +46,21 @@ class RecurrentArgs(C.Structure):
     ]
 
 
+PREP_L2NORM, PREP_GATE, PREP_BETA_SIGMOID, PREP_NEG_EIGVAL = 1, 2, 4, 8
+PREP_PART_ROWS = 4096
+
+
+class PrepArgs(C.Structure):
+    _fields_ = [
+        ('struct_bytes', C.c_int32), ('rows', C.c_int32), ('H', C.c_int32), ('HV', C.c_int32), ('K', C.c_int32),
+        ('flags', C.c_uint32), ('qk_dtype', C.c_int32), ('gb_dtype', C.c_int32),
+        ('q', _p), ('k', _p), ('g', _p), ('beta', _p), ('A_log', _p), ('dt_bias', _p),
+        ('qn', _p), ('kn', _p), ('rstd_q', _p), ('rstd_k', _p), ('g_out', _p), ('beta_out', _p),
+        ('dqn', _p), ('dkn', _p), ('dg', _p), ('dbeta', _p),
+        ('dq', _p), ('dk', _p), ('dg_raw', _p), ('dbeta_raw', _p), ('dA_log', _p), ('ddt_bias', _p), ('partials', _p),
+    ]
+
+
 class AffineArgs(C.Structure):
     _fields_ = [
         ('struct_bytes', C.c_int32), ('HV', C.c_int32), ('K', C.c_int32), ('V', C.c_int32),
@@ -57,7 +72,7 @@ class AffineArgs(C.Structure):
 EXPORTS = (
     'b200gdn_chunk_fwd', 'b200gdn_chunk_bwd', 'b200gdn_recurrent_fwd', 'b200gdn_affine_apply',
     'b200gdn_saved_bytes', 'b200gdn_bwd_workspace_bytes', 'b200gdn_last_launch_count',
-    'b200gdn_abi_version', 'b200gdn_last_error', 'b200gdn_device_status',
+    'b200gdn_abi_version', 'b200gdn_last_error', 'b200gdn_device_status', 'b200gdn_prep_fwd', 'b200gdn_prep_bwd',
 )
 
 _lib = None
@@ -81,7 +96,8 @@ def load():
                 f'{LIB_PATH} is missing: build it with `make -C flash-linear-attention_b200/csrc` '
                 '(or __graft_entry__.build()). There is no fallback path.')
         lib = C.CDLL(LIB_PATH)
-        for name in ('b200gdn_chunk_fwd', 'b200gdn_chunk_bwd', 'b200gdn_recurrent_fwd', 'b200gdn_affine_apply'):
+        for name in ('b200gdn_chunk_fwd', 'b200gdn_chunk_bwd', 'b200gdn_recurrent_fwd', 'b200gdn_affine_apply',
+                     'b200gdn_prep_fwd', 'b200gdn_prep_bwd'):
             fn = getattr(lib, name)
             fn.restype = C.c_int
             fn.argtypes = [C.c_void_p, C.c_void_p]

@@ -10,7 +10,6 @@ import warnings
 from typing import Optional
 
 import torch
-import torch.nn.functional as F
 
 from . import _lib
 from .index import tables_for
@@ -22,18 +21,109 @@ def _stream(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
-def _l2norm(x: torch.Tensor) -> torch.Tensor:
-    """x * rsqrt(sum x^2 + 1e-6) in fp32, result in x.dtype (fla/modules/l2norm.py:84-109)."""
-    xf = x.float()
-    return (xf * torch.rsqrt(xf.square().sum(-1, keepdim=True) + 1e-6)).to(x.dtype)
+_DTYPE_CODE = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 
 
-def _gate(g: torch.Tensor, A_log: torch.Tensor, dt_bias: Optional[torch.Tensor]) -> torch.Tensor:
-    """-exp(A_log) * softplus(g + dt_bias) in fp32 (fla/ops/gated_delta_rule/gate.py:21-46)."""
-    g = g.float()
-    if dt_bias is not None:
-        g = g + dt_bias.float()
-    return -A_log.float().exp() * F.softplus(g)
+class LayerOptionsFunction(torch.autograd.Function):
+    """The three options fla.layers.GatedDeltaNet turns on (fla/layers/gated_deltanet.py:309-325), computed by
+    b200gdn_prep_fwd / b200gdn_prep_bwd: q, k L2-normalised to bf16 (fla/modules/l2norm.py:84-144), the gate
+    ``-exp(A_log) softplus(g + dt_bias)`` (fla/ops/gated_delta_rule/gate.py:63-158, with dA_log and ddt_bias) and
+    ``beta = s sigmoid(beta)`` (fla/ops/common/gate.py:18-50).  Returns what the chunk kernels consume."""
+
+    @staticmethod
+    def forward(ctx, q, k, g, beta, A_log, dt_bias, flags):
+        dev = q.device
+        with torch.cuda.device(dev):
+            a = _lib.PrepArgs()
+            a.rows, a.H, a.K = q.shape[0] * q.shape[1], q.shape[2], q.shape[3]
+            a.HV = g.shape[-1]
+            a.flags = flags
+            qn, kn, g_out, beta_out = q, k, g, beta
+            rstd_q = rstd_k = None
+            if flags & _lib.PREP_L2NORM:
+                if q.dtype not in _DTYPE_CODE or k.dtype != q.dtype:
+                    raise _lib.B200GDNError(f'q/k dtypes {q.dtype}/{k.dtype} are not supported by the L2-norm option')
+                q, k = q.contiguous(), k.contiguous()
+                a.qk_dtype = _DTYPE_CODE[q.dtype]
+                qn, kn = (torch.empty(q.shape, dtype=torch.bfloat16, device=dev) for _ in range(2))
+                rstd_q, rstd_k = (torch.empty(q.shape[:-1], dtype=torch.float32, device=dev) for _ in range(2))
+                a.q, a.k, a.qn, a.kn = q.data_ptr(), k.data_ptr(), qn.data_ptr(), kn.data_ptr()
+                a.rstd_q, a.rstd_k = rstd_q.data_ptr(), rstd_k.data_ptr()
+            gb_in = (g.dtype if flags & _lib.PREP_GATE else beta.dtype)
+            if (flags & _lib.PREP_GATE) and (flags & _lib.PREP_BETA_SIGMOID) and g.dtype != beta.dtype:
+                gb_in = torch.float32
+            if gb_in not in _DTYPE_CODE:
+                gb_in = torch.float32
+            a.gb_dtype = _DTYPE_CODE[gb_in]
+            if flags & _lib.PREP_GATE:
+                g = g.to(gb_in).contiguous()
+                A_log_f = A_log.detach().float().contiguous()
+                bias_f = None if dt_bias is None else dt_bias.detach().float().contiguous()
+                g_out = torch.empty(g.shape, dtype=torch.float32, device=dev)
+                a.g, a.A_log, a.dt_bias, a.g_out = g.data_ptr(), A_log_f.data_ptr(), _lib.ptr(bias_f), g_out.data_ptr()
+            else:
+                A_log_f = bias_f = None
+            if flags & _lib.PREP_BETA_SIGMOID:
+                beta = beta.to(gb_in).contiguous()
+                beta_out = torch.empty(beta.shape, dtype=torch.float32, device=dev)
+                a.beta, a.beta_out = beta.data_ptr(), beta_out.data_ptr()
+            _lib.call('b200gdn_prep_fwd', a, _stream(q))
+        ctx.flags, ctx.gb_in = flags, gb_in
+        ctx.in_dtypes = (g.dtype, beta.dtype)
+        ctx.has_bias = dt_bias is not None
+        ctx.param_dtypes = (None if A_log is None else A_log.dtype, None if dt_bias is None else dt_bias.dtype)
+        ctx.save_for_backward(q, k, rstd_q, rstd_k, g, beta, A_log_f, bias_f)
+        return qn, kn, g_out, beta_out
+
+    @staticmethod
+    def backward(ctx, dqn, dkn, dg, dbeta):
+        q, k, rstd_q, rstd_k, g, beta, A_log_f, bias_f = ctx.saved_tensors
+        flags = ctx.flags
+        dev = q.device
+        dq, dk, dg_raw, dbeta_raw, dA_log, ddt_bias = dqn, dkn, dg, dbeta, None, None
+        with torch.cuda.device(dev):
+            a = _lib.PrepArgs()
+            a.rows, a.H, a.K = q.shape[0] * q.shape[1], q.shape[2], q.shape[3]
+            a.HV = g.shape[-1]
+            a.flags = 0
+            keep = []
+            if (flags & _lib.PREP_L2NORM) and dqn is not None and dkn is not None:
+                a.flags |= _lib.PREP_L2NORM
+                a.qk_dtype = _DTYPE_CODE[q.dtype]
+                dqn, dkn = dqn.to(torch.bfloat16).contiguous(), dkn.to(torch.bfloat16).contiguous()
+                dq, dk = torch.empty_like(q), torch.empty_like(k)
+                a.q, a.k, a.rstd_q, a.rstd_k = q.data_ptr(), k.data_ptr(), rstd_q.data_ptr(), rstd_k.data_ptr()
+                a.dqn, a.dkn, a.dq, a.dk = dqn.data_ptr(), dkn.data_ptr(), dq.data_ptr(), dk.data_ptr()
+            a.gb_dtype = _DTYPE_CODE[ctx.gb_in]
+            if (flags & _lib.PREP_GATE) and dg is not None:
+                a.flags |= _lib.PREP_GATE
+                dg = dg.float().contiguous()
+                dg_raw = torch.empty(g.shape, dtype=ctx.gb_in, device=dev)
+                n_part = (a.rows + _lib.PREP_PART_ROWS - 1) // _lib.PREP_PART_ROWS
+                partials = torch.empty(n_part, 2, a.HV, dtype=torch.float32, device=dev)
+                dA_log = torch.empty(a.HV, dtype=torch.float32, device=dev)
+                ddt_bias = torch.empty(a.HV, dtype=torch.float32, device=dev) if ctx.has_bias else None
+                a.g, a.A_log, a.dt_bias = g.data_ptr(), A_log_f.data_ptr(), _lib.ptr(bias_f)
+                a.dg, a.dg_raw, a.partials = dg.data_ptr(), dg_raw.data_ptr(), partials.data_ptr()
+                a.dA_log, a.ddt_bias = dA_log.data_ptr(), _lib.ptr(ddt_bias)
+                keep += [partials]
+            if (flags & _lib.PREP_BETA_SIGMOID) and dbeta is not None:
+                a.flags |= _lib.PREP_BETA_SIGMOID | (flags & _lib.PREP_NEG_EIGVAL)
+                dbeta = dbeta.float().contiguous()
+                dbeta_raw = torch.empty(beta.shape, dtype=ctx.gb_in, device=dev)
+                a.beta, a.dbeta, a.dbeta_raw = beta.data_ptr(), dbeta.data_ptr(), dbeta_raw.data_ptr()
+            if a.flags:
+                _lib.call('b200gdn_prep_bwd', a, _stream(q))
+        g_dtype, beta_dtype = ctx.in_dtypes
+        if dg_raw is not None and dg_raw.dtype != g_dtype:
+            dg_raw = dg_raw.to(g_dtype)
+        if dbeta_raw is not None and dbeta_raw.dtype != beta_dtype:
+            dbeta_raw = dbeta_raw.to(beta_dtype)
+        if dA_log is not None:
+            dA_log = dA_log.to(ctx.param_dtypes[0])
+        if ddt_bias is not None:
+            ddt_bias = ddt_bias.to(ctx.param_dtypes[1])
+        return dq, dk, dg_raw, dbeta_raw, dA_log, ddt_bias, None
 
 
 def new_chunk_args(q, k, v, scale, tables) -> _lib.ChunkArgs:
@@ -202,14 +292,15 @@ def chunk_gated_delta_rule(
         raise _lib.B200GDNError(f'head dimensions K={q.shape[-1]}, V={v.shape[-1]} are not built; '
                                 f'supported: {_SUPPORTED_HEAD_DIMS}')
 
-    # The three options the layer turns on (fla/layers/gated_deltanet.py:309-325).  They are cheap
-    # element-wise pre-processing; torch autograd differentiates them.
-    if use_qk_l2norm_in_kernel:
-        q, k = _l2norm(q), _l2norm(k)
-    if use_beta_sigmoid_in_kernel:
-        beta = torch.sigmoid(beta.float()) * (2.0 if allow_neg_eigval else 1.0)
-    if use_gate_in_kernel:
-        g = _gate(g, A_log, dt_bias)
+    # The three options the layer turns on (fla/layers/gated_deltanet.py:309-325): one pass of the library before the
+    # chunk kernels, one after their backward.
+    flags = ((_lib.PREP_L2NORM if use_qk_l2norm_in_kernel else 0) | (_lib.PREP_GATE if use_gate_in_kernel else 0)
+             | (_lib.PREP_BETA_SIGMOID if use_beta_sigmoid_in_kernel else 0) | (_lib.PREP_NEG_EIGVAL if allow_neg_eigval else 0))
+    if flags & (_lib.PREP_L2NORM | _lib.PREP_GATE | _lib.PREP_BETA_SIGMOID):
+        if use_gate_in_kernel and A_log.numel() != v.shape[2]:
+            raise ValueError(f"A_log must have HV={v.shape[2]} elements, got {A_log.numel()}.")
+        q, k, g, beta = LayerOptionsFunction.apply(q, k, g, beta, A_log if use_gate_in_kernel else None,
+                                                   dt_bias if use_gate_in_kernel else None, flags)
     if state_v_first and initial_state is not None:
         initial_state = initial_state.transpose(-1, -2)
 

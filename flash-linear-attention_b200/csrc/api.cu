@@ -153,6 +153,49 @@ int64_t b200gdn_bwd_workspace_bytes(int32_t rows, int32_t H, int32_t HV, int32_t
          + (HV > H ? r * H * K * 4 : 0);     /* dq_acc */
 }
 
+static int check_prep_args(const b200gdn_prep_args* a, const char* who, bool bwd) {
+  using namespace gdn;
+  if (a == nullptr) return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: args is NULL", who);
+  if (a->struct_bytes != (int32_t)sizeof(b200gdn_prep_args))
+    return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: struct_bytes %d != %zu (ABI mismatch)", who, a->struct_bytes,
+                     sizeof(b200gdn_prep_args));
+  if (a->rows <= 0 || a->H <= 0 || a->HV <= 0) return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: bad sizes", who);
+  if (a->qk_dtype < 0 || a->qk_dtype > 2 || a->gb_dtype < 0 || a->gb_dtype > 2)
+    return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: dtype codes are 0 (bf16), 1 (fp16), 2 (fp32)", who);
+  if (a->flags & B200GDN_PREP_L2NORM) {
+    if (a->K <= 0 || a->K % 64 != 0 || a->K > 512)
+      return set_error(B200GDN_ERR_UNSUPPORTED, "%s: K=%d (a multiple of 64 up to 512 is built)", who, a->K);
+    REQUIRE(a->q, who); REQUIRE(a->k, who); REQUIRE(a->rstd_q, who); REQUIRE(a->rstd_k, who);
+    if (!bwd) { REQUIRE(a->qn, who); REQUIRE(a->kn, who); }
+    else { REQUIRE(a->dqn, who); REQUIRE(a->dkn, who); REQUIRE(a->dq, who); REQUIRE(a->dk, who); }
+  }
+  if (a->flags & B200GDN_PREP_GATE) {
+    if (a->HV > 256) return set_error(B200GDN_ERR_UNSUPPORTED, "%s: HV=%d (at most 256 value heads)", who, a->HV);
+    REQUIRE(a->g, who); REQUIRE(a->A_log, who);
+    if (!bwd) { REQUIRE(a->g_out, who); }
+    else { REQUIRE(a->dg, who); REQUIRE(a->dg_raw, who); REQUIRE(a->dA_log, who); REQUIRE(a->partials, who); }
+  }
+  if (a->flags & B200GDN_PREP_BETA_SIGMOID) {
+    if (a->HV > 256) return set_error(B200GDN_ERR_UNSUPPORTED, "%s: HV=%d (at most 256 value heads)", who, a->HV);
+    REQUIRE(a->beta, who);
+    if (!bwd) { REQUIRE(a->beta_out, who); }
+    else { REQUIRE(a->dbeta, who); REQUIRE(a->dbeta_raw, who); }
+  }
+  return 0;
+}
+
+int b200gdn_prep_fwd(const b200gdn_prep_args* a, void* stream) {
+  gdn::g_launches = 0;
+  if (int e = check_prep_args(a, "prep_fwd", false)) return e;
+  return gdn::launch_prep(*a, static_cast<cudaStream_t>(stream), false);
+}
+
+int b200gdn_prep_bwd(const b200gdn_prep_args* a, void* stream) {
+  gdn::g_launches = 0;
+  if (int e = check_prep_args(a, "prep_bwd", true)) return e;
+  return gdn::launch_prep(*a, static_cast<cudaStream_t>(stream), true);
+}
+
 int b200gdn_device_status(void) {
   struct { const char* name; int (*flag)(); } k[] = {
       {"intra_fwd", gdn::intra_fwd_timeout_flag}, {"scan_fwd", gdn::scan_fwd_timeout_flag}, {"out_fwd", gdn::out_fwd_timeout_flag},

@@ -161,6 +161,56 @@ typedef struct b200gdn_affine_args {
 } b200gdn_affine_args;
 int b200gdn_affine_apply(const b200gdn_affine_args* args, void* stream);
 
+/* The three options fla.layers.GatedDeltaNet turns on (fla/layers/gated_deltanet.py:309-325), as one pass before the
+ * chunk kernels and one pass after their backward:
+ *   L2NORM        y = x rsqrt(sum x^2 + 1e-6) over K for q and k, fp32 math; rstd saved
+ *                 (l2norm_fwd_kernel / l2norm_bwd_kernel, fla/modules/l2norm.py:84-144)
+ *   GATE          g = -exp(A_log) softplus(g_raw + dt_bias) per value head; backward also gives dA_log, ddt_bias
+ *                 (gdn_gate_chunk_cumsum_scalar_kernel / gdn_gate_bwd_kernel, fla/ops/gated_delta_rule/gate.py:63-158;
+ *                 the chunk cumulative sum itself stays inside b200gdn_chunk_fwd)
+ *   BETA_SIGMOID  beta = s sigmoid(beta_raw), s = 2 with NEG_EIGVAL else 1
+ *                 (fused_beta_sigmoid_fwd/bwd_kernel, fla/ops/common/gate.py:18-50)
+ * Outputs the chunk entry points consume directly: q, k in bf16, g and beta in fp32.  An option that is off leaves
+ * its outputs untouched (pass the raw tensor to the chunk call instead). */
+#define B200GDN_PREP_L2NORM 1u
+#define B200GDN_PREP_GATE 2u
+#define B200GDN_PREP_BETA_SIGMOID 4u
+#define B200GDN_PREP_NEG_EIGVAL 8u
+#define B200GDN_PREP_PART_ROWS 4096      /* rows of g reduced by one CTA of the backward pass */
+typedef struct b200gdn_prep_args {
+  int32_t struct_bytes;
+  int32_t rows, H, HV, K;        /* K a multiple of 64, at most 512 */
+  uint32_t flags;                /* B200GDN_PREP_* */
+  int32_t qk_dtype;              /* 0 = bf16, 1 = fp16, 2 = fp32: element type of q, k, dq, dk */
+  int32_t gb_dtype;              /* same code: element type of g, beta, dg_raw, dbeta_raw */
+  const void* q;                 /* raw [rows,H,K] */
+  const void* k;
+  const void* g;                 /* raw [rows,HV] */
+  const void* beta;              /* raw [rows,HV] */
+  const float* A_log;            /* [HV] (GATE) */
+  const float* dt_bias;          /* [HV] or NULL */
+  void* qn;                      /* out bf16 [rows,H,K] (L2NORM) */
+  void* kn;
+  float* rstd_q;                 /* out [rows,H] (L2NORM) */
+  float* rstd_k;
+  float* g_out;                  /* out fp32 [rows,HV] (GATE) */
+  float* beta_out;               /* out fp32 [rows,HV] (BETA_SIGMOID) */
+  /* backward only */
+  const void* dqn;               /* bf16 [rows,H,K]: gradients w.r.t. the normalised q, k */
+  const void* dkn;
+  const float* dg;               /* fp32 [rows,HV]: gradient w.r.t. the activated gate */
+  const float* dbeta;            /* fp32 [rows,HV] */
+  void* dq;                      /* out, qk_dtype [rows,H,K] */
+  void* dk;
+  void* dg_raw;                  /* out, gb_dtype [rows,HV] */
+  void* dbeta_raw;               /* out, gb_dtype [rows,HV] */
+  float* dA_log;                 /* out [HV] */
+  float* ddt_bias;               /* out [HV] or NULL */
+  float* partials;               /* workspace fp32 [ceil(rows / B200GDN_PREP_PART_ROWS), 2, HV] (GATE backward) */
+} b200gdn_prep_args;
+int b200gdn_prep_fwd(const b200gdn_prep_args* args, void* stream);
+int b200gdn_prep_bwd(const b200gdn_prep_args* args, void* stream);
+
 /* Bytes of forward-saved tensors and of backward workspace for a problem (what the caller allocates). */
 int64_t b200gdn_saved_bytes(int32_t rows, int32_t H, int32_t HV, int32_t K, int32_t V, int32_t n_chunks);
 int64_t b200gdn_bwd_workspace_bytes(int32_t rows, int32_t H, int32_t HV, int32_t K, int32_t V, int32_t n_chunks);
