@@ -33,14 +33,16 @@ def test_struct_layouts_match_header(tmp_path):
     from b200gdn import _lib
     prog = tmp_path / 'sz.c'
     prog.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "b200gdn.h"\nint main(void){'
-                    'printf("%zu %zu %zu %zu %zu %zu\\n", sizeof(b200gdn_chunk_args), sizeof(b200gdn_recurrent_args),'
+                    'printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(b200gdn_chunk_args), sizeof(b200gdn_recurrent_args),'
                     'sizeof(b200gdn_affine_args), offsetof(b200gdn_chunk_args, chunk_meta), offsetof(b200gdn_chunk_args, dq_acc),'
-                    'offsetof(b200gdn_recurrent_args, cu_seqlens));return 0;}\n')
+                    'offsetof(b200gdn_recurrent_args, cu_seqlens), sizeof(b200gdn_prep_args), offsetof(b200gdn_prep_args, q),'
+                    'offsetof(b200gdn_prep_args, partials));return 0;}\n')
     exe = tmp_path / 'sz'
     subprocess.check_call(['gcc', '-I', os.path.join(ROOT, 'include'), str(prog), '-o', str(exe)])
     got = [int(x) for x in subprocess.check_output([str(exe)]).split()]
     want = [ctypes.sizeof(_lib.ChunkArgs), ctypes.sizeof(_lib.RecurrentArgs), ctypes.sizeof(_lib.AffineArgs),
-            _lib.ChunkArgs.chunk_meta.offset, _lib.ChunkArgs.dq_acc.offset, _lib.RecurrentArgs.cu_seqlens.offset]
+            _lib.ChunkArgs.chunk_meta.offset, _lib.ChunkArgs.dq_acc.offset, _lib.RecurrentArgs.cu_seqlens.offset,
+            ctypes.sizeof(_lib.PrepArgs), _lib.PrepArgs.q.offset, _lib.PrepArgs.partials.offset]
     assert got == want
 
 
@@ -55,6 +57,12 @@ def test_argument_errors_without_gpu():
     assert lib.b200gdn_chunk_bwd(ctypes.byref(a), None) == -1
     assert b'ABI mismatch' in lib.b200gdn_last_error()
     assert lib.b200gdn_recurrent_fwd(None, None) == -1
+    p = _lib.PrepArgs()
+    p.struct_bytes = ctypes.sizeof(p)
+    p.rows, p.H, p.HV, p.K, p.flags = 64, 2, 2, 100, _lib.PREP_L2NORM
+    assert lib.b200gdn_prep_fwd(ctypes.byref(p), None) == -2 and b'multiple of 64' in lib.b200gdn_last_error()
+    p.K, p.flags = 128, _lib.PREP_GATE
+    assert lib.b200gdn_prep_bwd(ctypes.byref(p), None) == -1 and b'is NULL' in lib.b200gdn_last_error()
     assert lib.b200gdn_saved_bytes(16384, 16, 16, 128, 128, 256) == 16384 * 16 * (4 + 128 + 256 * 3) + 256 * 16 * 32768
     assert lib.b200gdn_bwd_workspace_bytes(64, 2, 4, 128, 128, 1) > 0
 
