@@ -54,7 +54,7 @@ def stage_bytes(R, C, NS):
     snap = C * HV * K * V * 2                         # h or dh snapshots
     st32 = NS * HV * K * V * 4                        # h0, ht, dht, dh0
     gam, vec = C * HV * BT * 4, R * HV * 4
-    dkp = R * H * K * 4
+    dkp = R * H * K * 2                               # chunk-local part of dk, bf16, passed through the dk buffer
     return {
         'intra_fwd': qk + wv + 2 * vec + a_ + w + wv + gam,
         'scan_fwd': w + qk + wv + gam + st32 + snap + wv + st32,
@@ -181,7 +181,7 @@ def time_stages(batch, steps):
                dq=torch.empty(rows, H, K, **bf), dk=torch.empty(rows, H, K, **bf), dv=torch.empty(rows, HV, V, **bf),
                dg=torch.empty(rows, HV, **f32), dbeta=torch.empty(rows, HV, **f32), dh0=torch.empty(n_seq, HV, K, V, **f32),
                dh=torch.empty(n_chunks, HV, K, V, **bf), dv2=torch.empty(rows, HV, V, **bf),
-               dk_part=torch.empty(rows, H, K, **f32), dG=torch.empty(rows, HV, **f32))
+               dG=torch.empty(rows, HV, **f32))
     a = new_chunk_args(batch['q'], batch['k'], batch['v'], K ** -0.5, tables)
     a.g, a.beta, a.h0 = batch['g'].data_ptr(), batch['beta'].data_ptr(), batch['h0'].data_ptr()
     a.d_o = batch['do'].data_ptr()

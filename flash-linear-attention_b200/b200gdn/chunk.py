@@ -197,7 +197,7 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             dh0 = torch.empty(n_seq, HV, K, V, **f32) if has_h0 else None
             dh = torch.empty(n_chunks, HV, K, V, **bf16)
             dv2 = torch.empty(rows, HV, V, **bf16)
-            dk_part = torch.empty(rows, H, K, **f32)
+            dk_part = torch.empty(rows, H, K, **f32) if HV > H else None
             dG = torch.empty(rows, HV, **f32)
             dq_acc = torch.empty(rows, H, K, **f32) if HV > H else None
             a.beta, a.gamma, a.A, a.w, a.h, a.v_new = (x.data_ptr() for x in (bf, gamma, A, w, h, v_new))
@@ -205,7 +205,7 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             a.dq, a.dk, a.dv, a.dg, a.dbeta, a.dh0 = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dg.data_ptr(), \
                 dbeta.data_ptr(), _lib.ptr(dh0)
             a.dh, a.dv2, a.dk_part, a.dG, a.dq_acc = dh.data_ptr(), dv2.data_ptr(), \
-                dk_part.data_ptr(), dG.data_ptr(), _lib.ptr(dq_acc)
+                _lib.ptr(dk_part), dG.data_ptr(), _lib.ptr(dq_acc)
             _lib.call('b200gdn_chunk_bwd', a, _stream(qb))
         qd, kd, vd, gd, bd = in_dtypes
         return dq.to(qd), dk.to(kd), dv.to(vd), dg.to(gd), dbeta.to(bd), None, dh0, None, None, None

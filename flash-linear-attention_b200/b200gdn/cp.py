@@ -248,7 +248,7 @@ class ChunkGatedDeltaRuleCPFunction(torch.autograd.Function):
             dbeta = torch.empty(B, T, HV, **f32)
             dh = torch.empty(n_chunks, HV, K, V, **bf16)
             dv2 = torch.empty(rows, HV, V, **bf16)
-            dk_part = torch.empty(rows, H, K, **f32)
+            dk_part = torch.empty(rows, H, K, **f32) if HV > H else None
             dG = torch.empty(rows, HV, **f32)
             dq_acc = torch.empty(rows, H, K, **f32) if HV > H else None
             st = _stream(qb)
@@ -259,7 +259,7 @@ class ChunkGatedDeltaRuleCPFunction(torch.autograd.Function):
             a.d_o = dob.data_ptr()
             a.dq, a.dk, a.dv, a.dg, a.dbeta = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dg.data_ptr(), dbeta.data_ptr()
             a.dh, a.dv2, a.dk_part, a.dG, a.dq_acc = dh.data_ptr(), dv2.data_ptr(), \
-                dk_part.data_ptr(), dG.data_ptr(), _lib.ptr(dq_acc)
+                _lib.ptr(dk_part), dG.data_ptr(), _lib.ptr(dq_acc)
             a.stage_mask = _lib.BWD_DVLOCAL
             _lib.call('b200gdn_chunk_bwd', a, st)
 

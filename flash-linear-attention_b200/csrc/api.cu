@@ -90,12 +90,12 @@ int b200gdn_chunk_bwd(const b200gdn_chunk_args* a, void* stream) {
   if (m & B200GDN_BWD_DQKWG) {
     REQUIRE(a->q, "chunk_bwd"); REQUIRE(a->k, "chunk_bwd"); REQUIRE(a->v_new, "chunk_bwd"); REQUIRE(a->gamma, "chunk_bwd");
     REQUIRE(a->h, "chunk_bwd"); REQUIRE(a->dh, "chunk_bwd"); REQUIRE(a->dv2, "chunk_bwd"); REQUIRE(a->d_o, "chunk_bwd");
-    REQUIRE(a->dq, "chunk_bwd"); REQUIRE(a->dk_part, "chunk_bwd"); REQUIRE(a->dG, "chunk_bwd");
+    REQUIRE(a->dq, "chunk_bwd"); REQUIRE(a->dk, "chunk_bwd"); REQUIRE(a->dG, "chunk_bwd");
     if (int e = launch_bwd_dqk(*a, st)) return e;
   }
   if (m & B200GDN_BWD_WY) {
     REQUIRE(a->k, "chunk_bwd"); REQUIRE(a->v, "chunk_bwd"); REQUIRE(a->beta, "chunk_bwd"); REQUIRE(a->gamma, "chunk_bwd");
-    REQUIRE(a->A, "chunk_bwd"); REQUIRE(a->h, "chunk_bwd"); REQUIRE(a->dv2, "chunk_bwd"); REQUIRE(a->dk_part, "chunk_bwd");
+    REQUIRE(a->A, "chunk_bwd"); REQUIRE(a->h, "chunk_bwd"); REQUIRE(a->dv2, "chunk_bwd");
     REQUIRE(a->dG, "chunk_bwd"); REQUIRE(a->dk, "chunk_bwd"); REQUIRE(a->dv, "chunk_bwd"); REQUIRE(a->dg, "chunk_bwd");
     REQUIRE(a->dbeta, "chunk_bwd");
     if (int e = launch_bwd_wy(*a, st)) return e;
@@ -147,10 +147,8 @@ int64_t b200gdn_bwd_workspace_bytes(int32_t rows, int32_t H, int32_t HV, int32_t
   int64_t r = rows, hv = HV;
   return (int64_t)n_chunks * hv * K * V * 2 /* dh */
          + r * hv * V * 2                    /* dv2 */
-         + r * hv * K * 2                    /* dw */
-         + r * H * K * 4                     /* dk_part */
          + r * hv * 4                        /* dG */
-         + (HV > H ? r * H * K * 4 : 0);     /* dq_acc */
+         + (HV > H ? 2 * r * H * K * 4 : 0); /* dq_acc, dk_part: fp32 sums over a group of value heads */
 }
 
 static int check_prep_args(const b200gdn_prep_args* a, const char* who, bool bwd) {

@@ -36,7 +36,7 @@ struct DqkSmem {
 };
 
 struct DqkMaps {
-  CUtensorMap q, k, d_o, vn, h, dh;
+  CUtensorMap q, k, d_o, vn, h, dh, dk;
 };
 
 template <int DK, int DV>
@@ -331,15 +331,24 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
           const float d2 = r[b][4 * i + 2] + s[b][4 * i + 2], d3 = r[b][4 * i + 3] + s[b][4 * i + 3];
           rk_lo += d0 * ka.x + d1 * ka.y;
           rk_hi += d2 * kb.x + d3 * kb.y;
-          if (r_lo < cm.len) {
-            float2* pp = reinterpret_cast<float2*>(buf + r_lo * stride + col);
-            float2 o = first ? make_float2(0.f, 0.f) : *pp;
-            *pp = make_float2(d0 + o.x, d1 + o.y);
+          // the value heads of a group add up in fp32 (through dk_part); the group sum leaves in bf16 through the
+          // dk buffer, where the WY-backward kernel adds its terms
+          float2 lo = make_float2(d0, d1), hi = make_float2(d2, d3);
+          if (G > 1) {
+            if (r_lo < cm.len) {
+              float2* pp = reinterpret_cast<float2*>(buf + r_lo * stride + col);
+              if (!first) { const float2 o = *pp; lo.x += o.x; lo.y += o.y; }
+              if (!last) *pp = lo;
+            }
+            if (r_hi < cm.len) {
+              float2* pp = reinterpret_cast<float2*>(buf + r_hi * stride + col);
+              if (!first) { const float2 o = *pp; hi.x += o.x; hi.y += o.y; }
+              if (!last) *pp = hi;
+            }
           }
-          if (r_hi < cm.len) {
-            float2* pp = reinterpret_cast<float2*>(buf + r_hi * stride + col);
-            float2 o = first ? make_float2(0.f, 0.f) : *pp;
-            *pp = make_float2(d2 + o.x, d3 + o.y);
+          if (last) {
+            *swz_ptr32(dHp, r_lo, col, BT) = pack_bf16(lo.x, lo.y);
+            *swz_ptr32(dHp, r_hi, col, BT) = pack_bf16(hi.x, hi.y);
           }
         }
       rk_lo += __shfl_xor_sync(0xffffffffu, rk_lo, 1);
@@ -360,8 +369,20 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
         rks[hc * BT + r_hi] = rk_hi;
       }
     }
+    tc5::fence_async_smem();
     tc5::fence_before_sync();
     __syncthreads();
+    if (last) {   // the chunk-local part of dk (staged over the dh panel)
+      if (cm.len == BT) {
+        if (tid == 32) {
+          tma::store_3d(&maps.dk, (int)cm.row, (hq * DK) / 64, dHp);
+          tma::store_commit();
+        }
+      } else {
+        store_tile_swz<BT, DK, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.dk) + (row0 * a.H + hq) * DK, (int64_t)a.H * DK, dHp,
+                                         cm.len, tid);
+      }
+    }
     if (tid < cm.len) {
       float sh = 0.f, sr = 0.f;
 #pragma unroll
@@ -375,6 +396,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
     }
   }
 
+  if (tid == 32) tma::store_wait_all<0>();   // shared memory must outlive the bulk store that reads it
   if (failed && tid == 0) atomicExch(&g_dqk_timeout, 1);
   tc5::fence_before_sync();
   __syncthreads();
@@ -393,6 +415,7 @@ int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
   rc |= tma::encode_bf16_panels(&m.k, a.k, a.rows, pk, pk, BT, DK / 64);
   rc |= tma::encode_bf16_panels(&m.d_o, a.d_o, a.rows, pv, pv, BT, DV / 64);
   rc |= tma::encode_bf16_panels(&m.vn, a.v_new, a.rows, pv, pv, BT, DV / 64);
+  rc |= tma::encode_bf16_panels(&m.dk, a.dk, a.rows, pk, pk, BT, DK / 64);
   rc |= tma::encode_bf16_2d(&m.h, a.h, hrows, DV, DV, DK);
   rc |= tma::encode_bf16_2d(&m.dh, a.dh, hrows, DV, DV, DK);
   if (rc != 0) return set_error(B200GDN_ERR_CUDA, "bwd_dqk: cuTensorMapEncodeTiled failed (%d)", rc);
@@ -404,7 +427,8 @@ int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
 }  // namespace
 
 int launch_bwd_dqk(const b200gdn_chunk_args& a, cudaStream_t st) {
-  if (a.HV > a.H && a.dq_acc == nullptr) return set_error(B200GDN_ERR_BAD_ARGUMENT, "bwd_dqk: dq_acc is required when HV > H");
+  if (a.HV > a.H && (a.dq_acc == nullptr || a.dk_part == nullptr))
+    return set_error(B200GDN_ERR_BAD_ARGUMENT, "bwd_dqk: dq_acc and dk_part are required when HV > H");
   if (a.K == 128 && a.V == 128) return launch<128, 128>(a, st);
   if (a.K == 64 && a.V == 64) return launch<64, 64>(a, st);
   return set_error(B200GDN_ERR_UNSUPPORTED, "bwd_dqk: K=%d V=%d not built (64/64 and 128/128 are)", a.K, a.V);

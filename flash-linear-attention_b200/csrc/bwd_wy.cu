@@ -6,7 +6,7 @@
 //     dW   = -dU h^T                                    dU = dv2
 //     dA   = strict_tril((dW K^T) (beta 2^gamma)_j + (dU V^T) beta_j)
 //     M    = -strict_tril(A^T dA A^T) 2^(gamma_i - gamma_j),   M2 = M beta_i
-//     dk   = dk_part + (A beta 2^gamma)_col^T dW + M2 K + M2^T K
+//     dk   = (chunk-local part from the dq/dk kernel) + (A beta 2^gamma)_col^T dW + M2 K + M2^T K
 //     dv   = (A^T dU) beta_i
 //     dbeta= colsum(A . dW K^T) 2^gamma + colsum(A . dU V^T) + rowsum(M . K K^T)
 //     dG   = dG_part + colsum(A . dW K^T) beta 2^gamma + beta rowsum(M . K K^T) - colsum(M2 . K K^T)
@@ -58,7 +58,9 @@ __device__ __forceinline__ float sum_over_t(float x) {
   return x;
 }
 
-template <int DK, int DV>
+// GROUPED: more than one value head per q/k head (the heads of a group are walked by one CTA and their dk terms
+// add up in fp32 through dk_part); the common ungrouped case is compiled without that path.
+template <int DK, int DV, bool GROUPED>
 __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk_args a, const __grid_constant__ WyMaps maps) {
   using S = WyTcSmem<DK, DV>;
   constexpr int KB = DK / 64, VB = DV / 64;   // 32-column blocks of a wide accumulator per warp
@@ -95,7 +97,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
   const int q = warp & 3, hc = warp >> 2;
   const int g = lane >> 2, t = lane & 3;
   const int c = blockIdx.x, hq = blockIdx.y;
-  const int G = a.HV / a.H;
+  const int G = GROUPED ? a.HV / a.H : 1;
   const ChunkMeta cm = load_chunk_meta(a.chunk_meta, c);
   const int64_t row0 = cm.row;
   const int r_lo = q * 16 + g, r_hi = r_lo + 8;
@@ -121,9 +123,10 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
 
   if (warp == 1) tc5::tmem_alloc(tmem_slot, 256);
   {
-    // the dq/dk kernel's part of dk is read at the very end: pull it into L2 now (one 128-byte line per thread)
+    // the dq/dk kernel's part of dk (bf16, in the dk buffer) is read at the very end: pull it into L2 now
     const int r = tid >> 2, seg = tid & 3;
-    if (r < cm.len && seg * 32 < DK) tma::prefetch_line(a.dk_part + ((row0 + r) * a.H + hq) * DK + seg * 32);
+    if (r < cm.len && seg * 64 < DK)
+      tma::prefetch_line(reinterpret_cast<const __nv_bfloat16*>(a.dk) + ((row0 + r) * a.H + hq) * DK + seg * 64);
 
   }
   tc5::fence_before_sync();
@@ -375,12 +378,24 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
     // the dq/dk kernel's part of dk: fetched now so that its latency hides behind the MMAs
     float* const dkbuf = a.dk_part + (row0 * a.H + hq) * DK + hc * (DK / 2);
     const int64_t dkstride = (int64_t)a.H * DK;
-    float2 part[KB * 4][2];
+    // first head of the group: the bf16 sum the dq/dk kernel left in the dk buffer; later heads: the fp32 running
+    // sum of this kernel (dk_part)
+    const __nv_bfloat16* const dkin = reinterpret_cast<const __nv_bfloat16*>(a.dk) + (row0 * a.H + hq) * DK + hc * (DK / 2);
+    uint32_t part16[GROUPED ? 1 : KB * 4][2];        // ungrouped: bf16 pairs, unpacked when they are used
+    float2 part32[GROUPED ? KB * 4 : 1][2];          // grouped: fp32 pairs
 #pragma unroll
     for (int n8 = 0; n8 < KB * 4; ++n8) {
       const int col = n8 * 8 + 2 * t;
-      part[n8][0] = r_lo < cm.len ? *reinterpret_cast<const float2*>(dkbuf + r_lo * dkstride + col) : make_float2(0.f, 0.f);
-      part[n8][1] = r_hi < cm.len ? *reinterpret_cast<const float2*>(dkbuf + r_hi * dkstride + col) : make_float2(0.f, 0.f);
+      if (!GROUPED) {
+        part16[n8][0] = r_lo < cm.len ? *reinterpret_cast<const uint32_t*>(dkin + r_lo * dkstride + col) : 0u;
+        part16[n8][1] = r_hi < cm.len ? *reinterpret_cast<const uint32_t*>(dkin + r_hi * dkstride + col) : 0u;
+      } else if (gi == 0) {
+        part32[n8][0] = unpack_bf16(r_lo < cm.len ? *reinterpret_cast<const uint32_t*>(dkin + r_lo * dkstride + col) : 0u);
+        part32[n8][1] = unpack_bf16(r_hi < cm.len ? *reinterpret_cast<const uint32_t*>(dkin + r_hi * dkstride + col) : 0u);
+      } else {
+        part32[n8][0] = r_lo < cm.len ? *reinterpret_cast<const float2*>(dkbuf + r_lo * dkstride + col) : make_float2(0.f, 0.f);
+        part32[n8][1] = r_hi < cm.len ? *reinterpret_cast<const float2*>(dkbuf + r_hi * dkstride + col) : make_float2(0.f, 0.f);
+      }
     }
     __syncthreads();   // column / row sums of every warp are in place
     // gate / beta gradients while the MMAs run: dG per row, then the reverse cumsum as a two-warp suffix scan
@@ -413,8 +428,16 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int n8 = b * 4 + i, col = n8 * 8 + 2 * t;
-          const float d0 = r[b][4 * i] + part[n8][0].x, d1 = r[b][4 * i + 1] + part[n8][0].y;
-          const float d2 = r[b][4 * i + 2] + part[n8][1].x, d3 = r[b][4 * i + 3] + part[n8][1].y;
+          float2 p_lo, p_hi;
+          if (!GROUPED) {
+            p_lo = unpack_bf16(part16[GROUPED ? 0 : n8][0]);
+            p_hi = unpack_bf16(part16[GROUPED ? 0 : n8][1]);
+          } else {
+            p_lo = part32[GROUPED ? n8 : 0][0];
+            p_hi = part32[GROUPED ? n8 : 0][1];
+          }
+          const float d0 = r[b][4 * i] + p_lo.x, d1 = r[b][4 * i + 1] + p_lo.y;
+          const float d2 = r[b][4 * i + 2] + p_hi.x, d3 = r[b][4 * i + 3] + p_hi.y;
           if (!last) {
             if (r_lo < cm.len) *reinterpret_cast<float2*>(dkbuf + r_lo * dkstride + col) = make_float2(d0, d1);
             if (r_hi < cm.len) *reinterpret_cast<float2*>(dkbuf + r_hi * dkstride + col) = make_float2(d2, d3);
@@ -438,10 +461,10 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
   if (warp == 1) tc5::tmem_dealloc(tm, 256);
 }
 
-template <int DK, int DV>
+template <int DK, int DV, bool GROUPED>
 int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
   using S = WyTcSmem<DK, DV>;
-  if (int e = ensure_smem(bwd_wy_kernel<DK, DV>, S::bytes)) return e;
+  if (int e = ensure_smem(bwd_wy_kernel<DK, DV, GROUPED>, S::bytes)) return e;
   WyMaps m;
   const uint64_t pk = (uint64_t)a.H * DK, pv = (uint64_t)a.HV * DV;
   int rc = 0;
@@ -453,15 +476,17 @@ int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
   rc |= tma::encode_bf16_panels(&m.h, a.h, (uint64_t)a.n_chunks * a.HV * DK, DV, DV, DK, DV / 64);
   if (rc != 0) return set_error(B200GDN_ERR_CUDA, "bwd_wy: cuTensorMapEncodeTiled failed (%d)", rc);
   dim3 grid(a.n_chunks, a.H);
-  bwd_wy_kernel<DK, DV><<<grid, NTHREADS, S::bytes, st>>>(a, m);
+  bwd_wy_kernel<DK, DV, GROUPED><<<grid, NTHREADS, S::bytes, st>>>(a, m);
   return check_launch("bwd_wy");
 }
 
 }  // namespace
 
 int launch_bwd_wy(const b200gdn_chunk_args& a, cudaStream_t st) {
-  if (a.K == 128 && a.V == 128) return launch<128, 128>(a, st);
-  if (a.K == 64 && a.V == 64) return launch<64, 64>(a, st);
+  if (a.HV > a.H && a.dk_part == nullptr) return set_error(B200GDN_ERR_BAD_ARGUMENT, "bwd_wy: dk_part is required when HV > H");
+  const bool grouped = a.HV > a.H;
+  if (a.K == 128 && a.V == 128) return grouped ? launch<128, 128, true>(a, st) : launch<128, 128, false>(a, st);
+  if (a.K == 64 && a.V == 64) return grouped ? launch<64, 64, true>(a, st) : launch<64, 64, false>(a, st);
   return set_error(B200GDN_ERR_UNSUPPORTED, "bwd_wy: K=%d V=%d not built (64/64 and 128/128 are)", a.K, a.V);
 }
 

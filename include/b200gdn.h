@@ -47,8 +47,8 @@ typedef enum b200gdn_status {
 #define B200GDN_FWD_OUT 4u       /* o                      <- q, k, v_new, h, gamma */
 #define B200GDN_BWD_DVLOCAL 1u   /* dv2 (local part)       <- q, k, gamma, do */
 #define B200GDN_BWD_SCAN 2u      /* dh, dh0, dv2           <- q, k, w, gamma, do, dht */
-#define B200GDN_BWD_DQKWG 4u     /* dq, dk_part, dG        <- q, k, v_new, gamma, h, dv2, do, dh */
-#define B200GDN_BWD_WY 8u        /* dk, dv, dbeta, dg      <- k, v, beta, gamma, A, h, dv2, dk_part, dG */
+#define B200GDN_BWD_DQKWG 4u     /* dq, dk (local part), dG <- q, k, v_new, gamma, h, dv2, do, dh */
+#define B200GDN_BWD_WY 8u        /* dk, dv, dbeta, dg      <- k, v, beta, gamma, A, h, dv2, dk (local part), dG */
 
 typedef struct b200gdn_chunk_args {
   int32_t struct_bytes;          /* = sizeof(b200gdn_chunk_args), checked */
@@ -81,7 +81,8 @@ typedef struct b200gdn_chunk_args {
   const float* dht;              /* [n_seq,HV,K,V] or NULL */
   /* backward outputs */
   void* dq;                      /* bf16 [rows,H,K] */
-  void* dk;                      /* bf16 [rows,H,K] */
+  void* dk;                      /* bf16 [rows,H,K]; between B200GDN_BWD_DQKWG and B200GDN_BWD_WY it holds the
+                                    chunk-local part of dk, to which the WY stage adds its terms in place */
   void* dv;                      /* bf16 [rows,HV,V] */
   float* dg;                     /* [rows,HV] */
   float* dbeta;                  /* [rows,HV] */
@@ -90,7 +91,7 @@ typedef struct b200gdn_chunk_args {
   void* dh;                      /* bf16 [n_chunks,HV,K,V] */
   void* dv2;                     /* bf16 [rows,HV,V] */
   void* dw;                      /* unused (dw = -dv2 h^T stays on chip); may be NULL */
-  float* dk_part;                /* [rows,H,K] */
+  float* dk_part;                /* [rows,H,K], only read/written when HV > H (fp32 sum over a group's heads) */
   float* dG;                     /* [rows,HV] */
   float* dq_acc;                 /* [rows,H,K], only read/written when HV > H */
 } b200gdn_chunk_args;

@@ -74,8 +74,8 @@ def run_abi(d, dev='cuda', fwd_mask=0, bwd_mask=0, overrides=None, do_bwd=True):
         dv=torch.full((rows, HV, V), nan, **bf), dg=torch.full((rows, HV), nan, **f32),
         dbeta=torch.full((rows, HV), nan, **f32), dh0=torch.full((n_seq, HV, K, V), nan, **f32),
         dh=torch.full((n_chunks, HV, K, V), nan, **bf), dv2=torch.full((rows, HV, V), nan, **bf),
-        dk_part=torch.full((rows, H, K), nan, **f32),
-        dG=torch.full((rows, HV), nan, **f32), dq_acc=torch.full((rows, H, K), nan, **f32),
+        dk_part=torch.full((rows, H, K), nan, **f32) if HV > H else None,
+        dG=torch.full((rows, HV), nan, **f32), dq_acc=torch.full((rows, H, K), nan, **f32) if HV > H else None,
     )
     a = new_chunk_args(q, k, v, d['scale'], (chunk_meta, seq_meta, (n_chunks, n_seq)))
     a.g, a.beta, a.h0 = g.data_ptr(), beta.data_ptr(), _lib.ptr(h0)
@@ -86,7 +86,7 @@ def run_abi(d, dev='cuda', fwd_mask=0, bwd_mask=0, overrides=None, do_bwd=True):
                 val = gamma_to_chunks(val, d['bounds'])
             t[name] = val.to(dev).to(t[name].dtype).contiguous()
     for name, val in t.items():
-        setattr(a, name, val.data_ptr())
+        setattr(a, name, _lib.ptr(val))
     st = torch.cuda.current_stream().cuda_stream
     a.stage_mask = fwd_mask
     if fwd_mask >= 0:
@@ -95,6 +95,6 @@ def run_abi(d, dev='cuda', fwd_mask=0, bwd_mask=0, overrides=None, do_bwd=True):
         a.stage_mask = bwd_mask
         _lib.call('b200gdn_chunk_bwd', a, st)
     torch.cuda.synchronize()
-    out = {n_: x.float().cpu() for n_, x in t.items()}
+    out = {n_: x.float().cpu() for n_, x in t.items() if x is not None}
     out['gamma'] = gamma_from_chunks(out['gamma'], d['bounds'], rows)
     return out
