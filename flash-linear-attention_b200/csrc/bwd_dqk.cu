@@ -36,10 +36,12 @@ struct DqkSmem {
 };
 
 struct DqkMaps {
-  CUtensorMap q, k, d_o, vn, h, dh, dk;
+  CUtensorMap q, k, d_o, vn, h, dh, dk, dq;
 };
 
-template <int DK, int DV>
+// GROUPED: more than one value head per q/k head (their dq / dk contributions add up in fp32 through dq_acc and
+// dk_part); the common ungrouped case is compiled without that path.
+template <int DK, int DV, bool GROUPED>
 __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chunk_args a, const __grid_constant__ DqkMaps maps,
                                                               const int pf_dist) {
   using S = DqkSmem<DK, DV>;
@@ -68,7 +70,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
   const int q = warp & 3, hc = warp >> 2;
   const int g = lane >> 2, t = lane & 3;
   const int c = blockIdx.x, hq = blockIdx.y;
-  const int G = a.HV / a.H;
+  const int G = GROUPED ? a.HV / a.H : 1;
   const ChunkMeta cm = load_chunk_meta(a.chunk_meta, c);
   const int64_t row0 = cm.row;
   const int r_lo = q * 16 + g, r_hi = r_lo + 8;
@@ -258,7 +260,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
           const float2 qa = swz_ld2(Qs, r_lo, col, BT), qb = swz_ld2(Qs, r_hi, col, BT);
           rq_lo += r[4 * i] * qa.x + r[4 * i + 1] * qa.y;
           rq_hi += r[4 * i + 2] * qb.x + r[4 * i + 3] * qb.y;
-          if (G > 1) {
+          if (GROUPED) {
             float* buf = a.dq_acc + (row0 * a.H + hq) * DK;
             const int64_t stride = (int64_t)a.H * DK;
             if (r_lo < cm.len) {
@@ -287,6 +289,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
         rqs[hc * BT + r_hi] = rq_hi;
       }
     }
+    tc5::fence_async_smem();
     tc5::fence_before_sync();
     __syncthreads();  // every warp has drained the dq columns; staging tile complete
 
@@ -296,9 +299,17 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
       issue_mma_t<4>(TM_DKI, opPm, opQ, 64, DK, 0);
       ph.commit();
     }
-    if (last)
-      store_tile_swz<BT, DK, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.dq) + (row0 * a.H + hq) * DK, (int64_t)a.H * DK, Hp,
-                                       cm.len, tid);
+    if (last) {
+      if (cm.len == BT) {
+        if (tid == 32) {
+          tma::store_3d(&maps.dq, (int)cm.row, (hq * DK) / 64, Hp);
+          tma::store_commit();
+        }
+      } else {
+        store_tile_swz<BT, DK, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.dq) + (row0 * a.H + hq) * DK, (int64_t)a.H * DK, Hp,
+                                         cm.len, tid);
+      }
+    }
     if (__syncthreads_or(!ph.wait())) { failed = true; break; }
 
     // ---- epilogue 3: dk = dk_state + dk_intra, gate-gradient rows, tail
@@ -334,7 +345,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
           // the value heads of a group add up in fp32 (through dk_part); the group sum leaves in bf16 through the
           // dk buffer, where the WY-backward kernel adds its terms
           float2 lo = make_float2(d0, d1), hi = make_float2(d2, d3);
-          if (G > 1) {
+          if (GROUPED) {
             if (r_lo < cm.len) {
               float2* pp = reinterpret_cast<float2*>(buf + r_lo * stride + col);
               if (!first) { const float2 o = *pp; lo.x += o.x; lo.y += o.y; }
@@ -403,10 +414,10 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
   if (warp == 1) tc5::tmem_dealloc(tm, 256);
 }
 
-template <int DK, int DV>
+template <int DK, int DV, bool GROUPED>
 int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
   using S = DqkSmem<DK, DV>;
-  if (int e = ensure_smem(bwd_dqk_kernel<DK, DV>, S::bytes)) return e;
+  if (int e = ensure_smem(bwd_dqk_kernel<DK, DV, GROUPED>, S::bytes)) return e;
   DqkMaps m;
   const uint64_t pk = (uint64_t)a.H * DK, pv = (uint64_t)a.HV * DV;
   const uint64_t hrows = (uint64_t)a.n_chunks * a.HV * DK;
@@ -416,11 +427,12 @@ int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
   rc |= tma::encode_bf16_panels(&m.d_o, a.d_o, a.rows, pv, pv, BT, DV / 64);
   rc |= tma::encode_bf16_panels(&m.vn, a.v_new, a.rows, pv, pv, BT, DV / 64);
   rc |= tma::encode_bf16_panels(&m.dk, a.dk, a.rows, pk, pk, BT, DK / 64);
+  rc |= tma::encode_bf16_panels(&m.dq, a.dq, a.rows, pk, pk, BT, DK / 64);
   rc |= tma::encode_bf16_2d(&m.h, a.h, hrows, DV, DV, DK);
   rc |= tma::encode_bf16_2d(&m.dh, a.dh, hrows, DV, DV, DK);
   if (rc != 0) return set_error(B200GDN_ERR_CUDA, "bwd_dqk: cuTensorMapEncodeTiled failed (%d)", rc);
   dim3 grid(a.n_chunks, a.H);
-  bwd_dqk_kernel<DK, DV><<<grid, NTHREADS, S::bytes, st>>>(a, m, resident_ctas(bwd_dqk_kernel<DK, DV>, NTHREADS, S::bytes));
+  bwd_dqk_kernel<DK, DV, GROUPED><<<grid, NTHREADS, S::bytes, st>>>(a, m, resident_ctas(bwd_dqk_kernel<DK, DV, GROUPED>, NTHREADS, S::bytes));
   return check_launch("bwd_dqk");
 }
 
@@ -429,8 +441,9 @@ int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
 int launch_bwd_dqk(const b200gdn_chunk_args& a, cudaStream_t st) {
   if (a.HV > a.H && (a.dq_acc == nullptr || a.dk_part == nullptr))
     return set_error(B200GDN_ERR_BAD_ARGUMENT, "bwd_dqk: dq_acc and dk_part are required when HV > H");
-  if (a.K == 128 && a.V == 128) return launch<128, 128>(a, st);
-  if (a.K == 64 && a.V == 64) return launch<64, 64>(a, st);
+  const bool grouped = a.HV > a.H;
+  if (a.K == 128 && a.V == 128) return grouped ? launch<128, 128, true>(a, st) : launch<128, 128, false>(a, st);
+  if (a.K == 64 && a.V == 64) return grouped ? launch<64, 64, true>(a, st) : launch<64, 64, false>(a, st);
   return set_error(B200GDN_ERR_UNSUPPORTED, "bwd_dqk: K=%d V=%d not built (64/64 and 128/128 are)", a.K, a.V);
 }
 

@@ -42,7 +42,7 @@ struct WyTcSmem {
 };
 
 struct WyMaps {
-  CUtensorMap k, v, du, a, h, dv;
+  CUtensorMap k, v, du, a, h, dv, dk;
 };
 
 // sum over the 8 row-lanes of a warp (lanes that differ in bits 2..4), result valid in lanes with g == 0
@@ -447,11 +447,20 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
           }
         }
     }
+    tc5::fence_async_smem();
     tc5::fence_before_sync();
     __syncthreads();
-    if (last)
-      store_tile_swz<BT, DK, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.dk) + (row0 * a.H + hq) * DK, (int64_t)a.H * DK, dWs,
-                                       cm.len, tid);
+    if (last) {
+      if (cm.len == BT) {
+        if (tid == 32) {
+          tma::store_3d(&maps.dk, (int)cm.row, (hq * DK) / 64, dWs);
+          tma::store_commit();
+        }
+      } else {
+        store_tile_swz<BT, DK, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.dk) + (row0 * a.H + hq) * DK, (int64_t)a.H * DK, dWs,
+                                         cm.len, tid);
+      }
+    }
   }
 
   if (tid == 32) tma::store_wait_all<0>();
@@ -473,6 +482,7 @@ int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
   rc |= tma::encode_bf16_panels(&m.du, a.dv2, a.rows, pv, pv, BT, DV / 64);
   rc |= tma::encode_bf16_2d(&m.a, a.A, a.rows, (uint64_t)a.HV * BT, (uint64_t)a.HV * BT, BT);
   rc |= tma::encode_bf16_panels(&m.dv, a.dv, a.rows, pv, pv, BT, DV / 64);
+  rc |= tma::encode_bf16_panels(&m.dk, a.dk, a.rows, pk, pk, BT, DK / 64);
   rc |= tma::encode_bf16_panels(&m.h, a.h, (uint64_t)a.n_chunks * a.HV * DK, DV, DV, DK, DV / 64);
   if (rc != 0) return set_error(B200GDN_ERR_CUDA, "bwd_wy: cuTensorMapEncodeTiled failed (%d)", rc);
   dim3 grid(a.n_chunks, a.H);
