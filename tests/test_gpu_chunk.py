@@ -297,3 +297,27 @@ def test_layer_option_kernels_against_torch(qk_dtype, gb_dtype):
                             ('ddt_bias', leaves[5], ref[5], 1e-5)):
         assert a.grad.dtype == a.dtype, name
         O.assert_close(name, b.grad.cpu(), a.grad.float().cpu(), tol)
+
+
+def test_chunk_forward_in_cuda_graph():
+    """A prefill step (forward only, static buffers) captured in a CUDA graph replays to the eager result: the library
+    only enqueues kernels on the caller's stream, and the tensor maps it builds on the host are kernel parameters."""
+    from b200gdn import chunk_gated_delta_rule
+    q, k, v, g, beta, _ = _inputs(2, 512, 4, 4, 128, 128, seed=6)
+    with torch.no_grad():
+        o_e, ht_e = chunk_gated_delta_rule(q, k, v, g, beta, output_final_state=True)   # also warms the chunk tables
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            chunk_gated_delta_rule(q, k, v, g, beta, output_final_state=True)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            o_g, ht_g = chunk_gated_delta_rule(q, k, v, g, beta, output_final_state=True)
+        v2 = torch.randn_like(v.float()).to(torch.bfloat16)
+        o_e2, ht_e2 = chunk_gated_delta_rule(q, k, v2, g, beta, output_final_state=True)
+        graph.replay()
+        assert torch.equal(o_g, o_e) and torch.equal(ht_g, ht_e)
+        v.copy_(v2)
+        graph.replay()
+        assert torch.equal(o_g, o_e2) and torch.equal(ht_g, ht_e2)

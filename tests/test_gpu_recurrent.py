@@ -120,3 +120,46 @@ def test_decode_sweep_single_token_steps(B):
         o_ref = torch.einsum('bhkv,bhk->bhv', ref, q[:, 0]) * scale
         O.assert_close(f'o step {step}', o_ref.cpu(), o[:, 0].cpu(), 1e-5)
         O.assert_close(f'state step {step}', ref.cpu(), state.cpu(), 1e-5)
+
+
+def test_decode_step_in_cuda_graph():
+    """The decode step only enqueues work on the caller's stream, so a serving loop can capture it in a CUDA graph
+    (static input buffers, state updated in place) and replay it; replays must reproduce the eager steps."""
+    from b200gdn import fused_recurrent_gated_delta_rule
+    dev = 'cuda'
+    B, H, K, V = 8, 16, 128, 128
+    gen = torch.Generator(device=dev).manual_seed(5)
+    mk = lambda *s: torch.randn(*s, device=dev, generator=gen)
+    steps = [dict(q=torch.nn.functional.normalize(mk(B, 1, H, K), dim=-1), k=torch.nn.functional.normalize(mk(B, 1, H, K), dim=-1),
+                  v=mk(B, 1, H, V), g=torch.nn.functional.logsigmoid(mk(B, 1, H)), beta=torch.sigmoid(mk(B, 1, H)))
+             for _ in range(4)]
+    state0 = mk(B, H, K, V) * 0.1
+    # eager
+    s_e = state0.clone()
+    outs_e = []
+    for st in steps:
+        o, _ = fused_recurrent_gated_delta_rule(st['q'], st['k'], st['v'], st['g'], beta=st['beta'], initial_state=s_e,
+                                                output_final_state=True, inplace_state=True)
+        outs_e.append(o.clone())
+    # captured once, replayed per step
+    buf = {n: torch.empty_like(x) for n, x in steps[0].items()}
+    s_g = state0.clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):   # warm-up outside the capture (library load, first launch)
+        for n in buf:
+            buf[n].copy_(steps[0][n])
+        fused_recurrent_gated_delta_rule(buf['q'], buf['k'], buf['v'], buf['g'], beta=buf['beta'], initial_state=s_g.clone(),
+                                         output_final_state=True, inplace_state=True)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        o_g, _ = fused_recurrent_gated_delta_rule(buf['q'], buf['k'], buf['v'], buf['g'], beta=buf['beta'], initial_state=s_g,
+                                                  output_final_state=True, inplace_state=True)
+    s_g.copy_(state0)
+    for i, st in enumerate(steps):
+        for n in buf:
+            buf[n].copy_(st[n])
+        graph.replay()
+        assert torch.equal(o_g, outs_e[i]), f'step {i}'
+    assert torch.equal(s_g, s_e)
