@@ -30,7 +30,7 @@ __device__ __forceinline__ void st_elem(void* p, int64_t i, int dtype, float x) 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
 template <int DK, bool VFIRST>
-__global__ void __launch_bounds__(NTHREADS) recurrent_kernel(const b200gdn_recurrent_args a) {
+__global__ void __launch_bounds__(NTHREADS, (DK <= 128 ? 8 : 4)) recurrent_kernel(const b200gdn_recurrent_args a) {
   __shared__ __align__(16) float qs[DK];
   __shared__ __align__(16) float ks[DK];
   __shared__ __align__(16) float vs[VS];

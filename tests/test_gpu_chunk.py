@@ -321,3 +321,26 @@ def test_chunk_forward_in_cuda_graph():
         v.copy_(v2)
         graph.replay()
         assert torch.equal(o_g, o_e2) and torch.equal(ht_g, ht_e2)
+
+
+@pytest.mark.parametrize('name', ['triton_d128_dense', 'triton_d128_varlen_gva', 'triton_d64_dense'])
+def test_public_api_against_reference_triton_path(name):
+    """Outputs and gradients of the reference's own Triton chunk path on a B200 (tests/golden/make_triton_golden.py)
+    on identical seeded inputs; tolerances of the reference's tests (tests/ops/test_gdn.py:203-278: o, ht 0.005;
+    dq, dk, dv, dh0 0.008; dbeta, dg 0.02)."""
+    from b200gdn import chunk_gated_delta_rule
+    from tests.golden.make_triton_golden import TRITON_CASES
+    B, T, H, HV, K, V, cu, seed = TRITON_CASES[name]
+    gold = np.load(os.path.join(os.path.dirname(__file__), 'golden', name + '.npz'))
+    d = O.make_inputs(B, T, H, HV, K, V, seed=seed, cu_seqlens=cu)
+    dev = 'cuda'
+    leaves = {n: d[n].to(torch.bfloat16).to(dev).requires_grad_(True) for n in ('q', 'k', 'v')}
+    leaves.update({n: d[n].float().to(dev).requires_grad_(True) for n in ('g', 'beta', 'h0')})
+    cu_t = None if cu is None else torch.tensor(cu, dtype=torch.long, device=dev)
+    o, ht = chunk_gated_delta_rule(leaves['q'], leaves['k'], leaves['v'], leaves['g'], leaves['beta'], scale=K ** -0.5,
+                                   initial_state=leaves['h0'], output_final_state=True, cu_seqlens=cu_t)
+    ((o.float() * d['do'].to(torch.bfloat16).float().to(dev)).sum() + (ht * d['dht'].to(dev)).sum()).backward()
+    O.assert_close('o', torch.from_numpy(gold['o']), o.float().cpu(), 0.005)
+    O.assert_close('ht', torch.from_numpy(gold['ht']), ht.cpu(), 0.005)
+    for n, tol in (('q', 0.008), ('k', 0.008), ('v', 0.008), ('h0', 0.008), ('beta', 0.02), ('g', 0.02)):
+        O.assert_close('d' + n, torch.from_numpy(gold['d' + n]), leaves[n].grad.float().cpu(), tol)

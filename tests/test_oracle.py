@@ -112,3 +112,23 @@ def test_metric():
     O.assert_close('x', a, a + 1e-7, 1e-9)
     with pytest.raises(AssertionError):
         O.assert_close('x', a, a * 1.1, 0.01)
+
+
+@pytest.mark.parametrize('name', ['triton_d128_dense', 'triton_d128_varlen_gva', 'triton_d64_dense'])
+def test_oracle_against_reference_triton_path(name):
+    """The oracle (exact fp32 math on the bf16-rounded inputs) against the outputs and gradients of the reference's
+    own Triton chunk path recorded on a B200 (tests/golden/make_triton_golden.py), within the tolerances the
+    reference's tests use for that path (tests/ops/test_gdn.py:203-278)."""
+    from tests.golden.make_triton_golden import TRITON_CASES
+    B, T, H, HV, K, V, cu, seed = TRITON_CASES[name]
+    gold = _load(name)
+    d = O.make_inputs(B, T, H, HV, K, V, seed=seed, cu_seqlens=cu)
+    rb = lambda x: x.to(torch.bfloat16).float()
+    o, ht, gr = O.naive_with_grads(rb(d['q']), rb(d['k']), rb(d['v']), d['g'], d['beta'], K ** -0.5, d['h0'],
+                                   rb(d['do']), d['dht'], cu_seqlens=cu)
+    assert O.err_ratio(o, gold['o']) < 0.005
+    assert O.err_ratio(ht, gold['ht']) < 0.005
+    for n in ('dq', 'dk', 'dv', 'dh0'):
+        assert O.err_ratio(gr[n], gold[n]) < 0.008, n
+    for n in ('dg', 'dbeta'):
+        assert O.err_ratio(gr[n], gold[n]) < 0.02, n
