@@ -73,6 +73,7 @@ EXPORTS = (
     'b200gdn_chunk_fwd', 'b200gdn_chunk_bwd', 'b200gdn_recurrent_fwd', 'b200gdn_affine_apply',
     'b200gdn_saved_bytes', 'b200gdn_bwd_workspace_bytes', 'b200gdn_last_launch_count',
     'b200gdn_abi_version', 'b200gdn_last_error', 'b200gdn_device_status', 'b200gdn_prep_fwd', 'b200gdn_prep_bwd',
+    'b200gdn_selftest_wait_expiry',
 )
 
 _lib = None
@@ -108,6 +109,8 @@ def load():
         lib.b200gdn_last_launch_count.restype = C.c_int
         lib.b200gdn_device_status.restype = C.c_int
         lib.b200gdn_device_status.argtypes = []
+        lib.b200gdn_selftest_wait_expiry.restype = C.c_int
+        lib.b200gdn_selftest_wait_expiry.argtypes = [C.c_void_p]
         lib.b200gdn_abi_version.restype = C.c_int
         lib.b200gdn_last_error.restype = C.c_char_p
         if lib.b200gdn_abi_version() != ABI_VERSION:

@@ -3,6 +3,7 @@
 #include <cstdio>
 
 #include "gdn_common.cuh"
+#include "tc5.cuh"
 
 namespace gdn {
 
@@ -43,6 +44,28 @@ static int check_chunk_args(const b200gdn_chunk_args* a, const char* who) {
 #define REQUIRE(ptr, who)                                                                  \
   if ((ptr) == nullptr) return gdn::set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: %s is NULL", who, #ptr)
 
+}  // namespace gdn
+
+namespace gdn {
+__device__ int g_selftest_timeout = 0;
+// One warp waits on an mbarrier that nothing will ever complete, with a short limit: the wait must give up, raise the
+// flag and let the kernel end normally (what every wait of the real kernels does when a completion is lost).
+__global__ void selftest_wait_expiry_kernel(uint32_t limit) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    tc5::mbar_init(&bar, 1);
+    tc5::fence_mbar_init();
+  }
+  __syncthreads();
+  const bool ok = tc5::mbar_wait(&bar, 0, limit);
+  if (!ok && threadIdx.x == 0) atomicExch(&g_selftest_timeout, 1);
+}
+static int selftest_timeout_flag() {
+  int v = 0, zero = 0;
+  cudaMemcpyFromSymbol(&v, g_selftest_timeout, sizeof(int));
+  if (v) cudaMemcpyToSymbol(g_selftest_timeout, &zero, sizeof(int));
+  return v;
+}
 }  // namespace gdn
 
 extern "C" {
@@ -194,11 +217,17 @@ int b200gdn_prep_bwd(const b200gdn_prep_args* a, void* stream) {
   return gdn::launch_prep(*a, static_cast<cudaStream_t>(stream), true);
 }
 
+int b200gdn_selftest_wait_expiry(void* stream) {
+  gdn::g_launches = 0;
+  gdn::selftest_wait_expiry_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(2000u);
+  return gdn::check_launch("selftest_wait_expiry");
+}
+
 int b200gdn_device_status(void) {
   struct { const char* name; int (*flag)(); } k[] = {
       {"intra_fwd", gdn::intra_fwd_timeout_flag}, {"scan_fwd", gdn::scan_fwd_timeout_flag}, {"out_fwd", gdn::out_fwd_timeout_flag},
       {"dv_local", gdn::dv_local_timeout_flag},   {"scan_bwd", gdn::scan_bwd_timeout_flag}, {"bwd_dqk", gdn::bwd_dqk_timeout_flag},
-      {"bwd_wy", gdn::bwd_wy_timeout_flag}};
+      {"bwd_wy", gdn::bwd_wy_timeout_flag},       {"selftest", gdn::selftest_timeout_flag}};
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return gdn::set_error(B200GDN_ERR_CUDA, "device_status: %s", cudaGetErrorString(e));
   int rc = B200GDN_OK;

@@ -30,7 +30,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(bar)) : "memory");
 }
 // Bounded wait for the phase with the given parity.  Returns false when the limit expires.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = 20000000u) {
+// (A legitimate wait in these kernels lasts microseconds; the default limit is seconds of polling.)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 22)) {
   const uint32_t addr = smem_addr(bar);
   for (uint32_t it = 0; it < limit; ++it) {
     uint32_t done;

@@ -223,6 +223,12 @@ int64_t b200gdn_bwd_workspace_bytes(int32_t rows, int32_t H, int32_t HV, int32_t
  * B200GDN_ERR_TIMEOUT (the results of the flagged kernel are then invalid; b200gdn_last_error() names it). */
 int b200gdn_device_status(void);
 
+/* No counterpart in the reference.  Launches one warp that waits, with a limit of 2000 polls, on an mbarrier nothing
+ * completes: the wait gives up, raises the flag and the kernel ends normally.  The next b200gdn_device_status() then
+ * returns B200GDN_ERR_TIMEOUT ("selftest") and the one after it B200GDN_OK: a host-side check that the expiry path of
+ * the kernels' waits works and leaves the context usable, without faulting or hanging the GPU. */
+int b200gdn_selftest_wait_expiry(void* stream);
+
 /* Number of kernels the last call on this thread enqueued (bench bookkeeping). */
 int b200gdn_last_launch_count(void);
 int b200gdn_abi_version(void);

@@ -1,6 +1,7 @@
 """GPU parity of the chunk path: every stage through the C ABI against the oracle's stage, then the
 public API against the naive recurrence with the reference's own tolerances
 (tests/ops/test_gdn.py:108-200: o/ht 0.005, dq/dk/dv/dh0 0.008, dbeta/dg 0.02)."""
+import ctypes
 import os
 
 import numpy as np
@@ -344,3 +345,21 @@ def test_public_api_against_reference_triton_path(name):
     O.assert_close('ht', torch.from_numpy(gold['ht']), ht.cpu(), 0.005)
     for n, tol in (('q', 0.008), ('k', 0.008), ('v', 0.008), ('h0', 0.008), ('beta', 0.02), ('g', 0.02)):
         O.assert_close('d' + n, torch.from_numpy(gold['d' + n]), leaves[n].grad.float().cpu(), tol)
+
+
+def test_wait_expiry_is_reported_and_context_survives():
+    """Failure detection without a GPU fault: a kernel whose wait can never complete gives up after its (short)
+    limit, the host reads B200GDN_ERR_TIMEOUT, the flag clears, and the context keeps working."""
+    import b200gdn
+    from b200gdn import _lib
+    lib = _lib.load()
+    b200gdn.device_status()                                     # clean before
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.b200gdn_selftest_wait_expiry(ctypes.c_void_p(st)) == 0
+    with pytest.raises(b200gdn.B200GDNError, match='selftest'):
+        b200gdn.device_status()
+    b200gdn.device_status()                                     # flag was cleared by the read
+    d = make_case(seed=1, **STAGE_CASES['d128_dense'])          # and real work still runs and is right
+    fwd, _ = oracle_chain(d)
+    out = run_abi(d, do_bwd=False)
+    O.assert_close('o after expiry', fwd['o'], out['o'], 0.005)
