@@ -189,6 +189,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
       float r[16];
       acc_ld32q(TM_DP, q, cs, r);
       tc5::tmem_ld_wait();
+      FragStore fs;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int j0 = cs + i * 8 + 2 * t;
@@ -198,9 +199,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
           const int ii = (e & 2) ? r_hi : r_lo, jj = j0 + (e & 1);
           v[e] = (ii >= jj) ? r[4 * i + e] * a.scale * exp2f(((e & 2) ? g_hi : g_lo) - gs[jj]) : 0.f;
         }
-        *swz_ptr32(Ps, r_lo, j0, BT) = pack_bf16(v[0], v[1]);
-        *swz_ptr32(Ps, r_hi, j0, BT) = pack_bf16(v[2], v[3]);
+        fs.set(i, v[0], v[1], v[2], v[3]);
       }
+      fs.store(Ps, BT, q * 16, cs, lane);
     }
     for (int idx = tid; idx < BT * DV / 8; idx += NTHREADS) {
       const int row = (idx % (BT * 8)) / 8;
@@ -254,10 +255,13 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
 #pragma unroll
       for (int b = 0; b < KB; ++b) {
         float (&r)[16] = racc[b];
+        FragStore fs;
+        FragLoad fq;
+        fq.load(Qs, BT, q * 16, ck + b * 32, lane);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int col = ck + b * 32 + i * 8 + 2 * t;
-          const float2 qa = swz_ld2(Qs, r_lo, col, BT), qb = swz_ld2(Qs, r_hi, col, BT);
+          const float2 qa = fq.lo2(i), qb = fq.hi2(i);
           rq_lo += r[4 * i] * qa.x + r[4 * i + 1] * qa.y;
           rq_hi += r[4 * i + 2] * qb.x + r[4 * i + 3] * qb.y;
           if (GROUPED) {
@@ -274,11 +278,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
               if (!last) *pp = make_float2(r[4 * i + 2], r[4 * i + 3]);
             }
           }
-          if (last) {
-            *swz_ptr32(Hp, r_lo, col, BT) = pack_bf16(r[4 * i], r[4 * i + 1]);
-            *swz_ptr32(Hp, r_hi, col, BT) = pack_bf16(r[4 * i + 2], r[4 * i + 3]);
-          }
+          fs.set(i, r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
         }
+        if (last) fs.store(Hp, BT, q * 16, ck + b * 32, lane);
       }
       rq_lo += __shfl_xor_sync(0xffffffffu, rq_lo, 1);
       rq_lo += __shfl_xor_sync(0xffffffffu, rq_lo, 2);
@@ -332,11 +334,14 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
           s[b][4 * i] *= e_lo; s[b][4 * i + 1] *= e_lo; s[b][4 * i + 2] *= e_hi; s[b][4 * i + 3] *= e_hi;
         }
 #pragma unroll
-      for (int b = 0; b < KB; ++b)
+      for (int b = 0; b < KB; ++b) {
+        FragStore fs;
+        FragLoad fk;
+        fk.load(Ks, BT, q * 16, ck + b * 32, lane);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int col = ck + b * 32 + i * 8 + 2 * t;
-          const float2 ka = swz_ld2(Ks, r_lo, col, BT), kb = swz_ld2(Ks, r_hi, col, BT);
+          const float2 ka = fk.lo2(i), kb = fk.hi2(i);
           rs += s[b][4 * i] * ka.x + s[b][4 * i + 1] * ka.y + s[b][4 * i + 2] * kb.x + s[b][4 * i + 3] * kb.y;
           const float d0 = r[b][4 * i] + s[b][4 * i], d1 = r[b][4 * i + 1] + s[b][4 * i + 1];
           const float d2 = r[b][4 * i + 2] + s[b][4 * i + 2], d3 = r[b][4 * i + 3] + s[b][4 * i + 3];
@@ -357,11 +362,10 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
               if (!last) *pp = hi;
             }
           }
-          if (last) {
-            *swz_ptr32(dHp, r_lo, col, BT) = pack_bf16(lo.x, lo.y);
-            *swz_ptr32(dHp, r_hi, col, BT) = pack_bf16(hi.x, hi.y);
-          }
+          fs.set(i, lo.x, lo.y, hi.x, hi.y);
         }
+        if (last) fs.store(dHp, BT, q * 16, ck + b * 32, lane);
+      }
       rk_lo += __shfl_xor_sync(0xffffffffu, rk_lo, 1);
       rk_lo += __shfl_xor_sync(0xffffffffu, rk_lo, 2);
       rk_hi += __shfl_xor_sync(0xffffffffu, rk_hi, 1);

@@ -45,12 +45,17 @@ struct WyMaps {
   CUtensorMap k, v, du, a, h, dv, dk;
 };
 
-// sum over the 8 row-lanes of a warp (lanes that differ in bits 2..4), result valid in lanes with g == 0
-__device__ __forceinline__ float sum_over_g(float x) {
-  x += __shfl_xor_sync(0xffffffffu, x, 4);
-  x += __shfl_xor_sync(0xffffffffu, x, 8);
-  x += __shfl_xor_sync(0xffffffffu, x, 16);
-  return x;
+// Eight values per lane (v[2 i + p]: n-tile i, column parity p), each to be summed over the eight row-lanes of the warp
+// (lanes that differ in bits 2..4).  Recursive halving: 7 shuffles instead of 24; afterwards the lane with row index g
+// holds the complete sum of value g, i.e. of column 8 (g >> 1) + 2 t + (g & 1) of the warp's 32-column block.
+__device__ __forceinline__ float sum8_over_g(const float (&v)[8], int g) {
+  float w[4], x[2];
+  const bool h4 = g & 4, h2 = g & 2, h1 = g & 1;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) w[j] = (h4 ? v[4 + j] : v[j]) + __shfl_xor_sync(0xffffffffu, h4 ? v[j] : v[4 + j], 16);
+#pragma unroll
+  for (int j = 0; j < 2; ++j) x[j] = (h2 ? w[2 + j] : w[j]) + __shfl_xor_sync(0xffffffffu, h2 ? w[j] : w[2 + j], 8);
+  return (h1 ? x[1] : x[0]) + __shfl_xor_sync(0xffffffffu, h1 ? x[0] : x[1], 4);
 }
 __device__ __forceinline__ float sum_over_t(float x) {
   x += __shfl_xor_sync(0xffffffffu, x, 1);
@@ -183,10 +188,17 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
       ph.commit();
     }
     // A with its columns scaled by beta 2^gamma (an operand of phase 3), while phase 1 runs
-    for (int idx = tid; idx < BT * BT / 2; idx += NTHREADS) {
-      const int i = idx / (BT / 2), j = (idx % (BT / 2)) * 2;
-      const float2 x = swz_ld2(As, i, j, BT);
-      *swz_ptr32(Abs, i, j, BT) = pack_bf16(x.x * bge[j], x.y * bge[j + 1]);
+    {   // every warp rescales its own 16 x 32 block of the tile
+      FragLoad fa;
+      fa.load(As, BT, q * 16, cs, lane);
+      FragStore fs;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 sc = *reinterpret_cast<const float2*>(&bge[cs + i * 8 + 2 * t]);
+        const float2 al = fa.lo2(i), ah = fa.hi2(i);
+        fs.set(i, al.x * sc.x, al.y * sc.y, ah.x * sc.x, ah.y * sc.y);
+      }
+      fs.store(Abs, BT, q * 16, cs, lane);
     }
     const float g_lo = gs[r_lo], g_hi = gs[r_hi];
     const float b_lo = bet[r_lo], b_hi = bet[r_hi];
@@ -199,13 +211,12 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
       for (int b = 0; b < KB; ++b) acc_ld32q(TM_BIG, q, hc * (DK / 2) + b * 32, r[b]);
       tc5::tmem_ld_wait();
 #pragma unroll
-      for (int b = 0; b < KB; ++b)
+      for (int b = 0; b < KB; ++b) {
+        FragStore fs;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int col = hc * (DK / 2) + b * 32 + i * 8 + 2 * t;
-          *swz_ptr32(dWs, r_lo, col, BT) = pack_bf16(r[b][4 * i], r[b][4 * i + 1]);
-          *swz_ptr32(dWs, r_hi, col, BT) = pack_bf16(r[b][4 * i + 2], r[b][4 * i + 3]);
-        }
+        for (int i = 0; i < 4; ++i) fs.set(i, r[b][4 * i], r[b][4 * i + 1], r[b][4 * i + 2], r[b][4 * i + 3]);
+        fs.store(dWs, BT, q * 16, hc * (DK / 2) + b * 32, lane);
+      }
     }
     float dA2[16];
     acc_ld32q(TM_S1, q, cs, dA2);
@@ -222,16 +233,18 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
       ph.commit();
     }
     // colsum(A . dA2), off the critical path
+    const int gcol = cs + 8 * (g >> 1) + 2 * t + (g & 1);   // the column whose sum this lane ends up with
+    {
+      FragLoad fa;
+      fa.load(As, BT, q * 16, cs, lane);
+      float pv[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int col = cs + i * 8 + 2 * t;
-      const float2 al = swz_ld2(As, r_lo, col, BT), ah = swz_ld2(As, r_hi, col, BT);
-      const float s0 = sum_over_g(al.x * dA2[4 * i] + ah.x * dA2[4 * i + 2]);
-      const float s1 = sum_over_g(al.y * dA2[4 * i + 1] + ah.y * dA2[4 * i + 3]);
-      if (g == 0) {
-        c_vb[q * BT + col] = s0;
-        c_vb[q * BT + col + 1] = s1;
+      for (int i = 0; i < 4; ++i) {
+        const float2 al = fa.lo2(i), ah = fa.hi2(i);
+        pv[2 * i] = al.x * dA2[4 * i] + ah.x * dA2[4 * i + 2];
+        pv[2 * i + 1] = al.y * dA2[4 * i + 1] + ah.y * dA2[4 * i + 3];
       }
+      c_vb[q * BT + gcol] = sum8_over_g(pv, g);
     }
     if (__syncthreads_or(!ph.wait())) { failed = true; break; }
 
@@ -243,6 +256,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
 #pragma unroll
       for (int b = 0; b < VB; ++b) acc_ld32q(TM_BIG, q, hc * (DV / 2) + b * 32, rv[b]);
       tc5::tmem_ld_wait();
+      FragStore fs_dA;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int col = cs + i * 8 + 2 * t;
@@ -252,9 +266,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
           const int ii = (e & 2) ? r_hi : r_lo, jj = col + (e & 1);
           v[e] = (ii > jj) ? r[4 * i + e] * bge[jj] + dA2[4 * i + e] * bet[jj] : 0.f;
         }
-        *swz_ptr32(dAs, r_lo, col, BT) = pack_bf16(v[0], v[1]);
-        *swz_ptr32(dAs, r_hi, col, BT) = pack_bf16(v[2], v[3]);
+        fs_dA.set(i, v[0], v[1], v[2], v[3]);
       }
+      fs_dA.store(dAs, BT, q * 16, cs, lane);
       tc5::fence_async_smem();
       tc5::fence_before_sync();
       __syncthreads();
@@ -266,25 +280,26 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
         issue_mma_t<BT / 16>(TM_BIG, opAb_mn, opdW_mn, 64, DK, 0);
         ph.commit();
       }
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int col = cs + i * 8 + 2 * t;
-        const float2 al = swz_ld2(As, r_lo, col, BT), ah = swz_ld2(As, r_hi, col, BT);
-        const float s0 = sum_over_g(al.x * r[4 * i] + ah.x * r[4 * i + 2]);
-        const float s1 = sum_over_g(al.y * r[4 * i + 1] + ah.y * r[4 * i + 3]);
-        if (g == 0) {
-          c_kbg[q * BT + col] = s0;
-          c_kbg[q * BT + col + 1] = s1;
-        }
-      }
-#pragma unroll
-      for (int b = 0; b < VB; ++b)
+      {
+        FragLoad fa;
+        fa.load(As, BT, q * 16, cs, lane);
+        float pv[8];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int col = hc * (DV / 2) + b * 32 + i * 8 + 2 * t;
-          *swz_ptr32(Stg, r_lo, col, BT) = pack_bf16(rv[b][4 * i] * b_lo, rv[b][4 * i + 1] * b_lo);
-          *swz_ptr32(Stg, r_hi, col, BT) = pack_bf16(rv[b][4 * i + 2] * b_hi, rv[b][4 * i + 3] * b_hi);
+          const float2 al = fa.lo2(i), ah = fa.hi2(i);
+          pv[2 * i] = al.x * r[4 * i] + ah.x * r[4 * i + 2];
+          pv[2 * i + 1] = al.y * r[4 * i + 1] + ah.y * r[4 * i + 3];
         }
+        c_kbg[q * BT + gcol] = sum8_over_g(pv, g);
+      }
+#pragma unroll
+      for (int b = 0; b < VB; ++b) {
+        FragStore fs;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          fs.set(i, rv[b][4 * i] * b_lo, rv[b][4 * i + 1] * b_lo, rv[b][4 * i + 2] * b_hi, rv[b][4 * i + 3] * b_hi);
+        fs.store(Stg, BT, q * 16, hc * (DV / 2) + b * 32, lane);
+      }
     }
     tc5::fence_async_smem();
     __syncthreads();
@@ -304,12 +319,10 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
       float r[16];
       acc_ld32q(TM_S1, q, cs, r);
       tc5::tmem_ld_wait();
+      FragStore fs;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int col = cs + i * 8 + 2 * t;
-        *swz_ptr32(Ys, r_lo, col, BT) = pack_bf16(r[4 * i], r[4 * i + 1]);
-        *swz_ptr32(Ys, r_hi, col, BT) = pack_bf16(r[4 * i + 2], r[4 * i + 3]);
-      }
+      for (int i = 0; i < 4; ++i) fs.set(i, r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+      fs.store(Ys, BT, q * 16, cs, lane);
     }
     if (tid == 32) tma::store_wait_read<0>();   // the dv staging tile is rewritten (as M2) after the next barrier
     tc5::fence_async_smem();
@@ -331,6 +344,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
       acc_ld32q(TM_S1, q, cs, r);
       acc_ld32q(TM_KK, q, cs, kk);
       tc5::tmem_ld_wait();
+      FragStore fs_m2;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int col = cs + i * 8 + 2 * t;
@@ -339,9 +353,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
           const int ii = (e & 2) ? r_hi : r_lo, jj = col + (e & 1);
           m[4 * i + e] = (ii > jj) ? -r[4 * i + e] * exp2f(((e & 2) ? g_hi : g_lo) - gs[jj]) : 0.f;
         }
-        *swz_ptr32(M2s, r_lo, col, BT) = pack_bf16(m[4 * i] * b_lo, m[4 * i + 1] * b_lo);
-        *swz_ptr32(M2s, r_hi, col, BT) = pack_bf16(m[4 * i + 2] * b_hi, m[4 * i + 3] * b_hi);
+        fs_m2.set(i, m[4 * i] * b_lo, m[4 * i + 1] * b_lo, m[4 * i + 2] * b_hi, m[4 * i + 3] * b_hi);
       }
+      fs_m2.store(M2s, BT, q * 16, cs, lane);
     }
     tc5::fence_async_smem();
     tc5::fence_before_sync();
@@ -356,18 +370,15 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
     }
     {
       float rmk_lo = 0.f, rmk_hi = 0.f;
+      float pv[8];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int col = cs + i * 8 + 2 * t;
         rmk_lo += m[4 * i] * kk[4 * i] + m[4 * i + 1] * kk[4 * i + 1];
         rmk_hi += m[4 * i + 2] * kk[4 * i + 2] + m[4 * i + 3] * kk[4 * i + 3];
-        const float s0 = sum_over_g(m[4 * i] * b_lo * kk[4 * i] + m[4 * i + 2] * b_hi * kk[4 * i + 2]);
-        const float s1 = sum_over_g(m[4 * i + 1] * b_lo * kk[4 * i + 1] + m[4 * i + 3] * b_hi * kk[4 * i + 3]);
-        if (g == 0) {
-          c_m2[q * BT + col] = s0;
-          c_m2[q * BT + col + 1] = s1;
-        }
+        pv[2 * i] = m[4 * i] * b_lo * kk[4 * i] + m[4 * i + 2] * b_hi * kk[4 * i + 2];
+        pv[2 * i + 1] = m[4 * i + 1] * b_lo * kk[4 * i + 1] + m[4 * i + 3] * b_hi * kk[4 * i + 3];
       }
+      c_m2[q * BT + gcol] = sum8_over_g(pv, g);
       rmk_lo = sum_over_t(rmk_lo);
       rmk_hi = sum_over_t(rmk_hi);
       if (t == 0) {
@@ -424,7 +435,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
       for (int b = 0; b < KB; ++b) acc_ld32q(TM_BIG, q, hc * (DK / 2) + b * 32, r[b]);
       tc5::tmem_ld_wait();
 #pragma unroll
-      for (int b = 0; b < KB; ++b)
+      for (int b = 0; b < KB; ++b) {
+        FragStore fs;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int n8 = b * 4 + i, col = n8 * 8 + 2 * t;
@@ -442,10 +454,11 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
             if (r_lo < cm.len) *reinterpret_cast<float2*>(dkbuf + r_lo * dkstride + col) = make_float2(d0, d1);
             if (r_hi < cm.len) *reinterpret_cast<float2*>(dkbuf + r_hi * dkstride + col) = make_float2(d2, d3);
           } else {
-            *swz_ptr32(dWs, r_lo, hc * (DK / 2) + col, BT) = pack_bf16(d0, d1);
-            *swz_ptr32(dWs, r_hi, hc * (DK / 2) + col, BT) = pack_bf16(d2, d3);
+            fs.set(i, d0, d1, d2, d3);
           }
         }
+        if (last) fs.store(dWs, BT, q * 16, hc * (DK / 2) + b * 32, lane);
+      }
     }
     tc5::fence_async_smem();
     tc5::fence_before_sync();

@@ -99,7 +99,8 @@ __global__ void __launch_bounds__(NTHREADS, 4) dv_local_kernel(const b200gdn_chu
       acc_ld32(TM_P, warp, 32, r[1]);
       tc5::tmem_ld_wait();
 #pragma unroll
-      for (int b = 0; b < 2; ++b)
+      for (int b = 0; b < 2; ++b) {
+        FragStore fs;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int j0 = b * 32 + i * 8 + 2 * t;
@@ -109,9 +110,10 @@ __global__ void __launch_bounds__(NTHREADS, 4) dv_local_kernel(const b200gdn_chu
             const int ii = (e & 2) ? r_hi : r_lo, jj = j0 + (e & 1);
             v[e] = (ii >= jj && ii < cm.len) ? r[b][4 * i + e] * a.scale * exp2f(((e & 2) ? g_hi : g_lo) - gs[jj]) : 0.f;
           }
-          *swz_ptr32(Ps, r_lo, j0, BT) = pack_bf16(v[0], v[1]);
-          *swz_ptr32(Ps, r_hi, j0, BT) = pack_bf16(v[2], v[3]);
+          fs.set(i, v[0], v[1], v[2], v[3]);
         }
+        fs.store(Ps, BT, warp * 16, b * 32, lane);
+      }
     }
     tc5::fence_async_smem();
     tc5::fence_before_sync();
@@ -130,13 +132,12 @@ __global__ void __launch_bounds__(NTHREADS, 4) dv_local_kernel(const b200gdn_chu
       for (int b = 0; b < DV / 32; ++b) acc_ld32(TM_D, warp, b * 32, r[b]);
       tc5::tmem_ld_wait();
 #pragma unroll
-      for (int b = 0; b < DV / 32; ++b)
+      for (int b = 0; b < DV / 32; ++b) {
+        FragStore fs;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int col = b * 32 + i * 8 + 2 * t;
-          *swz_ptr32(Stg, r_lo, col, BT) = pack_bf16(r[b][4 * i], r[b][4 * i + 1]);
-          *swz_ptr32(Stg, r_hi, col, BT) = pack_bf16(r[b][4 * i + 2], r[b][4 * i + 3]);
-        }
+        for (int i = 0; i < 4; ++i) fs.set(i, r[b][4 * i], r[b][4 * i + 1], r[b][4 * i + 2], r[b][4 * i + 3]);
+        fs.store(Stg, BT, warp * 16, b * 32, lane);
+      }
       tc5::fence_async_smem();
       tc5::fence_before_sync();
       __syncthreads();

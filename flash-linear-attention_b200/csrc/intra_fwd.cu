@@ -247,22 +247,27 @@ __global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_ch
 
     // ---- bf16 operand tiles (over the fp32 inverse and the merge temporary, hence through registers):
     //      A with its columns scaled for the W and U right-hand sides, and A itself
-    {
-      float2 x[BT * BT / 2 / NTHREADS];
+    {   // every warp converts its own 16 x 32 block (rows 16 q .., columns cs ..) in the accumulator-fragment layout
+      float2 x_lo[4], x_hi[4];
 #pragma unroll
-      for (int it = 0; it < BT * BT / 2 / NTHREADS; ++it) {
-        const int idx = it * NTHREADS + tid;
-        x[it] = *reinterpret_cast<const float2*>(&Af[(idx >> 5) * LDF + (idx & 31) * 2]);
+      for (int i = 0; i < 4; ++i) {
+        const int col = cs + i * 8 + 2 * t;
+        x_lo[i] = *reinterpret_cast<const float2*>(&Af[r_lo * LDF + col]);
+        x_hi[i] = *reinterpret_cast<const float2*>(&Af[r_hi * LDF + col]);
       }
       __syncthreads();
+      FragStore fw, fu, fa;
 #pragma unroll
-      for (int it = 0; it < BT * BT / 2 / NTHREADS; ++it) {
-        const int idx = it * NTHREADS + tid;
-        const int i = idx >> 5, j = (idx & 31) * 2;
-        *swz_ptr32(Aw, i, j, BT) = pack_bf16(x[it].x * bge[j], x[it].y * bge[j + 1]);
-        *swz_ptr32(Au, i, j, BT) = pack_bf16(x[it].x * bet[j], x[it].y * bet[j + 1]);
-        *swz_ptr32(Ab, i, j, BT) = pack_bf16(x[it].x, x[it].y);
+      for (int i = 0; i < 4; ++i) {
+        const int col = cs + i * 8 + 2 * t;
+        const float2 sw = *reinterpret_cast<const float2*>(&bge[col]), su = *reinterpret_cast<const float2*>(&bet[col]);
+        fw.set(i, x_lo[i].x * sw.x, x_lo[i].y * sw.y, x_hi[i].x * sw.x, x_hi[i].y * sw.y);
+        fu.set(i, x_lo[i].x * su.x, x_lo[i].y * su.y, x_hi[i].x * su.x, x_hi[i].y * su.y);
+        fa.set(i, x_lo[i].x, x_lo[i].y, x_hi[i].x, x_hi[i].y);
       }
+      fw.store(Aw, BT, q * 16, cs, lane);
+      fu.store(Au, BT, q * 16, cs, lane);
+      fa.store(Ab, BT, q * 16, cs, lane);
     }
     tc5::fence_async_smem();
     tc5::fence_before_sync();
@@ -306,13 +311,12 @@ __global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_ch
         ph.commit();
       }
 #pragma unroll
-      for (int b = 0; b < KB; ++b)
+      for (int b = 0; b < KB; ++b) {
+        FragStore fs;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int col = ck + b * 32 + i * 8 + 2 * t;
-          *swz_ptr32(Ks, r_lo, col, BT) = pack_bf16(rw[b][4 * i], rw[b][4 * i + 1]);
-          *swz_ptr32(Ks, r_hi, col, BT) = pack_bf16(rw[b][4 * i + 2], rw[b][4 * i + 3]);
-        }
+        for (int i = 0; i < 4; ++i) fs.set(i, rw[b][4 * i], rw[b][4 * i + 1], rw[b][4 * i + 2], rw[b][4 * i + 3]);
+        fs.store(Ks, BT, q * 16, ck + b * 32, lane);
+      }
       tc5::fence_async_smem();
       if (!ph.sync_wait()) {
         failed = true;
@@ -331,13 +335,12 @@ __global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_ch
         for (int b = 0; b < VB; ++b) acc_ld32q(tm, q, cv + b * 32, ru[b]);
         tc5::tmem_ld_wait();
 #pragma unroll
-        for (int b = 0; b < VB; ++b)
+        for (int b = 0; b < VB; ++b) {
+          FragStore fs;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int col = cv + b * 32 + i * 8 + 2 * t;
-            *swz_ptr32(Vs, r_lo, col, BT) = pack_bf16(ru[b][4 * i], ru[b][4 * i + 1]);
-            *swz_ptr32(Vs, r_hi, col, BT) = pack_bf16(ru[b][4 * i + 2], ru[b][4 * i + 3]);
-          }
+          for (int i = 0; i < 4; ++i) fs.set(i, ru[b][4 * i], ru[b][4 * i + 1], ru[b][4 * i + 2], ru[b][4 * i + 3]);
+          fs.store(Vs, BT, q * 16, cv + b * 32, lane);
+        }
         tc5::fence_async_smem();
         tc5::fence_before_sync();
         __syncthreads();

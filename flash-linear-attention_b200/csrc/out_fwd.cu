@@ -107,7 +107,8 @@ __global__ void __launch_bounds__(NTHREADS, 3) out_fwd_kernel(const b200gdn_chun
       acc_ld32(tm, warp, 32, r[1]);
       tc5::tmem_ld_wait();
 #pragma unroll
-      for (int b = 0; b < 2; ++b)
+      for (int b = 0; b < 2; ++b) {
+        FragStore fs;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int j0 = b * 32 + i * 8 + 2 * t;
@@ -117,9 +118,10 @@ __global__ void __launch_bounds__(NTHREADS, 3) out_fwd_kernel(const b200gdn_chun
             const int ii = (e & 2) ? r_hi : r_lo, jj = j0 + (e & 1);
             v[e] = (ii >= jj) ? r[b][4 * i + e] * exp2f(((e & 2) ? g_hi : g_lo) - gs[jj]) : 0.f;
           }
-          *swz_ptr32(Ps, r_lo, j0, BT) = pack_bf16(v[0], v[1]);
-          *swz_ptr32(Ps, r_hi, j0, BT) = pack_bf16(v[2], v[3]);
+          fs.set(i, v[0], v[1], v[2], v[3]);
         }
+        fs.store(Ps, BT, warp * 16, b * 32, lane);
+      }
     }
     if (!tc5::mbar_wait(bar_h, 0)) failed = true;
     tc5::fence_async_smem();
@@ -175,13 +177,13 @@ __global__ void __launch_bounds__(NTHREADS, 3) out_fwd_kernel(const b200gdn_chun
             for (int b = 0; b < DV / 32; ++b) acc_ld32(tm, warp, b * 32, r[b]);
             tc5::tmem_ld_wait();
 #pragma unroll
-            for (int b = 0; b < DV / 32; ++b)
+            for (int b = 0; b < DV / 32; ++b) {
+              FragStore fs;
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const int col = b * 32 + i * 8 + 2 * t;
-                *swz_ptr32(Qs, r_lo, col, BT) = pack_bf16(r[b][4 * i] * a.scale, r[b][4 * i + 1] * a.scale);
-                *swz_ptr32(Qs, r_hi, col, BT) = pack_bf16(r[b][4 * i + 2] * a.scale, r[b][4 * i + 3] * a.scale);
-              }
+              for (int i = 0; i < 4; ++i)
+                fs.set(i, r[b][4 * i] * a.scale, r[b][4 * i + 1] * a.scale, r[b][4 * i + 2] * a.scale, r[b][4 * i + 3] * a.scale);
+              fs.store(Qs, BT, warp * 16, b * 32, lane);
+            }
             tc5::fence_async_smem();
             tc5::fence_before_sync();
             __syncthreads();

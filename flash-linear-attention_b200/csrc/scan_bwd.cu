@@ -190,13 +190,12 @@ __global__ void __launch_bounds__(NTHREADS) scan_bwd_kernel(const b200gdn_chunk_
         tc5::tmem_ld_wait();
       }
 #pragma unroll
-      for (int hf = 0; hf < NH; ++hf)
+      for (int hf = 0; hf < NH; ++hf) {
+        FragStore fs;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int col = 32 * hc + 8 * i + 2 * t, r = srow0 + 16 * hf + g;
-          sts32(swz_pair_addr(sb_tile, DK, r, col), pack_bf16(Sr[hf][4 * i], Sr[hf][4 * i + 1]));
-          sts32(swz_pair_addr(sb_tile, DK, r + 8, col), pack_bf16(Sr[hf][4 * i + 2], Sr[hf][4 * i + 3]));
-        }
+        for (int i = 0; i < 4; ++i) fs.set(i, Sr[hf][4 * i], Sr[hf][4 * i + 1], Sr[hf][4 * i + 2], Sr[hf][4 * i + 3]);
+        fs.store(sb_tile, DK, srow0 + 16 * hf, 32 * hc, lane);
+      }
       if (!tc5::mbar_wait(&full[s], (ic / NSTAGE) & 1)) { failed = true; break; }
       const float glast = gs[BT - 1];
       const float dec = exp2f(glast);
@@ -218,16 +217,24 @@ __global__ void __launch_bounds__(NTHREADS) scan_bwd_kernel(const b200gdn_chunk_
       const float q_lo = ok_lo ? a.scale * exp2f(gs[r_lo]) : 0.f, q_hi = ok_hi ? a.scale * exp2f(gs[r_hi]) : 0.f;
       const float e_lo = ok_lo ? exp2f(glast - gs[r_lo]) : 0.f, e_hi = ok_hi ? exp2f(glast - gs[r_hi]) : 0.f;
       float2 l_lo[4], l_hi[4];
+      {
+        FragLoad fl;
+        fl.load(dl_tile, BT, 16 * q, 32 * hc, lane);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int col = 32 * hc + 8 * i + 2 * t;
-        l_lo[i] = unpack_bf16(lds32(swz_pair_addr(dl_tile, BT, r_lo, col)));
-        l_hi[i] = unpack_bf16(lds32(swz_pair_addr(dl_tile, BT, r_hi, col)));
+        for (int i = 0; i < 4; ++i) {
+          l_lo[i] = fl.lo2(i);
+          l_hi[i] = fl.hi2(i);
+        }
         if (has_do) {
-          const uint32_t a_lo = swz_pair_addr(do_tile, BT, r_lo, col), a_hi = swz_pair_addr(do_tile, BT, r_hi, col);
-          const float2 d_lo = unpack_bf16(lds32(a_lo)), d_hi = unpack_bf16(lds32(a_hi));
-          sts32(a_lo, pack_bf16(d_lo.x * q_lo, d_lo.y * q_lo));
-          sts32(a_hi, pack_bf16(d_hi.x * q_hi, d_hi.y * q_hi));
+          FragLoad fd;
+          fd.load(do_tile, BT, 16 * q, 32 * hc, lane);
+          FragStore fs;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 d_lo = fd.lo2(i), d_hi = fd.hi2(i);
+            fs.set(i, d_lo.x * q_lo, d_lo.y * q_lo, d_hi.x * q_hi, d_hi.y * q_hi);
+          }
+          fs.store(do_tile, BT, 16 * q, 32 * hc, lane);
         }
       }
       if (!tc5::mbar_wait(v_ready, ic & 1)) { failed = true; break; }
@@ -235,14 +242,14 @@ __global__ void __launch_bounds__(NTHREADS) scan_bwd_kernel(const b200gdn_chunk_
       float acc[16];
       tc5::tmem_ld_16x256b_x4(TM_V + s_lane + 32 * hc, acc);
       tc5::tmem_ld_wait();
+      FragStore fs_d2;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int col = 32 * hc + 8 * i + 2 * t;
         const float v00 = ok_lo ? acc[4 * i] * e_lo + l_lo[i].x : 0.f, v01 = ok_lo ? acc[4 * i + 1] * e_lo + l_lo[i].y : 0.f;
         const float v10 = ok_hi ? acc[4 * i + 2] * e_hi + l_hi[i].x : 0.f, v11 = ok_hi ? acc[4 * i + 3] * e_hi + l_hi[i].y : 0.f;
-        sts32(swz_pair_addr(d2_tile, BT, r_lo, col), pack_bf16(v00, v01));
-        sts32(swz_pair_addr(d2_tile, BT, r_hi, col), pack_bf16(v10, v11));
+        fs_d2.set(i, v00, v01, v10, v11);
       }
+      fs_d2.store(d2_tile, BT, 16 * q, 32 * hc, lane);
       tc5::fence_async_smem();
       tc5::fence_before_sync();
       __syncwarp();

@@ -197,13 +197,12 @@ __global__ void __launch_bounds__(NTHREADS) scan_fwd_kernel(const b200gdn_chunk_
       }
       // bf16 snapshot (operand of W S and source of the h_c store) ...
 #pragma unroll
-      for (int hf = 0; hf < NH; ++hf)
+      for (int hf = 0; hf < NH; ++hf) {
+        FragStore fs;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int col = 32 * hc + 8 * i + 2 * t, r = srow0 + 16 * hf + g;
-          sts32(swz_pair_addr(sb_tile, DK, r, col), pack_bf16(Sr[hf][4 * i], Sr[hf][4 * i + 1]));
-          sts32(swz_pair_addr(sb_tile, DK, r + 8, col), pack_bf16(Sr[hf][4 * i + 2], Sr[hf][4 * i + 3]));
-        }
+        for (int i = 0; i < 4; ++i) fs.set(i, Sr[hf][4 * i], Sr[hf][4 * i + 1], Sr[hf][4 * i + 2], Sr[hf][4 * i + 3]);
+        fs.store(sb_tile, DK, srow0 + 16 * hf, 32 * hc, lane);
+      }
       // ... and the decayed state back to TMEM, where the second contraction accumulates onto it
       if (!tc5::mbar_wait(&full[s], (ic / NSTAGE) & 1)) { failed = true; break; }
       const float glast = gs[BT - 1];
@@ -223,11 +222,14 @@ __global__ void __launch_bounds__(NTHREADS) scan_fwd_kernel(const b200gdn_chunk_
       // v_new = U - V_acc  (rows 16q + {g, g+8}, columns 32*hc ..)
       const int r_lo = 16 * q + g, r_hi = r_lo + 8;
       float2 u_lo[4], u_hi[4];
+      {
+        FragLoad fu;
+        if (has_u) fu.load(u_tile, BT, 16 * q, 32 * hc, lane);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int col = 32 * hc + 8 * i + 2 * t;
-        u_lo[i] = has_u ? unpack_bf16(lds32(swz_pair_addr(u_tile, BT, r_lo, col))) : make_float2(0.f, 0.f);
-        u_hi[i] = has_u ? unpack_bf16(lds32(swz_pair_addr(u_tile, BT, r_hi, col))) : make_float2(0.f, 0.f);
+        for (int i = 0; i < 4; ++i) {
+          u_lo[i] = has_u ? fu.lo2(i) : make_float2(0.f, 0.f);
+          u_hi[i] = has_u ? fu.hi2(i) : make_float2(0.f, 0.f);
+        }
       }
       const float e_lo = r_lo < cm.len ? exp2f(glast - gs[r_lo]) : 0.f;   // rows past the chunk's end contribute nothing
       const float e_hi = r_hi < cm.len ? exp2f(glast - gs[r_hi]) : 0.f;
@@ -236,16 +238,16 @@ __global__ void __launch_bounds__(NTHREADS) scan_fwd_kernel(const b200gdn_chunk_
       float acc[16];
       tc5::tmem_ld_16x256b_x4(TM_V + s_lane + 32 * hc, acc);
       tc5::tmem_ld_wait();
+      FragStore fs_vn, fs_vt;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int col = 32 * hc + 8 * i + 2 * t;
         const float v00 = u_lo[i].x - acc[4 * i], v01 = u_lo[i].y - acc[4 * i + 1];
         const float v10 = u_hi[i].x - acc[4 * i + 2], v11 = u_hi[i].y - acc[4 * i + 3];
-        sts32(swz_pair_addr(vn_tile, BT, r_lo, col), pack_bf16(v00, v01));
-        sts32(swz_pair_addr(vn_tile, BT, r_hi, col), pack_bf16(v10, v11));
-        sts32(swz_pair_addr(vt_tile, BT, r_lo, col), pack_bf16(v00 * e_lo, v01 * e_lo));
-        sts32(swz_pair_addr(vt_tile, BT, r_hi, col), pack_bf16(v10 * e_hi, v11 * e_hi));
+        fs_vn.set(i, v00, v01, v10, v11);
+        fs_vt.set(i, v00 * e_lo, v01 * e_lo, v10 * e_hi, v11 * e_hi);
       }
+      fs_vn.store(vn_tile, BT, 16 * q, 32 * hc, lane);
+      fs_vt.store(vt_tile, BT, 16 * q, 32 * hc, lane);
       tc5::fence_async_smem();
       tc5::fence_before_sync();
       __syncwarp();

@@ -51,6 +51,54 @@ __device__ __forceinline__ float2 swz_ld2(const unsigned char* tile, int row, in
   return unpack_bf16(*reinterpret_cast<const uint32_t*>(tile + tc5::swz_offset(row, col, rows)));
 }
 
+// One 16-row x 32-column block of bf16 pairs in the accumulator-fragment layout (what acc_ld32 / acc_ld32q return,
+// after the epilogue math) on its way into a swizzled tile: set() packs n-tile i, store() writes the block with two
+// stmatrix.x4 (each moves eight rows of four 8 x 8 matrices; lane L supplies the address of row L % 8 of matrix L / 8),
+// instead of eight 32-bit stores per thread.
+struct FragStore {
+  uint32_t lo[4], hi[4];
+  __device__ __forceinline__ void set(int i, float a, float b, float c, float d) {
+    lo[i] = pack_bf16(a, b);
+    hi[i] = pack_bf16(c, d);
+  }
+  // rows row0 .. row0+15, columns col0 .. col0+31 (col0 a multiple of 8) of a tile of `rows` rows
+  __device__ __forceinline__ void store(unsigned char* tile, int rows, int row0, int col0, int lane) const {
+    store(tc5::smem_addr(tile), rows, row0, col0, lane);
+  }
+  // the same with the tile given by its shared-memory address
+  __device__ __forceinline__ void store(uint32_t tile, int rows, int row0, int col0, int lane) const {
+    const uint32_t addr = tile + tc5::swz_offset(row0 + (lane & 7), col0 + 8 * (lane >> 3), rows);
+    asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(lo[0]), "r"(lo[1]),
+                 "r"(lo[2]), "r"(lo[3])
+                 : "memory");
+    asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};\n" ::"r"(addr + 1024u), "r"(hi[0]),
+                 "r"(hi[1]), "r"(hi[2]), "r"(hi[3])
+                 : "memory");
+  }
+};
+
+// The reverse: one 16-row x 32-column block of a swizzled bf16 tile into the accumulator-fragment layout with two
+// ldmatrix.x4: lo[i] / hi[i] hold (row g, row g + 8) x columns (8 i + 2 t, + 1) of the block as bf16 pairs.
+struct FragLoad {
+  uint32_t lo[4], hi[4];
+  __device__ __forceinline__ void load(uint32_t tile, int rows, int row0, int col0, int lane) {
+    const uint32_t addr = tile + tc5::swz_offset(row0 + (lane & 7), col0 + 8 * (lane >> 3), rows);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];\n"
+                 : "=r"(lo[0]), "=r"(lo[1]), "=r"(lo[2]), "=r"(lo[3])
+                 : "r"(addr)
+                 : "memory");
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];\n"
+                 : "=r"(hi[0]), "=r"(hi[1]), "=r"(hi[2]), "=r"(hi[3])
+                 : "r"(addr + 1024u)
+                 : "memory");
+  }
+  __device__ __forceinline__ void load(const unsigned char* tile, int rows, int row0, int col0, int lane) {
+    load(tc5::smem_addr(tile), rows, row0, col0, lane);
+  }
+  __device__ __forceinline__ float2 lo2(int i) const { return unpack_bf16(lo[i]); }
+  __device__ __forceinline__ float2 hi2(int i) const { return unpack_bf16(hi[i]); }
+};
+
 // Zero rows [valid, ROWS) of a swizzled [ROWS][COLS] tile (a ragged last chunk arrives by TMA as a full box
 // whose extra rows belong to the next sequence).  The caller fences and synchronises afterwards.
 template <int ROWS, int COLS>
