@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int ii = (e & 2) ? r_hi : r_lo, jj = j0 + (e & 1);
-          v[e] = (ii >= jj) ? r[4 * i + e] * a.scale * exp2f(((e & 2) ? g_hi : g_lo) - gs[jj]) : 0.f;
+          v[e] = (ii >= jj) ? r[4 * i + e] * a.scale * fast_exp2(((e & 2) ? g_hi : g_lo) - gs[jj]) : 0.f;
         }
         fs.set(i, v[0], v[1], v[2], v[3]);
       }
@@ -205,7 +205,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
     }
     for (int idx = tid; idx < BT * DV / 8; idx += NTHREADS) {
       const int row = (idx % (BT * 8)) / 8;
-      const float fo = a.scale * exp2f(gs[row]);
+      const float fo = a.scale * fast_exp2(gs[row]);
       uint4* po = reinterpret_cast<uint4*>(Do + idx * 16);
       uint4 x = *po;
       uint32_t* xu = reinterpret_cast<uint32_t*>(&x);
@@ -326,7 +326,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
         acc_ld32q(TM_DKI, q, ck + b * 32, r[b]);
       }
       tc5::tmem_ld_wait();
-      const float e_lo = exp2f(glast - g_lo), e_hi = exp2f(glast - g_hi);
+      const float e_lo = fast_exp2(glast - g_lo), e_hi = fast_exp2(glast - g_hi);
 #pragma unroll
       for (int b = 0; b < KB; ++b)
 #pragma unroll
@@ -405,7 +405,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
         sh += red[w];
         sr += red[8 + w];
       }
-      const float tail = exp2f(glast) * sh + sr;
+      const float tail = fast_exp2(glast) * sh + sr;
       const float dGrow = (rqs[tid] + rqs[BT + tid]) - (rks[tid] + rks[BT + tid]);
       a.dG[(row0 + tid) * a.HV + hv] = dGrow + (tid == cm.len - 1 ? tail : 0.f);
     }

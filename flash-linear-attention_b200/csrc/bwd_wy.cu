@@ -172,7 +172,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
       zero_tail_rows<BT, BT>(As, cm.len, tid, NTHREADS);
     }
     if (tid < BT) {   // bet[tid] was written by this very thread
-      const float e = exp2f(gs[tid]);
+      const float e = fast_exp2(gs[tid]);
       eg[tid] = e;
       bge[tid] = bet[tid] * e;
     }
@@ -351,7 +351,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int ii = (e & 2) ? r_hi : r_lo, jj = col + (e & 1);
-          m[4 * i + e] = (ii > jj) ? -r[4 * i + e] * exp2f(((e & 2) ? g_hi : g_lo) - gs[jj]) : 0.f;
+          m[4 * i + e] = (ii > jj) ? -r[4 * i + e] * fast_exp2(((e & 2) ? g_hi : g_lo) - gs[jj]) : 0.f;
         }
         fs_m2.set(i, m[4 * i] * b_lo, m[4 * i + 1] * b_lo, m[4 * i + 2] * b_hi, m[4 * i + 3] * b_hi);
       }

@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(NTHREADS, 4) dv_local_kernel(const b200gdn_chu
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int ii = (e & 2) ? r_hi : r_lo, jj = j0 + (e & 1);
-            v[e] = (ii >= jj && ii < cm.len) ? r[b][4 * i + e] * a.scale * exp2f(((e & 2) ? g_hi : g_lo) - gs[jj]) : 0.f;
+            v[e] = (ii >= jj && ii < cm.len) ? r[b][4 * i + e] * a.scale * fast_exp2(((e & 2) ? g_hi : g_lo) - gs[jj]) : 0.f;
           }
           fs.set(i, v[0], v[1], v[2], v[3]);
         }

@@ -182,7 +182,7 @@ __global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_ch
     if (tid < BT) {
       const float gm = graw[tid];
       gam[tid] = gm;
-      bge[tid] = bet[tid] * exp2f(gm);
+      bge[tid] = bet[tid] * fast_exp2(gm);
       a.gamma[((int64_t)c * a.HV + hv) * BT + tid] = gm;   // padded rows carry the last valid value (their g is 0)
     }
     if (!ph.sync_wait()) failed = true;
@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_ch
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int ii = (e & 2) ? r_hi : r_lo, jj = j0 + (e & 1);
-          v[e] = (ii > jj) ? r[4 * i + e] * ((e & 2) ? b_hi : b_lo) * exp2f(((e & 2) ? g_hi : g_lo) - gam[jj]) : 0.f;
+          v[e] = (ii > jj) ? r[4 * i + e] * ((e & 2) ? b_hi : b_lo) * fast_exp2(((e & 2) ? g_hi : g_lo) - gam[jj]) : 0.f;
         }
         *reinterpret_cast<float2*>(&Lf[r_lo * LDF + j0]) = make_float2(v[0], v[1]);
         *reinterpret_cast<float2*>(&Lf[r_hi * LDF + j0]) = make_float2(v[2], v[3]);

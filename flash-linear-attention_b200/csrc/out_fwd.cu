@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(NTHREADS, 3) out_fwd_kernel(const b200gdn_chun
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int ii = (e & 2) ? r_hi : r_lo, jj = j0 + (e & 1);
-            v[e] = (ii >= jj) ? r[b][4 * i + e] * exp2f(((e & 2) ? g_hi : g_lo) - gs[jj]) : 0.f;
+            v[e] = (ii >= jj) ? r[b][4 * i + e] * fast_exp2(((e & 2) ? g_hi : g_lo) - gs[jj]) : 0.f;
           }
           fs.set(i, v[0], v[1], v[2], v[3]);
         }
@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(NTHREADS, 3) out_fwd_kernel(const b200gdn_chun
       } else {
         // ---- epilogue 1b: O rows scaled by 2^gamma_i in place
         {
-          const float e_lo = exp2f(g_lo), e_hi = exp2f(g_hi);
+          const float e_lo = fast_exp2(g_lo), e_hi = fast_exp2(g_hi);
           float r[DV / 32][16];
 #pragma unroll
           for (int b = 0; b < DV / 32; ++b) acc_ld32(tm, warp, b * 32, r[b]);

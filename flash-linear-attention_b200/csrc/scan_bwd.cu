@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(NTHREADS) scan_bwd_kernel(const b200gdn_chunk_
       }
       if (!tc5::mbar_wait(&full[s], (ic / NSTAGE) & 1)) { failed = true; break; }
       const float glast = gs[BT - 1];
-      const float dec = exp2f(glast);
+      const float dec = fast_exp2(glast);
 #pragma unroll
       for (int hf = 0; hf < NH; ++hf) {
 #pragma unroll
@@ -214,8 +214,8 @@ __global__ void __launch_bounds__(NTHREADS) scan_bwd_kernel(const b200gdn_chunk_
       // do_s = do scale 2^gamma (in place, rows past the chunk's end zeroed); dv_local into registers
       const int r_lo = 16 * q + g, r_hi = r_lo + 8;
       const bool ok_lo = r_lo < cm.len, ok_hi = r_hi < cm.len;
-      const float q_lo = ok_lo ? a.scale * exp2f(gs[r_lo]) : 0.f, q_hi = ok_hi ? a.scale * exp2f(gs[r_hi]) : 0.f;
-      const float e_lo = ok_lo ? exp2f(glast - gs[r_lo]) : 0.f, e_hi = ok_hi ? exp2f(glast - gs[r_hi]) : 0.f;
+      const float q_lo = ok_lo ? a.scale * fast_exp2(gs[r_lo]) : 0.f, q_hi = ok_hi ? a.scale * fast_exp2(gs[r_hi]) : 0.f;
+      const float e_lo = ok_lo ? fast_exp2(glast - gs[r_lo]) : 0.f, e_hi = ok_hi ? fast_exp2(glast - gs[r_hi]) : 0.f;
       float2 l_lo[4], l_hi[4];
       {
         FragLoad fl;

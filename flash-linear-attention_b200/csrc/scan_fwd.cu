@@ -206,7 +206,7 @@ __global__ void __launch_bounds__(NTHREADS) scan_fwd_kernel(const b200gdn_chunk_
       // ... and the decayed state back to TMEM, where the second contraction accumulates onto it
       if (!tc5::mbar_wait(&full[s], (ic / NSTAGE) & 1)) { failed = true; break; }
       const float glast = gs[BT - 1];
-      const float dec = exp2f(glast);
+      const float dec = fast_exp2(glast);
 #pragma unroll
       for (int hf = 0; hf < NH; ++hf) {
 #pragma unroll
@@ -231,8 +231,8 @@ __global__ void __launch_bounds__(NTHREADS) scan_fwd_kernel(const b200gdn_chunk_
           u_hi[i] = has_u ? fu.hi2(i) : make_float2(0.f, 0.f);
         }
       }
-      const float e_lo = r_lo < cm.len ? exp2f(glast - gs[r_lo]) : 0.f;   // rows past the chunk's end contribute nothing
-      const float e_hi = r_hi < cm.len ? exp2f(glast - gs[r_hi]) : 0.f;
+      const float e_lo = r_lo < cm.len ? fast_exp2(glast - gs[r_lo]) : 0.f;   // rows past the chunk's end contribute nothing
+      const float e_hi = r_hi < cm.len ? fast_exp2(glast - gs[r_hi]) : 0.f;
       if (!tc5::mbar_wait(v_ready, ic & 1)) { failed = true; break; }
       tc5::fence_after_sync();
       float acc[16];

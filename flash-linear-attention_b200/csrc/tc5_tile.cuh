@@ -51,6 +51,14 @@ __device__ __forceinline__ float2 swz_ld2(const unsigned char* tile, int row, in
   return unpack_bf16(*reinterpret_cast<const uint32_t*>(tile + tc5::swz_offset(row, col, rows)));
 }
 
+// 2^x with one MUFU instruction (ex2.approx.ftz: about 2 ulp, results below 2^-126 flush to zero).  The gate factors
+// of this path are 2^(gamma_i - gamma_j) <= 1 multiplied into bf16-rounded tiles, so neither matters.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // One 16-row x 32-column block of bf16 pairs in the accumulator-fragment layout (what acc_ld32 / acc_ld32q return,
 // after the epilogue math) on its way into a swizzled tile: set() packs n-tile i, store() writes the block with two
 // stmatrix.x4 (each moves eight rows of four 8 x 8 matrices; lane L supplies the address of row L % 8 of matrix L / 8),
