@@ -29,20 +29,22 @@ struct IntraSmem {
   //   K tile                      -> W staging
   //   fp32 L                      -> V tile (loaded once L is dead) -> U staging
   //   fp32 inverse                -> bf16 A (beta 2^gamma)_col | A beta_col
-  //   fp32 merge temporary (32x32)-> bf16 A
+  //   fp32 merge temporary (32x32)
+  // 56 896 bytes at K = V = 128: with the 1 KiB the system keeps per CTA, four CTAs fill the 228 KiB of an SM exactly,
+  // which is why the dynamic window is used from its (1024-byte aligned, checked) start without an alignment slack.
   static constexpr size_t fmat = ((sizeof(float) * BT * LDF + 1023) / 1024) * 1024;
   static constexpr size_t o_k = 0;
   static constexpr size_t o_l = o_k + BT * DK * 2;
   static constexpr size_t o_a = o_l + (fmat > BT * DV * 2 ? fmat : BT * DV * 2);
   static constexpr size_t o_t = o_a + fmat;
-  static constexpr size_t o_vec = o_t + BT * 128;
-  static constexpr size_t bytes = o_vec + 4 * BT * 4 + 64 + 1024;
+  static constexpr size_t o_vec = o_t + sizeof(float) * 32 * LDT;
+  static constexpr size_t bytes = o_vec + 4 * BT * 4 + 64;
   static_assert(fmat >= 2 * BT * 128, "two bf16 64x64 tiles fit in the fp32 inverse");
-  static_assert(sizeof(float) * 32 * LDT <= BT * 128, "merge temporary fits");
+  static_assert((sizeof(float) * 32 * LDT) % 16 == 0, "vectors stay 16-byte aligned");
 };
 
 struct IntraMaps {
-  CUtensorMap k, v, a, w, u;
+  CUtensorMap k, v, w, u;
 };
 
 // T = L21 * A11 ;  A21 = -A22 * T   for an N x N off-diagonal block whose top-left corner is (r0, c0).
@@ -62,13 +64,15 @@ __device__ __forceinline__ void merge_step1(const float* Lf, const float* Af, fl
     *reinterpret_cast<float4*>(&T[i * LDT + j0]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
   }
 }
+// A22 is lower triangular, so row i only needs m <= i; `m_end` is that bound rounded up to something uniform over
+// the calling warp (the rows of a warp are consecutive), which keeps the loop free of divergence.
 template <int N>
-__device__ __forceinline__ void merge_step2(const float* T, float* Af, int r0, int c0, int t, int nthr) {
+__device__ __forceinline__ void merge_step2(const float* T, float* Af, int r0, int c0, int t, int nthr, int m_end) {
   for (int o = t; o < N * N / 4; o += nthr) {
     const int i = o / (N / 4), j0 = (o % (N / 4)) * 4;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int m = 0; m < N; ++m) {
+#pragma unroll 4
+    for (int m = 0; m < m_end; ++m) {
       const float a22 = Af[(r0 + i) * LDF + r0 + m];
       const float4 tv = *reinterpret_cast<const float4*>(&T[m * LDT + j0]);
       acc[0] += a22 * tv.x; acc[1] += a22 * tv.y; acc[2] += a22 * tv.z; acc[3] += a22 * tv.w;
@@ -78,12 +82,16 @@ __device__ __forceinline__ void merge_step2(const float* T, float* Af, int r0, i
 }
 
 template <int DK, int DV>
-__global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_chunk_args a, const __grid_constant__ IntraMaps maps,
+__global__ void __launch_bounds__(NTHREADS, 4) intra_fwd_kernel(const b200gdn_chunk_args a, const __grid_constant__ IntraMaps maps,
                                                                 const int pf_dist) {
   using S = IntraSmem<DK, DV>;
   constexpr int KB = DK / 64, VB = DV / 64;
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = smem_raw;
+  if ((tc5::smem_addr(smem) & 1023u) != 0) {   // the swizzled tiles need it; never seen, but never silently wrong either
+    if (threadIdx.x == 0) atomicExch(&g_intra_timeout, 2);
+    return;
+  }
   unsigned char* Ks = smem + S::o_k;      // later the W staging tile
   unsigned char* Vs = smem + S::o_l;      // after L; later the U staging tile
   float* Lf = reinterpret_cast<float*>(smem + S::o_l);
@@ -91,7 +99,6 @@ __global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_ch
   float* Tf = reinterpret_cast<float*>(smem + S::o_t);
   unsigned char* Aw = smem + S::o_a;      // after the fp32 inverse has been read into registers
   unsigned char* Au = Aw + BT * 128;
-  unsigned char* Ab = smem + S::o_t;
   float* gam = reinterpret_cast<float*>(smem + S::o_vec);
   float* bet = gam + BT;
   float* bge = bet + BT;
@@ -231,7 +238,7 @@ __global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_ch
     // ---- 16 -> 32: blocks (16,0) and (48,32), 64 threads each
     if (tid < 128) merge_step1<16>(Lf, Af, Tf + (tid >> 6) * 16, (tid >> 6) ? 48 : 16, (tid >> 6) ? 32 : 0, tid & 63, 64);
     __syncthreads();
-    if (tid < 128) merge_step2<16>(Tf + (tid >> 6) * 16, Af, (tid >> 6) ? 48 : 16, (tid >> 6) ? 32 : 0, tid & 63, 64);
+    if (tid < 128) merge_step2<16>(Tf + (tid >> 6) * 16, Af, (tid >> 6) ? 48 : 16, (tid >> 6) ? 32 : 0, tid & 63, 64, 8 * (warp & 1) + 8);
     __syncthreads();
     // ---- 32 -> 64: block (32,0), all threads
     merge_step1<32>(Lf, Af, Tf, 32, 0, tid, NTHREADS);
@@ -242,7 +249,7 @@ __global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_ch
       tc5::mbar_expect_tx(bar_v, (uint32_t)(BT * DV * 2));
       tma::load_3d(Vs, &maps.v, cm.row, (hv * DV) / 64, bar_v);
     }
-    merge_step2<32>(Tf, Af, 32, 0, tid, NTHREADS);
+    merge_step2<32>(Tf, Af, 32, 0, tid, NTHREADS, 4 * warp + 4);
     __syncthreads();
 
     // ---- bf16 operand tiles (over the fp32 inverse and the merge temporary, hence through registers):
@@ -267,7 +274,14 @@ __global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_ch
       }
       fw.store(Aw, BT, q * 16, cs, lane);
       fu.store(Au, BT, q * 16, cs, lane);
-      fa.store(Ab, BT, q * 16, cs, lane);
+      // A itself goes straight to global memory (16 contiguous bytes per lane quad and row)
+      __nv_bfloat16* Ag = reinterpret_cast<__nv_bfloat16*>(a.A) + (row0 * a.HV + hv) * BT + cs + 2 * t;
+      const int64_t astride = (int64_t)a.HV * BT;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (r_lo < cm.len) *reinterpret_cast<uint32_t*>(Ag + r_lo * astride + i * 8) = fa.lo[i];
+        if (r_hi < cm.len) *reinterpret_cast<uint32_t*>(Ag + r_hi * astride + i * 8) = fa.hi[i];
+      }
     }
     tc5::fence_async_smem();
     tc5::fence_before_sync();
@@ -278,16 +292,6 @@ __global__ void __launch_bounds__(NTHREADS, 3) intra_fwd_kernel(const b200gdn_ch
       tc5::fence_after_sync();
       issue_mma_t<BT / 16>(tm, Operand{tc5::smem_addr(Aw), BT, 0}, Operand{tc5::smem_addr(Ks), BT, 1}, 64, DK, 0);
       ph.commit();
-    }
-    // A leaves while the tensor cores work
-    if (cm.len == BT) {
-      if (tid == 32) {
-        tma::store_2d(&maps.a, hv * BT, (int)cm.row, Ab);
-        tma::store_commit();
-      }
-    } else {
-      store_tile_swz<BT, BT, NTHREADS>(reinterpret_cast<__nv_bfloat16*>(a.A) + (row0 * a.HV + hv) * BT, (int64_t)a.HV * BT, Ab,
-                                       cm.len, tid);
     }
     if (!tc5::mbar_wait(bar_v, 0)) failed = true;
     if (cm.len < BT) {
@@ -368,11 +372,10 @@ int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
   using S = IntraSmem<DK, DV>;
   if (int e = ensure_smem(intra_fwd_kernel<DK, DV>, S::bytes)) return e;
   IntraMaps m;
-  const uint64_t pk = (uint64_t)a.H * DK, pw = (uint64_t)a.HV * DK, pv = (uint64_t)a.HV * DV, pa = (uint64_t)a.HV * BT;
+  const uint64_t pk = (uint64_t)a.H * DK, pw = (uint64_t)a.HV * DK, pv = (uint64_t)a.HV * DV;
   int rc = 0;
   rc |= tma::encode_bf16_panels(&m.k, a.k, a.rows, pk, pk, BT, DK / 64);
   rc |= tma::encode_bf16_panels(&m.v, a.v, a.rows, pv, pv, BT, DV / 64);
-  rc |= tma::encode_bf16_2d(&m.a, a.A, a.rows, pa, pa, BT);
   rc |= tma::encode_bf16_panels(&m.w, a.w, a.rows, pw, pw, BT, DK / 64);
   rc |= tma::encode_bf16_panels(&m.u, a.u, a.rows, pv, pv, BT, DV / 64);
   if (rc != 0) return set_error(B200GDN_ERR_CUDA, "intra_fwd: cuTensorMapEncodeTiled failed (%d)", rc);
