@@ -69,8 +69,8 @@ def stage_bytes(R, C, NS):
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the headline workload, from one ncu
 # capture of this script on a B200 (summary kept under profiles/); a kernel missing here was not captured.
 NCU_TRAFFIC_BYTES = {
-    'intra_fwd': 258.6e6, 'scan_fwd': 363.0e6, 'out_fwd': 388.2e6, 'dv_local': 244.3e6,
-    'scan_bwd': 507.4e6, 'bwd_dqk': 713.2e6, 'bwd_wy': 628.2e6,
+    'intra_fwd': 256.8e6, 'scan_fwd': 364.1e6, 'out_fwd': 388.7e6, 'dv_local': 244.2e6,
+    'scan_bwd': 507.2e6, 'bwd_dqk': 654.0e6, 'bwd_wy': 553.0e6,
 }
 
 F_FWD = sum(STAGE_FLOPS[s] for s in ('intra_fwd', 'scan_fwd', 'out_fwd'))
