@@ -22,6 +22,7 @@ STAGE_CASES = {
     'd128_ragged': dict(B=1, T=333, H=1, HV=2, K=128, V=128, cu=[0, 1, 16, 80, 143, 270, 333]),
     'd64_ragged_gva': dict(B=1, T=300, H=2, HV=4, K=64, V=64, cu=[0, 37, 101, 165, 300]),
     'd128_nh0': dict(B=1, T=100, H=2, HV=2, K=128, V=128, with_h0=False),
+    'd128_group4': dict(B=2, T=130, H=1, HV=4, K=128, V=128),
 }
 
 # err-ratio bounds per tensor (bf16 storage: eps = 2^-8 = 0.0039 per rounding)
