@@ -141,15 +141,20 @@ class ClockSampler:
 
 
 def make_batch(seed, device=None, pin=False):
-    """Synthetic inputs with the distributions of the headline configuration (seeded, generated on the
-    host so the CPU oracle and the GPU see identical bits)."""
-    from oracle.gdn_oracle import make_inputs
-    d = make_inputs(B, T, H, HV, K, V, seed=seed)
-    out = {}
-    for n in ('q', 'k', 'v', 'do'):
-        out[n] = d[n].to(torch.bfloat16)
-    for n in ('g', 'beta', 'h0'):
-        out[n] = d[n].float()
+    """Synthetic inputs with the distributions of the headline configuration (seeded, generated on the host):
+    q, k ~ N(0,1) L2-normalised over K; v, do ~ N(0,1); g = logsigmoid(N(0,1)); beta = sigmoid(N(0,1));
+    initial state ~ N(0, 0.1^2) fp32 (benchmarks/ops/registry.py:323-335 of the reference)."""
+    gen = torch.Generator().manual_seed(seed)
+    nrm = torch.nn.functional.normalize
+    out = {
+        'q': nrm(torch.randn(B, T, H, K, generator=gen), p=2, dim=-1).to(torch.bfloat16),
+        'k': nrm(torch.randn(B, T, H, K, generator=gen), p=2, dim=-1).to(torch.bfloat16),
+        'v': torch.randn(B, T, HV, V, generator=gen).to(torch.bfloat16),
+        'g': torch.nn.functional.logsigmoid(torch.randn(B, T, HV, generator=gen)),
+        'beta': torch.sigmoid(torch.randn(B, T, HV, generator=gen)),
+        'h0': torch.randn(B, HV, K, V, generator=gen) * 0.1,
+        'do': torch.randn(B, T, HV, V, generator=gen).to(torch.bfloat16),
+    }
     if pin:
         out = {n: x.pin_memory() for n, x in out.items()}
     if device is not None:
