@@ -227,7 +227,8 @@ int b200gdn_device_status(void) {
   struct { const char* name; int (*flag)(); } k[] = {
       {"intra_fwd", gdn::intra_fwd_timeout_flag}, {"scan_fwd", gdn::scan_fwd_timeout_flag}, {"out_fwd", gdn::out_fwd_timeout_flag},
       {"dv_local", gdn::dv_local_timeout_flag},   {"scan_bwd", gdn::scan_bwd_timeout_flag}, {"bwd_dqk", gdn::bwd_dqk_timeout_flag},
-      {"bwd_wy", gdn::bwd_wy_timeout_flag},       {"selftest", gdn::selftest_timeout_flag}};
+      {"bwd_wy", gdn::bwd_wy_timeout_flag},       {"selftest", gdn::selftest_timeout_flag},
+      {"decode_stream", gdn::decode_timeout_flag}};
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return gdn::set_error(B200GDN_ERR_CUDA, "device_status: %s", cudaGetErrorString(e));
   int rc = B200GDN_OK;

@@ -389,6 +389,7 @@ int launch_bwd_wy(const b200gdn_chunk_args& a, cudaStream_t st);
 int launch_recurrent(const b200gdn_recurrent_args& a, cudaStream_t st);
 int launch_affine(const b200gdn_affine_args& a, cudaStream_t st);
 int launch_prep(const b200gdn_prep_args& a, cudaStream_t st, bool bwd);
+int decode_timeout_flag();
 int intra_fwd_timeout_flag();
 int scan_fwd_timeout_flag();
 int out_fwd_timeout_flag();

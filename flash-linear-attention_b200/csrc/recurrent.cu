@@ -8,6 +8,8 @@
 // registers.  [K,V] layout: lanes run along V, the reductions over K go through registers, two shuffles
 // and a 4-warp shared-memory combine.  [V,K] layout: lanes run along K and the reductions are shuffles only.
 #include "gdn_common.cuh"
+#include "tc5.cuh"
+#include "tma.cuh"
 
 #include <cuda_fp16.h>
 
@@ -203,8 +205,326 @@ __global__ void __launch_bounds__(NTHREADS, (DK <= 128 ? 8 : 4)) recurrent_kerne
   }
 }
 
+// [K,V] layout with V = 128: one CTA of eight warps owns the whole state of one (sequence, head) - K rows of 512
+// contiguous bytes, i.e. one contiguous block of K * 512 bytes - so that every DRAM page of the state is opened once
+// for the read and once for the write (the 32-channel slices of the kernel above touch each page four times, which
+// costs about a quarter of the bandwidth at large batch).  Warp w keeps rows [w K/8, (w+1) K/8), lane l the columns
+// 4 l .. 4 l + 3: a warp moves one full row per 128-bit access.
+template <int DK>
+__global__ void __launch_bounds__(256, 2) recurrent_rows_kernel(const b200gdn_recurrent_args a) {
+  constexpr int NT = 256, DV = 128, RW = DK / 8;   // rows per warp
+  __shared__ __align__(16) float qs[DK];
+  __shared__ __align__(16) float ks[DK];
+  __shared__ __align__(16) float vs[DV];
+  __shared__ __align__(16) float red[8][DV];
+  __shared__ float sc[2];  // decay, beta
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int hv = blockIdx.x, n = blockIdx.y;
+  const int G = a.HV / a.H, hq = hv / G;
+  int64_t bos, len;
+  if (a.cu_seqlens != nullptr) {
+    bos = a.cu_seqlens[n];
+    len = a.cu_seqlens[n + 1] - bos;
+  } else {
+    bos = (int64_t)n * a.T;
+    len = a.T;
+  }
+  float4 st[RW];
+  const float* h0 = a.h0 ? a.h0 + ((int64_t)n * a.HV + hv) * DK * DV : nullptr;
+  float* ht = a.ht ? a.ht + ((int64_t)n * a.HV + hv) * DK * DV : nullptr;
+  const int col = 4 * lane, r0 = warp * RW;
+#pragma unroll
+  for (int i = 0; i < RW; ++i)
+    st[i] = h0 ? *reinterpret_cast<const float4*>(h0 + (int64_t)(r0 + i) * DV + col) : make_float4(0.f, 0.f, 0.f, 0.f);
+
+  for (int64_t tok = 0; tok < len; ++tok) {
+    const int64_t row = bos + tok;
+    __syncthreads();  // previous token's shared inputs are no longer read
+    if (tid < DK) {
+      qs[tid] = ld_elem(a.q, (row * a.H + hq) * DK + tid, a.qkv_dtype);
+      ks[tid] = ld_elem(a.k, (row * a.H + hq) * DK + tid, a.qkv_dtype);
+    } else if (tid < DK + DV) {
+      vs[tid - DK] = ld_elem(a.v, (row * a.HV + hv) * DV + tid - DK, a.qkv_dtype);
+    }
+    if (tid == NT - 1) {
+      float gg = a.g ? a.g[row * a.HV + hv] : 0.f;
+      if (a.flags & B200GDN_REC_GATE) {
+        if (a.dt_bias) gg += a.dt_bias[hv];
+        gg = -expf(a.A_log[hv]) * softplus_f(gg);
+      }
+      float bb = a.beta[row * a.HV + hv];
+      if (a.flags & B200GDN_REC_BETA_SIGMOID) {
+        bb = 1.f / (1.f + expf(-bb));
+        if (a.flags & B200GDN_REC_NEG_EIGVAL) bb *= 2.f;
+      }
+      sc[0] = expf(gg);
+      sc[1] = bb;
+    }
+    __syncthreads();
+    float qn = a.scale, kn = 1.f;
+    if (a.flags & B200GDN_REC_L2NORM) {
+      float sq = 0.f, sk = 0.f;
+      for (int i = lane; i < DK; i += 32) {
+        sq += qs[i] * qs[i];
+        sk += ks[i] * ks[i];
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        sk += __shfl_xor_sync(0xffffffffu, sk, o);
+      }
+      qn = a.scale * rsqrtf(sq + 1e-6f);
+      kn = rsqrtf(sk + 1e-6f);
+    }
+    const float decay = sc[0], beta = sc[1];
+
+    // S <- S decay;  partial S^T k over this warp's rows
+    float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < RW; ++i) {
+      st[i].x *= decay; st[i].y *= decay; st[i].z *= decay; st[i].w *= decay;
+      const float kk = ks[r0 + i] * kn;
+      d.x += st[i].x * kk; d.y += st[i].y * kk; d.z += st[i].z * kk; d.w += st[i].w * kk;
+    }
+    *reinterpret_cast<float4*>(&red[warp][col]) = d;
+    __syncthreads();
+    float4 r;
+    {
+      float4 s = *reinterpret_cast<const float4*>(&red[0][col]);
+#pragma unroll
+      for (int w = 1; w < 8; ++w) {
+        const float4 x = *reinterpret_cast<const float4*>(&red[w][col]);
+        s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+      }
+      const float4 vv = *reinterpret_cast<const float4*>(&vs[col]);
+      r.x = beta * (vv.x - s.x); r.y = beta * (vv.y - s.y); r.z = beta * (vv.z - s.z); r.w = beta * (vv.w - s.w);
+    }
+    __syncthreads();   // every warp has read the partial sums before they are overwritten below
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < RW; ++i) {
+      const float kk = ks[r0 + i] * kn, qq = qs[r0 + i] * qn;
+      st[i].x += kk * r.x; st[i].y += kk * r.y; st[i].z += kk * r.z; st[i].w += kk * r.w;
+      o.x += st[i].x * qq; o.y += st[i].y * qq; o.z += st[i].z * qq; o.w += st[i].w * qq;
+    }
+    *reinterpret_cast<float4*>(&red[warp][col]) = o;
+    __syncthreads();
+    if (tid < DV) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) s += red[w][tid];
+      st_elem(a.o, (row * a.HV + hv) * DV + tid, a.qkv_dtype, s);
+    }
+  }
+
+  if (ht != nullptr) {
+#pragma unroll
+    for (int i = 0; i < RW; ++i) *reinterpret_cast<float4*>(ht + (int64_t)(r0 + i) * DV + col) = st[i];
+  }
+}
+
+// Single-token decode at large batch as a stream: the kernels above load a state, compute and store it, so the
+// memory pipe of an SM idles while its CTAs compute.  Here one persistent CTA per SM walks its (sequence, head) items
+// through a three-stage ring in shared memory: a producer warp brings each 64 KiB state (one contiguous bulk copy), the
+// token's q, k, v rows and the activated gate scalars two items ahead and writes finished states back (one bulk copy);
+// eight consumer warps only compute, shared memory to shared memory.  Every wait is bounded.
+__device__ int g_decode_timeout = 0;
+
+template <int DK>
+struct DecodeSmem {
+  static constexpr int NS = 3;
+  static constexpr size_t state_bytes = (size_t)DK * 128 * 4;
+  static constexpr size_t o_q = state_bytes, o_k = o_q + 512, o_v = o_k + 512, o_sc = o_v + 512;
+  static constexpr size_t stage = o_sc + 128;
+  static constexpr size_t o_red = NS * stage;
+  static constexpr size_t o_bar = o_red + 8 * 128 * 4;
+  static constexpr size_t bytes = o_bar + 128;
+};
+
+template <int DK>
+__global__ void __launch_bounds__(288, 1) decode_stream_kernel(const b200gdn_recurrent_args a, const int n_items) {
+  using S = DecodeSmem<DK>;
+  constexpr int NS = S::NS, DV = 128, RW = DK / 8;
+  extern __shared__ __align__(128) unsigned char dsm[];
+  float (*red)[DV] = reinterpret_cast<float (*)[DV]>(dsm + S::o_red);
+  uint64_t* full = reinterpret_cast<uint64_t*>(dsm + S::o_bar);
+  uint64_t* done = full + NS;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int esz = a.qkv_dtype == 2 ? 4 : 2;
+  const int n_local = (n_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int G = a.HV / a.H;
+
+  if (tid == 0) {
+    for (int s = 0; s < NS; ++s) {
+      tc5::mbar_init(&full[s], 1);
+      tc5::mbar_init(&done[s], 256);
+    }
+    tc5::fence_mbar_init();
+  }
+  __syncthreads();
+
+  if (warp == 8) {
+    // ---- producer: write-back of the item that used the stage last, then the load of the item NS further on
+    if (lane == 0) {
+      bool failed = false;
+      for (int jj = 0; jj < n_local + NS && !failed; ++jj) {
+        const int s = jj % NS;
+        unsigned char* stg = dsm + (size_t)s * S::stage;
+        if (jj >= NS) {
+          const int item = (int)blockIdx.x + (jj - NS) * (int)gridDim.x;
+          if (!tc5::mbar_wait(&done[s], ((jj - NS) / NS) & 1)) { failed = true; break; }
+          float* ht = a.ht + (int64_t)item * DK * DV;
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(ht), "r"(tc5::smem_addr(stg)),
+                       "r"((uint32_t)S::state_bytes)
+                       : "memory");
+          tma::store_commit();
+          tma::store_wait_read<0>();   // the stage may be refilled once the copy has read it
+        }
+        if (jj < n_local) {
+          const int item = (int)blockIdx.x + jj * (int)gridDim.x;
+          const int n = item / a.HV, hv = item % a.HV, hq = hv / G;
+          const int64_t row = n;   // one token per sequence
+          float gg = a.g ? a.g[row * a.HV + hv] : 0.f;
+          if (a.flags & B200GDN_REC_GATE) {
+            if (a.dt_bias) gg += a.dt_bias[hv];
+            gg = -expf(a.A_log[hv]) * softplus_f(gg);
+          }
+          float bb = a.beta[row * a.HV + hv];
+          if (a.flags & B200GDN_REC_BETA_SIGMOID) {
+            bb = 1.f / (1.f + expf(-bb));
+            if (a.flags & B200GDN_REC_NEG_EIGVAL) bb *= 2.f;
+          }
+          float* sc = reinterpret_cast<float*>(stg + S::o_sc);
+          sc[0] = expf(gg);
+          sc[1] = bb;
+          const uint32_t qk_bytes = (uint32_t)(DK * esz), v_bytes = (uint32_t)(DV * esz);
+          tc5::mbar_expect_tx(&full[s], (uint32_t)S::state_bytes + 2 * qk_bytes + v_bytes);
+          tma::load_1d(stg, a.h0 + (int64_t)item * DK * DV, (uint32_t)S::state_bytes, &full[s]);
+          tma::load_1d(stg + S::o_q, static_cast<const char*>(a.q) + (row * a.H + hq) * DK * esz, qk_bytes, &full[s]);
+          tma::load_1d(stg + S::o_k, static_cast<const char*>(a.k) + (row * a.H + hq) * DK * esz, qk_bytes, &full[s]);
+          tma::load_1d(stg + S::o_v, static_cast<const char*>(a.v) + (row * a.HV + hv) * DV * esz, v_bytes, &full[s]);
+        }
+      }
+      tma::store_wait_all<0>();
+      if (failed) atomicExch(&g_decode_timeout, 1);
+    }
+    return;
+  }
+
+  // ---- consumers (8 warps): warp w keeps rows [w RW, (w+1) RW), lane l the columns 4 l .. 4 l + 3
+  const int col = 4 * lane, r0 = warp * RW;
+  auto sync_consumers = [] { asm volatile("bar.sync 1, 256;\n" ::: "memory"); };
+  for (int j = 0; j < n_local; ++j) {
+    const int s = j % NS;
+    unsigned char* stg = dsm + (size_t)s * S::stage;
+    float* St = reinterpret_cast<float*>(stg);
+    const int item = (int)blockIdx.x + j * (int)gridDim.x;
+    const int hv = item % a.HV;
+    {
+      // the consumers agree on the outcome of the bounded wait (a barrier-wide OR), so that they leave together;
+      // the producer then gives up on its own bounded wait
+      const uint32_t bad = tc5::mbar_wait(&full[s], (j / NS) & 1) ? 0u : 1u;
+      uint32_t any_bad;
+      asm volatile(
+          "{\n.reg .pred p, q;\nsetp.ne.b32 q, %1, 0;\nbar.red.or.pred p, 1, 256, q;\nselp.u32 %0, 1, 0, p;\n}\n"
+          : "=r"(any_bad)
+          : "r"(bad)
+          : "memory");
+      if (any_bad) {
+        if (tid == 0) atomicExch(&g_decode_timeout, 1);
+        return;
+      }
+    }
+    const float* sc = reinterpret_cast<const float*>(stg + S::o_sc);
+    const float decay = sc[0], beta = sc[1];
+    float qn = a.scale, kn = 1.f;
+    if (a.flags & B200GDN_REC_L2NORM) {
+      float sq = 0.f, sk = 0.f;
+      for (int i = lane; i < DK; i += 32) {
+        const float x = ld_elem(stg + S::o_q, i, a.qkv_dtype), y = ld_elem(stg + S::o_k, i, a.qkv_dtype);
+        sq += x * x;
+        sk += y * y;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        sk += __shfl_xor_sync(0xffffffffu, sk, o);
+      }
+      qn = a.scale * rsqrtf(sq + 1e-6f);
+      kn = rsqrtf(sk + 1e-6f);
+    }
+    float4 st[RW];
+    float kr[RW];
+    float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < RW; ++i) {
+      st[i] = *reinterpret_cast<const float4*>(St + (r0 + i) * DV + col);
+      kr[i] = ld_elem(stg + S::o_k, r0 + i, a.qkv_dtype) * kn;
+      st[i].x *= decay; st[i].y *= decay; st[i].z *= decay; st[i].w *= decay;
+      d.x += st[i].x * kr[i]; d.y += st[i].y * kr[i]; d.z += st[i].z * kr[i]; d.w += st[i].w * kr[i];
+    }
+    *reinterpret_cast<float4*>(&red[warp][col]) = d;
+    sync_consumers();
+    float4 r;
+    {
+      float4 sum = *reinterpret_cast<const float4*>(&red[0][col]);
+#pragma unroll
+      for (int w = 1; w < 8; ++w) {
+        const float4 x = *reinterpret_cast<const float4*>(&red[w][col]);
+        sum.x += x.x; sum.y += x.y; sum.z += x.z; sum.w += x.w;
+      }
+      const float v0 = ld_elem(stg + S::o_v, col, a.qkv_dtype), v1 = ld_elem(stg + S::o_v, col + 1, a.qkv_dtype);
+      const float v2 = ld_elem(stg + S::o_v, col + 2, a.qkv_dtype), v3 = ld_elem(stg + S::o_v, col + 3, a.qkv_dtype);
+      r.x = beta * (v0 - sum.x); r.y = beta * (v1 - sum.y); r.z = beta * (v2 - sum.z); r.w = beta * (v3 - sum.w);
+    }
+    sync_consumers();   // the partial sums have been read by everybody before they are overwritten
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < RW; ++i) {
+      const float qq = ld_elem(stg + S::o_q, r0 + i, a.qkv_dtype) * qn;
+      st[i].x += kr[i] * r.x; st[i].y += kr[i] * r.y; st[i].z += kr[i] * r.z; st[i].w += kr[i] * r.w;
+      o.x += st[i].x * qq; o.y += st[i].y * qq; o.z += st[i].z * qq; o.w += st[i].w * qq;
+      *reinterpret_cast<float4*>(St + (r0 + i) * DV + col) = st[i];
+    }
+    *reinterpret_cast<float4*>(&red[warp][col]) = o;
+    tc5::fence_async_smem();       // the new state is read by the producer's bulk copy
+    sync_consumers();
+    if (tid < DV) {
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) sum += red[w][tid];
+      st_elem(a.o, ((int64_t)(item / a.HV) * a.HV + hv) * DV + tid, a.qkv_dtype, sum);
+    }
+    tc5::mbar_arrive(&done[s]);
+    sync_consumers();   // red is free again for the next item
+  }
+}
+
 template <int DK>
 int launch(const b200gdn_recurrent_args& a, cudaStream_t st) {
+  if constexpr (DK == 64 || DK == 128) {
+    // one token per sequence at large batch: the streaming kernel (state and token rows by bulk copies, ring of three)
+    if (!(a.flags & B200GDN_REC_STATE_V_FIRST) && a.V == 128 && a.T == 1 && a.cu_seqlens == nullptr && a.h0 != nullptr &&
+        a.ht != nullptr && (int64_t)a.n_seq * a.HV >= 256 && (reinterpret_cast<uintptr_t>(a.q) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(a.k) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.v) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(a.h0) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.ht) & 15) == 0) {
+      using S = DecodeSmem<DK>;
+      if (int e = ensure_smem(decode_stream_kernel<DK>, S::bytes)) return e;
+      int dev = 0, sms = 148;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      const int n_items = a.n_seq * a.HV;
+      decode_stream_kernel<DK><<<n_items < sms ? n_items : sms, 288, S::bytes, st>>>(a, n_items);
+      return check_launch("decode_stream");
+    }
+    // whole-state CTAs (contiguous state traffic) once there are enough (sequence, head) pairs to fill the GPU;
+    // smaller problems keep the four-times finer slicing of the kernel above
+    if (!(a.flags & B200GDN_REC_STATE_V_FIRST) && a.V == 128 && (int64_t)a.n_seq * a.HV >= 256) {
+      recurrent_rows_kernel<DK><<<dim3(a.HV, a.n_seq), 256, 0, st>>>(a);
+      return check_launch("recurrent_rows");
+    }
+  }
   dim3 grid(a.V / VS, a.HV, a.n_seq);
   if (a.flags & B200GDN_REC_STATE_V_FIRST)
     recurrent_kernel<DK, true><<<grid, NTHREADS, 0, st>>>(a);
@@ -226,6 +546,14 @@ int launch_recurrent(const b200gdn_recurrent_args& a, cudaStream_t st) {
     case 256: return launch<256>(a, st);
   }
   return set_error(B200GDN_ERR_UNSUPPORTED, "recurrent: K=%d not built (32, 64, 128, 256 are)", a.K);
+}
+
+// Reads and clears the flag a bounded device wait raises when it expires (synchronises with the device).
+int decode_timeout_flag() {
+  int v = 0, zero = 0;
+  cudaMemcpyFromSymbol(&v, g_decode_timeout, sizeof(int));
+  if (v) cudaMemcpyToSymbol(g_decode_timeout, &zero, sizeof(int));
+  return v;
 }
 
 }  // namespace gdn

@@ -163,3 +163,29 @@ def test_decode_step_in_cuda_graph():
         graph.replay()
         assert torch.equal(o_g, outs_e[i]), f'step {i}'
     assert torch.equal(s_g, s_e)
+
+
+@pytest.mark.parametrize('K', [128, 64])
+@pytest.mark.parametrize('T', [1, 3])
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16, torch.float16])
+def test_large_batch_kernels_with_options(K, T, dtype):
+    """Enough (sequence, head) pairs for the large-batch kernels: T = 1 takes the streaming kernel (bulk-copy ring,
+    persistent CTAs), T = 3 the whole-state kernel; both with every in-kernel option on, grouped value heads, and the
+    state out of place, against the oracle recurrence."""
+    from b200gdn import fused_recurrent_gated_delta_rule
+    B, H, HV, V = 40, 4, 8, 128     # 320 (sequence, head) pairs
+    q, k, v, graw, braw, A_log, dt_bias, gen = _inputs(B, T, H, HV, K, V, 3, dtype)
+    h0 = torch.randn(B, HV, K, V, generator=gen) * 0.5
+    ref_o, ref_ht = O.recurrent_step_options(
+        q.float(), k.float(), v.float(), graw, braw, None, h0, True, True, True, A_log, dt_bias, True, True, False)
+    dev = 'cuda'
+    o, ht = fused_recurrent_gated_delta_rule(
+        q.to(dev), k.to(dev), v.to(dev), graw.to(dev), beta=braw.to(dev), initial_state=h0.to(dev),
+        output_final_state=True, use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True, A_log=A_log.to(dev),
+        dt_bias=dt_bias.to(dev), use_beta_sigmoid_in_kernel=True, allow_neg_eigval=True)
+    assert o.dtype == dtype and ht.dtype == torch.float32
+    tol = 1e-5 if dtype == torch.float32 else 0.004
+    O.assert_close('o', ref_o, o.float().cpu(), tol)
+    O.assert_close('ht', ref_ht, ht.cpu(), 1e-5)
+    import b200gdn
+    b200gdn.device_status()
