@@ -76,7 +76,6 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
   d |= 2ull << 61;   // SWIZZLE_128B
   return d;
 }
-__device__ __forceinline__ uint64_t desc_advance(uint64_t d, uint32_t bytes) { return d + (uint64_t)(bytes >> 4); }
 
 // Instruction descriptor for kind::f16 with bf16 operands and fp32 accumulation.
 //   a_mn / b_mn : operand is MN-major (1) or K-major (0);  neg_a: D -= A B instead of +=
@@ -110,15 +109,6 @@ __device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, float (&r)[16
   uint32_t* u = reinterpret_cast<uint32_t*>(r);
   asm volatile(
       "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-      : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
-        "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
-      : "r"(taddr));
-}
-// 32 lanes x 32 bits per repetition: thread t receives row (lane) t, 16 consecutive columns.
-__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, float (&r)[16]) {
-  uint32_t* u = reinterpret_cast<uint32_t*>(r);
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
       : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
         "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
       : "r"(taddr));

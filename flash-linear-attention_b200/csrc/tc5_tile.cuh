@@ -6,27 +6,9 @@
 
 namespace gdn {
 
-// ---- global -> shared, canonical swizzled layout -----------------------------------------------------
-// [ROWS][COLS] bf16 tile, global row stride `gstride` elements; rows >= valid are zero-filled.
-// Destination: 64-column panels of ROWS*128 bytes, 16-byte chunks XOR-swizzled with (row & 7).
-template <int ROWS, int COLS, int NTHREADS>
-__device__ __forceinline__ void load_tile_swz(unsigned char* dst, const __nv_bfloat16* src, int64_t gstride, int valid,
-                                              int tid) {
-  constexpr int CPR = COLS / 8;
-  constexpr int TOTAL = ROWS * CPR;
-  static_assert(TOTAL % NTHREADS == 0, "tile/threads mismatch");
-#pragma unroll
-  for (int it = 0; it < TOTAL / NTHREADS; ++it) {
-    int idx = it * NTHREADS + tid;
-    int r = idx / CPR, c = idx % CPR;
-    bool ok = r < valid;
-    const __nv_bfloat16* g = src + (ok ? (int64_t)r * gstride : 0) + c * 8;
-    unsigned char* d = dst + (c >> 3) * (ROWS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4);
-    cp_async16(d, g, ok);
-  }
-}
-
-// Swizzled tile -> global (16 bytes per access), rows < valid.
+// ---- swizzled shared tile -> global ------------------------------------------------------------------------
+// [ROWS][COLS] bf16 tile stored as 64-column panels of ROWS*128 bytes, 16-byte chunks XOR-swizzled with (row & 7);
+// 16 bytes per access, rows < valid only (the ragged-chunk path; full chunks leave through TMA stores).
 template <int ROWS, int COLS, int NTHREADS>
 __device__ __forceinline__ void store_tile_swz(__nv_bfloat16* dst, int64_t gstride, const unsigned char* src, int valid,
                                                int tid) {
@@ -42,13 +24,6 @@ __device__ __forceinline__ void store_tile_swz(__nv_bfloat16* dst, int64_t gstri
       *reinterpret_cast<uint4*>(dst + (int64_t)r * gstride + c * 8) = val;
     }
   }
-}
-
-__device__ __forceinline__ uint32_t* swz_ptr32(unsigned char* tile, int row, int col, int rows) {
-  return reinterpret_cast<uint32_t*>(tile + tc5::swz_offset(row, col, rows));
-}
-__device__ __forceinline__ float2 swz_ld2(const unsigned char* tile, int row, int col, int rows) {
-  return unpack_bf16(*reinterpret_cast<const uint32_t*>(tile + tc5::swz_offset(row, col, rows)));
 }
 
 // 2^x with one MUFU instruction (ex2.approx.ftz: about 2 ulp, results below 2^-126 flush to zero).  The gate factors
@@ -147,15 +122,6 @@ __device__ __forceinline__ void issue_mma_t(uint32_t d_tmem, const Operand& a, c
     tc5::mma_ss(d_tmem, da + (operand_step_bytes(a, ks) >> 4), db + (operand_step_bytes(b, ks) >> 4), idesc,
                 (acc || ks > 0) ? 1u : 0u);
 }
-__device__ __forceinline__ void issue_mma(uint32_t d_tmem, const Operand& a, const Operand& b, int M, int N, int ksteps,
-                                          int acc, int neg_a = 0) {
-  const uint32_t idesc = tc5::idesc_bf16(M, N, a.mn_major, b.mn_major, neg_a);
-  const uint64_t da = operand_desc0(a), db = operand_desc0(b);
-  for (int ks = 0; ks < ksteps; ++ks)
-    tc5::mma_ss(d_tmem, da + (operand_step_bytes(a, ks) >> 4), db + (operand_step_bytes(b, ks) >> 4), idesc,
-                (acc || ks > 0) ? 1u : 0u);
-}
-
 // ---- accumulator read-back -------------------------------------------------------------------------------
 // 16 rows x 32 columns of an M = 64 accumulator for this warp (rows 16*warp .. +15): r[4*i + e] is
 // n-tile i (columns c0 + 8i ..), e = {row g col 2t, row g col 2t+1, row g+8 col 2t, row g+8 col 2t+1}.
