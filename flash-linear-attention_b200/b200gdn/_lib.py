@@ -47,7 +47,7 @@ class RecurrentArgs(C.Structure):
 
 
 PREP_L2NORM, PREP_GATE, PREP_BETA_SIGMOID, PREP_NEG_EIGVAL = 1, 2, 4, 8
-PREP_PART_ROWS = 4096
+PREP_PART_ROWS = 128
 
 
 class PrepArgs(C.Structure):

@@ -184,8 +184,8 @@ static int check_prep_args(const b200gdn_prep_args* a, const char* who, bool bwd
   if (a->qk_dtype < 0 || a->qk_dtype > 2 || a->gb_dtype < 0 || a->gb_dtype > 2)
     return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: dtype codes are 0 (bf16), 1 (fp16), 2 (fp32)", who);
   if (a->flags & B200GDN_PREP_L2NORM) {
-    if (a->K <= 0 || a->K % 64 != 0 || a->K > 512)
-      return set_error(B200GDN_ERR_UNSUPPORTED, "%s: K=%d (a multiple of 64 up to 512 is built)", who, a->K);
+    if (a->K != 64 && a->K != 128 && a->K != 256 && a->K != 512)
+      return set_error(B200GDN_ERR_UNSUPPORTED, "%s: K=%d (64, 128, 256 and 512 are built)", who, a->K);
     REQUIRE(a->q, who); REQUIRE(a->k, who); REQUIRE(a->rstd_q, who); REQUIRE(a->rstd_k, who);
     if (!bwd) { REQUIRE(a->qn, who); REQUIRE(a->kn, who); }
     else { REQUIRE(a->dqn, who); REQUIRE(a->dkn, who); REQUIRE(a->dq, who); REQUIRE(a->dk, who); }

@@ -53,18 +53,24 @@ __device__ __forceinline__ void store8(void* base, int64_t idx, const float (&x)
     *reinterpret_cast<float4*>(static_cast<float*>(base) + idx + 4) = make_float4(x[4], x[5], x[6], x[7]);
   }
 }
-__device__ __forceinline__ float warp_sum(float v) {
+
+// LPV = K / 8 lanes own one (token, head) vector of K elements, eight consecutive elements (16 bytes of bf16) each, so
+// that every lane of a warp moves data for K = 64 ... 256; K = 512 takes two passes per lane (NV = 2).
+// blockIdx.y = 0 for q, 1 for k.
+template <int LPV>
+__device__ __forceinline__ float group_sum(float v) {
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  for (int o = LPV / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
 
-// One warp per (token, head) vector; blockIdx.y = 0 for q, 1 for k.  NV = K / 256 rounded up: 8-element groups per lane.
-template <typename T, int NV>
+template <typename T, int LPV, int NV>
 __global__ void __launch_bounds__(256) l2norm_fwd_kernel(const b200gdn_prep_args a) {
-  const int lane = threadIdx.x & 31;
-  const int64_t vec = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (vec >= (int64_t)a.rows * a.H) return;
+  constexpr int VPW = 32 / LPV;   // vectors per warp
+  const int lane = threadIdx.x & 31, sub = lane % LPV;
+  const int64_t nvec = (int64_t)a.rows * a.H;
+  const int64_t vec = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * VPW + lane / LPV;
+  const bool live = vec < nvec;
   const void* src = blockIdx.y ? a.k : a.q;
   void* dst = blockIdx.y ? a.kn : a.qn;
   float* rstd = blockIdx.y ? a.rstd_k : a.rstd_q;
@@ -72,45 +78,44 @@ __global__ void __launch_bounds__(256) l2norm_fwd_kernel(const b200gdn_prep_args
   float ss = 0.f;
 #pragma unroll
   for (int v = 0; v < NV; ++v) {
-    const int col = (v * 32 + lane) * 8;
-    if (col < a.K) {
-      load8<T>(src, vec * a.K + col, x[v]);
+    if (live) {
+      load8<T>(src, vec * a.K + (v * LPV + sub) * 8, x[v]);
 #pragma unroll
       for (int i = 0; i < 8; ++i) ss += x[v][i] * x[v][i];
     }
   }
-  ss = warp_sum(ss);
+  ss = group_sum<LPV>(ss);
   const float r = 1.f / sqrtf(ss + kL2Eps);
-  if (lane == 0) rstd[vec] = r;
+  if (live && sub == 0) rstd[vec] = r;
 #pragma unroll
   for (int v = 0; v < NV; ++v) {
-    const int col = (v * 32 + lane) * 8;
-    if (col < a.K) {
+    if (live) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) x[v][i] *= r;
-      store8<__nv_bfloat16>(dst, vec * a.K + col, x[v]);
+      store8<__nv_bfloat16>(dst, vec * a.K + (v * LPV + sub) * 8, x[v]);
     }
   }
 }
 
 // dx = (dy - (sum dy y) y) rstd with y = x rstd recomputed in fp32
-template <typename T, int NV>
+template <typename T, int LPV, int NV>
 __global__ void __launch_bounds__(256) l2norm_bwd_kernel(const b200gdn_prep_args a) {
-  const int lane = threadIdx.x & 31;
-  const int64_t vec = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (vec >= (int64_t)a.rows * a.H) return;
+  constexpr int VPW = 32 / LPV;
+  const int lane = threadIdx.x & 31, sub = lane % LPV;
+  const int64_t nvec = (int64_t)a.rows * a.H;
+  const int64_t vec = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * VPW + lane / LPV;
+  const bool live = vec < nvec;
   const void* src = blockIdx.y ? a.k : a.q;
   const void* dy = blockIdx.y ? a.dkn : a.dqn;
   void* dst = blockIdx.y ? a.dk : a.dq;
-  const float r = (blockIdx.y ? a.rstd_k : a.rstd_q)[vec];
+  const float r = live ? (blockIdx.y ? a.rstd_k : a.rstd_q)[vec] : 0.f;
   float y[NV][8], d[NV][8];
   float s = 0.f;
 #pragma unroll
   for (int v = 0; v < NV; ++v) {
-    const int col = (v * 32 + lane) * 8;
-    if (col < a.K) {
-      load8<T>(src, vec * a.K + col, y[v]);
-      load8<__nv_bfloat16>(dy, vec * a.K + col, d[v]);
+    if (live) {
+      load8<T>(src, vec * a.K + (v * LPV + sub) * 8, y[v]);
+      load8<__nv_bfloat16>(dy, vec * a.K + (v * LPV + sub) * 8, d[v]);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         y[v][i] *= r;
@@ -118,14 +123,13 @@ __global__ void __launch_bounds__(256) l2norm_bwd_kernel(const b200gdn_prep_args
       }
     }
   }
-  s = warp_sum(s);
+  s = group_sum<LPV>(s);
 #pragma unroll
   for (int v = 0; v < NV; ++v) {
-    const int col = (v * 32 + lane) * 8;
-    if (col < a.K) {
+    if (live) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) d[v][i] = (d[v][i] - s * y[v][i]) * r;
-      store8<T>(dst, vec * a.K + col, d[v]);
+      store8<T>(dst, vec * a.K + (v * LPV + sub) * 8, d[v]);
     }
   }
 }
@@ -208,19 +212,27 @@ __global__ void gate_param_grad_kernel(const b200gdn_prep_args a, int n_part) {
   if (a.ddt_bias) a.ddt_bias[hv] = tB;
 }
 
-template <typename T>
-int launch_rows(const b200gdn_prep_args& a, cudaStream_t st, bool bwd) {
-  const int64_t vecs = (int64_t)a.rows * a.H;
-  dim3 grid((unsigned)((vecs + 7) / 8), 2);
-  const int nv = (a.K + 255) / 256;
+template <typename T, int LPV, int NV>
+int launch_rows_k(const b200gdn_prep_args& a, cudaStream_t st, bool bwd) {
+  const int64_t vecs = (int64_t)a.rows * a.H, per_cta = 8 * (32 / LPV);
+  dim3 grid((unsigned)((vecs + per_cta - 1) / per_cta), 2);
   if (!bwd) {
-    if (nv == 1) l2norm_fwd_kernel<T, 1><<<grid, 256, 0, st>>>(a);
-    else l2norm_fwd_kernel<T, 2><<<grid, 256, 0, st>>>(a);
+    l2norm_fwd_kernel<T, LPV, NV><<<grid, 256, 0, st>>>(a);
     return check_launch("l2norm_fwd");
   }
-  if (nv == 1) l2norm_bwd_kernel<T, 1><<<grid, 256, 0, st>>>(a);
-  else l2norm_bwd_kernel<T, 2><<<grid, 256, 0, st>>>(a);
+  l2norm_bwd_kernel<T, LPV, NV><<<grid, 256, 0, st>>>(a);
   return check_launch("l2norm_bwd");
+}
+
+template <typename T>
+int launch_rows(const b200gdn_prep_args& a, cudaStream_t st, bool bwd) {
+  switch (a.K) {
+    case 64: return launch_rows_k<T, 8, 1>(a, st, bwd);
+    case 128: return launch_rows_k<T, 16, 1>(a, st, bwd);
+    case 256: return launch_rows_k<T, 32, 1>(a, st, bwd);
+    case 512: return launch_rows_k<T, 32, 2>(a, st, bwd);
+  }
+  return set_error(B200GDN_ERR_UNSUPPORTED, "l2norm: K=%d not built (64, 128, 256, 512 are)", a.K);
 }
 
 template <typename T>

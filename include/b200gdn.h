@@ -177,10 +177,10 @@ int b200gdn_affine_apply(const b200gdn_affine_args* args, void* stream);
 #define B200GDN_PREP_GATE 2u
 #define B200GDN_PREP_BETA_SIGMOID 4u
 #define B200GDN_PREP_NEG_EIGVAL 8u
-#define B200GDN_PREP_PART_ROWS 4096      /* rows of g reduced by one CTA of the backward pass */
+#define B200GDN_PREP_PART_ROWS 128       /* rows of g reduced by one CTA of the backward pass */
 typedef struct b200gdn_prep_args {
   int32_t struct_bytes;
-  int32_t rows, H, HV, K;        /* K a multiple of 64, at most 512 */
+  int32_t rows, H, HV, K;        /* K in {64, 128, 256, 512} */
   uint32_t flags;                /* B200GDN_PREP_* */
   int32_t qk_dtype;              /* 0 = bf16, 1 = fp16, 2 = fp32: element type of q, k, dq, dk */
   int32_t gb_dtype;              /* same code: element type of g, beta, dg_raw, dbeta_raw */

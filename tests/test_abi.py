@@ -60,7 +60,7 @@ def test_argument_errors_without_gpu():
     p = _lib.PrepArgs()
     p.struct_bytes = ctypes.sizeof(p)
     p.rows, p.H, p.HV, p.K, p.flags = 64, 2, 2, 100, _lib.PREP_L2NORM
-    assert lib.b200gdn_prep_fwd(ctypes.byref(p), None) == -2 and b'multiple of 64' in lib.b200gdn_last_error()
+    assert lib.b200gdn_prep_fwd(ctypes.byref(p), None) == -2 and b'are built' in lib.b200gdn_last_error()
     p.K, p.flags = 128, _lib.PREP_GATE
     assert lib.b200gdn_prep_bwd(ctypes.byref(p), None) == -1 and b'is NULL' in lib.b200gdn_last_error()
     assert lib.b200gdn_saved_bytes(16384, 16, 16, 128, 128, 256) == 16384 * 16 * (4 + 128 + 256 * 3) + 256 * 16 * 32768
