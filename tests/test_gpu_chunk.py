@@ -364,3 +364,21 @@ def test_wait_expiry_is_reported_and_context_survives():
     fwd, _ = oracle_chain(d)
     out = run_abi(d, do_bwd=False)
     O.assert_close('o after expiry', fwd['o'], out['o'], 0.005)
+
+
+@pytest.mark.parametrize('gscale', [0.02, 12.0])
+def test_extreme_gates(gscale):
+    """Nearly no decay (g ~ -0.01) and very strong decay (g down to -100 per token: 2^gamma underflows inside a
+    chunk): every factor the kernels form is 2^(non-positive), so nothing overflows and results stay finite and
+    within tolerance of the fp64 oracle chain."""
+    d = make_case(seed=13, **STAGE_CASES['d128_ragged'])
+    d['g'] = d['g'] * gscale
+    fwd, bwd = oracle_chain(d, dtype=torch.float64)
+    out = run_abi(d)
+    for n in ('o', 'ht', 'dq', 'dk', 'dv', 'dg', 'dbeta', 'dh0'):
+        assert torch.isfinite(out[n]).all(), n
+    for n, tol in FWD_TOL.items():
+        if n != 'gamma':
+            O.assert_close(f'{n}', fwd[n].float(), out[n], tol)
+    for n, tol in BWD_TOL.items():
+        O.assert_close(f'{n}', bwd[n].float(), out[n], tol)
