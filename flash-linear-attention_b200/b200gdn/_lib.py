@@ -42,7 +42,7 @@ class RecurrentArgs(C.Structure):
         ('K', C.c_int32), ('V', C.c_int32), ('n_seq', C.c_int32), ('scale', C.c_float), ('flags', C.c_uint32),
         ('qkv_dtype', C.c_int32),
         ('cu_seqlens', _p), ('q', _p), ('k', _p), ('v', _p), ('g', _p), ('beta', _p), ('A_log', _p),
-        ('dt_bias', _p), ('h0', _p), ('o', _p), ('ht', _p),
+        ('dt_bias', _p), ('h0', _p), ('o', _p), ('ht', _p), ('state_indices', _p),
     ]
 
 

@@ -16,7 +16,7 @@ class FusedRecurrentFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, g, beta, A_log, dt_bias, scale, initial_state, output_final_state, flags, cu_seqlens,
-                inplace_state):
+                inplace_state, state_indices=None):
         dev = q.device
         with torch.cuda.device(dev):
             dt = q.dtype if q.dtype in _DTYPE_CODE else torch.float32
@@ -45,7 +45,17 @@ class FusedRecurrentFunction(torch.autograd.Function):
             a.h0 = _lib.ptr(h0)
             o = torch.empty_like(vc)
             ht = None
-            if output_final_state:
+            idx32 = None
+            if state_indices is not None:
+                # a pool of state slots addressed per sequence; the update happens in the pool itself
+                if h0 is None or h0.data_ptr() != initial_state.data_ptr():
+                    raise ValueError("`state_indices` needs `initial_state` to be the fp32 contiguous pool of state slots.")
+                if state_indices.numel() != n_seq:
+                    raise ValueError(f"`state_indices` must have one entry per sequence ({n_seq}), got {state_indices.numel()}.")
+                idx32 = state_indices.to(device=dev, dtype=torch.int32).contiguous()
+                a.state_indices = idx32.data_ptr()
+                ht = initial_state
+            elif output_final_state:
                 if inplace_state and h0 is not None and h0.data_ptr() == initial_state.data_ptr():
                     ht = initial_state
                 else:
@@ -89,7 +99,9 @@ def fused_recurrent_gated_delta_rule(
     (``[N,HV,V,K]`` with ``state_v_first``).  Per-dimension decays ``gk`` / ``gv`` and per-channel beta
     ``[B,T,HV,V]`` belong to other operators of the reference and are rejected.  The extra keyword
     ``inplace_state=True`` writes the final state over ``initial_state`` (fp32, contiguous) instead of
-    allocating a new tensor.
+    allocating a new tensor.  The extra keyword ``state_indices [N]`` (no counterpart in the reference) makes
+    ``initial_state`` a pool of state slots ``[n_slots,HV,K,V]``: sequence ``n`` reads and updates slot
+    ``state_indices[n]`` in place (distinct slots per call), and the pool is returned as the final state.
     """
     if 'transpose_state_layout' in kwargs:
         if state_v_first:
@@ -98,6 +110,7 @@ def fused_recurrent_gated_delta_rule(
                       DeprecationWarning, stacklevel=2)
         state_v_first = kwargs.pop('transpose_state_layout')
     inplace_state = bool(kwargs.pop('inplace_state', False))
+    state_indices = kwargs.pop('state_indices', None)
     if gk is not None or gv is not None:
         raise NotImplementedError('per-dimension decays gk / gv are not part of the gated delta rule path')
     if cu_seqlens is not None:
@@ -105,7 +118,7 @@ def fused_recurrent_gated_delta_rule(
             raise ValueError(
                 f"The batch size is expected to be 1 rather than {q.shape[0]} when using `cu_seqlens`."
                 f"Please flatten variable-length inputs before processing.")
-        if initial_state is not None and initial_state.shape[0] != len(cu_seqlens) - 1:
+        if state_indices is None and initial_state is not None and initial_state.shape[0] != len(cu_seqlens) - 1:
             raise ValueError(
                 f"The number of initial states is expected to be equal to the number of input sequences, "
                 f"i.e., {len(cu_seqlens) - 1} rather than {initial_state.shape[0]}.")
@@ -134,7 +147,7 @@ def fused_recurrent_gated_delta_rule(
     flags |= _lib.REC_NEG_EIGVAL if allow_neg_eigval else 0
     flags |= _lib.REC_STATE_V_FIRST if state_v_first else 0
     return FusedRecurrentFunction.apply(q, k, v, g, beta, A_log, dt_bias, scale, initial_state, output_final_state,
-                                        flags, cu_seqlens, inplace_state)
+                                        flags, cu_seqlens, inplace_state, state_indices)
 
 
 fused_recurrent_gdn = fused_recurrent_gated_delta_rule

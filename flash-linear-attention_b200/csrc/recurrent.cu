@@ -58,8 +58,9 @@ __global__ void __launch_bounds__(NTHREADS, (DK <= 128 ? 8 : 4)) recurrent_kerne
   constexpr int NF = DK / 16;  // float4 per lane in both layouts
   float4 st[NF];
   const int l8 = lane & 7, lg = lane >> 3;
-  const float* h0 = a.h0 ? a.h0 + ((int64_t)n * a.HV + hv) * DK * DV : nullptr;
-  float* ht = a.ht ? a.ht + ((int64_t)n * a.HV + hv) * DK * DV : nullptr;
+  const int64_t slot = a.state_indices ? a.state_indices[n] : n;   // which state of the pool this sequence uses
+  const float* h0 = a.h0 ? a.h0 + (slot * a.HV + hv) * DK * DV : nullptr;
+  float* ht = a.ht ? a.ht + (slot * a.HV + hv) * DK * DV : nullptr;
   auto st_index = [&](int i) -> int64_t {
     if (!VFIRST) {
       int r = warp * (DK / 4) + 4 * i + lg;
@@ -231,8 +232,9 @@ __global__ void __launch_bounds__(256, 2) recurrent_rows_kernel(const b200gdn_re
     len = a.T;
   }
   float4 st[RW];
-  const float* h0 = a.h0 ? a.h0 + ((int64_t)n * a.HV + hv) * DK * DV : nullptr;
-  float* ht = a.ht ? a.ht + ((int64_t)n * a.HV + hv) * DK * DV : nullptr;
+  const int64_t slot = a.state_indices ? a.state_indices[n] : n;   // which state of the pool this sequence uses
+  const float* h0 = a.h0 ? a.h0 + (slot * a.HV + hv) * DK * DV : nullptr;
+  float* ht = a.ht ? a.ht + (slot * a.HV + hv) * DK * DV : nullptr;
   const int col = 4 * lane, r0 = warp * RW;
 #pragma unroll
   for (int i = 0; i < RW; ++i)
@@ -374,7 +376,8 @@ __global__ void __launch_bounds__(288, 1) decode_stream_kernel(const b200gdn_rec
         if (jj >= NS) {
           const int item = (int)blockIdx.x + (jj - NS) * (int)gridDim.x;
           if (!tc5::mbar_wait(&done[s], ((jj - NS) / NS) & 1)) { failed = true; break; }
-          float* ht = a.ht + (int64_t)item * DK * DV;
+          const int64_t slot = a.state_indices ? a.state_indices[item / a.HV] : item / a.HV;
+          float* ht = a.ht + (slot * a.HV + item % a.HV) * DK * DV;
           asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(ht), "r"(tc5::smem_addr(stg)),
                        "r"((uint32_t)S::state_bytes)
                        : "memory");
@@ -400,7 +403,8 @@ __global__ void __launch_bounds__(288, 1) decode_stream_kernel(const b200gdn_rec
           sc[1] = bb;
           const uint32_t qk_bytes = (uint32_t)(DK * esz), v_bytes = (uint32_t)(DV * esz);
           tc5::mbar_expect_tx(&full[s], (uint32_t)S::state_bytes + 2 * qk_bytes + v_bytes);
-          tma::load_1d(stg, a.h0 + (int64_t)item * DK * DV, (uint32_t)S::state_bytes, &full[s]);
+          const int64_t slot = a.state_indices ? a.state_indices[n] : n;
+          tma::load_1d(stg, a.h0 + (slot * a.HV + hv) * DK * DV, (uint32_t)S::state_bytes, &full[s]);
           tma::load_1d(stg + S::o_q, static_cast<const char*>(a.q) + (row * a.H + hq) * DK * esz, qk_bytes, &full[s]);
           tma::load_1d(stg + S::o_k, static_cast<const char*>(a.k) + (row * a.H + hq) * DK * esz, qk_bytes, &full[s]);
           tma::load_1d(stg + S::o_v, static_cast<const char*>(a.v) + (row * a.HV + hv) * DV * esz, v_bytes, &full[s]);

@@ -137,6 +137,10 @@ typedef struct b200gdn_recurrent_args {
   const float* h0;               /* [n_seq,HV,K,V] ([.,.,V,K] when V-first) or NULL */
   void* o;                       /* [B,T,HV,V] */
   float* ht;                     /* like h0, or NULL; may alias h0 for an in-place update */
+  const int32_t* state_indices;  /* device [n_seq] or NULL.  No counterpart in the reference: with it, h0 and ht are
+                                    pools of state slots [n_slots,HV,K,V] and sequence n uses slot state_indices[n]
+                                    (the slots of one call must be distinct), as a serving engine's state cache
+                                    addresses them; without it sequence n uses slot n */
 } b200gdn_recurrent_args;
 
 #define B200GDN_REC_L2NORM 1u         /* q, k <- x * rsqrt(sum x^2 + 1e-6) */

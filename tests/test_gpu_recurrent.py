@@ -189,3 +189,27 @@ def test_large_batch_kernels_with_options(K, T, dtype):
     O.assert_close('ht', ref_ht, ht.cpu(), 1e-5)
     import b200gdn
     b200gdn.device_status()
+
+
+@pytest.mark.parametrize('B,T', [(40, 1), (40, 2), (6, 1)])
+def test_state_pool_addressed_by_indices(B, T):
+    """`state_indices`: the state lives in a pool of slots (a serving engine's cache); each sequence reads and
+    updates its slot in place.  Must equal gather -> plain call -> scatter, bit for bit, and leave other slots alone.
+    (B = 40 exercises the streaming and the whole-state kernels, B = 6 the sliced kernel.)"""
+    from b200gdn import fused_recurrent_gated_delta_rule
+    dev = 'cuda'
+    H, HV, K, V, P = 4, 8, 128, 128, 64
+    gen = torch.Generator(device=dev).manual_seed(B * 10 + T)
+    mk = lambda *s: torch.randn(*s, device=dev, generator=gen)
+    q, k = torch.nn.functional.normalize(mk(B, T, H, K), dim=-1), torch.nn.functional.normalize(mk(B, T, H, K), dim=-1)
+    v, g, beta = mk(B, T, HV, V), torch.nn.functional.logsigmoid(mk(B, T, HV)), torch.sigmoid(mk(B, T, HV))
+    pool = mk(P, HV, K, V) * 0.3
+    idx = torch.randperm(P, device=dev, generator=gen)[:B]
+    o_ref, ht_ref = fused_recurrent_gated_delta_rule(q, k, v, g, beta=beta, initial_state=pool[idx].contiguous(),
+                                                     output_final_state=True)
+    want = pool.clone()
+    want[idx] = ht_ref
+    o, out_pool = fused_recurrent_gated_delta_rule(q, k, v, g, beta=beta, initial_state=pool, state_indices=idx)
+    assert out_pool.data_ptr() == pool.data_ptr()
+    assert torch.equal(o, o_ref)
+    assert torch.equal(pool, want)
