@@ -33,6 +33,7 @@ class ChunkArgs(C.Structure):
         ('d_o', _p), ('dht', _p),
         ('dq', _p), ('dk', _p), ('dv', _p), ('dg', _p), ('dbeta', _p), ('dh0', _p),
         ('dh', _p), ('dv2', _p), ('dw', _p), ('dk_part', _p), ('dG', _p), ('dq_acc', _p),
+        ('options', C.c_uint32), ('A_log', _p), ('dt_bias', _p), ('gate_partials', _p), ('dA_log', _p), ('ddt_bias', _p),
     ]
 
 

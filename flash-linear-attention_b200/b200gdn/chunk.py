@@ -144,7 +144,10 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     (the role of fla/ops/gated_delta_rule/chunk.py:253-392)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, cu_seqlens_cpu):
+    def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, cu_seqlens_cpu,
+                A_log=None, dt_bias=None, options=0):
+        # options: _lib.PREP_GATE / PREP_BETA_SIGMOID / PREP_NEG_EIGVAL bits; g / beta are then the raw pre-activations
+        # and the kernels apply (and differentiate) the activations themselves
         in_dtypes = (q.dtype, k.dtype, v.dtype, g.dtype, beta.dtype)
         dev = q.device
         with torch.cuda.device(dev):
@@ -168,18 +171,24 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             h = torch.empty(n_chunks, HV, K, V, **bf16)
             v_new = torch.empty(rows, HV, V, **bf16)
             a.g, a.beta, a.h0 = gf.data_ptr(), bf.data_ptr(), _lib.ptr(h0)
+            A_log_f = A_log.detach().float().contiguous() if (options & _lib.PREP_GATE) else None
+            bias_f = dt_bias.detach().float().contiguous() if (options & _lib.PREP_GATE) and dt_bias is not None else None
+            a.options, a.A_log, a.dt_bias = options, _lib.ptr(A_log_f), _lib.ptr(bias_f)
             a.o, a.ht = o.data_ptr(), _lib.ptr(ht)
             a.gamma, a.A, a.w, a.u, a.h, a.v_new = (x.data_ptr() for x in (gamma, A, w, u, h, v_new))
             _lib.call('b200gdn_chunk_fwd', a, _stream(qb))
-        ctx.save_for_backward(qb, kb, vb, bf, gamma, A, w, h, v_new, tables[0], tables[1])
-        ctx.meta = (scale, n_chunks, n_seq, initial_state is not None, in_dtypes)
+        ctx.save_for_backward(qb, kb, vb, bf, gamma, A, w, h, v_new, tables[0], tables[1],
+                              gf if (options & _lib.PREP_GATE) else None, A_log_f, bias_f)
+        ctx.meta = (scale, n_chunks, n_seq, initial_state is not None, in_dtypes, options,
+                    None if A_log is None else A_log.dtype, None if dt_bias is None else dt_bias.dtype)
         return o.to(q.dtype), ht
 
     @staticmethod
     def backward(ctx, do, dht):
-        qb, kb, vb, bf, gamma, A, w, h, v_new, chunk_meta, seq_meta = ctx.saved_tensors
-        scale, n_chunks, n_seq, has_h0, in_dtypes = ctx.meta
+        qb, kb, vb, bf, gamma, A, w, h, v_new, chunk_meta, seq_meta, gf, A_log_f, bias_f = ctx.saved_tensors
+        scale, n_chunks, n_seq, has_h0, in_dtypes, options, A_dtype, bias_dtype = ctx.meta
         dev = qb.device
+        dA_log = ddt_bias = None
         with torch.cuda.device(dev):
             B, T, H, K = qb.shape
             HV, V = vb.shape[2], vb.shape[3]
@@ -206,9 +215,21 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
                 dbeta.data_ptr(), _lib.ptr(dh0)
             a.dh, a.dv2, a.dk_part, a.dG, a.dq_acc = dh.data_ptr(), dv2.data_ptr(), \
                 _lib.ptr(dk_part), dG.data_ptr(), _lib.ptr(dq_acc)
+            a.options = options
+            if options & _lib.PREP_GATE:
+                gate_partials = torch.empty(n_chunks, HV, 2, **f32)
+                dA_log = torch.empty(HV, **f32)
+                ddt_bias = torch.empty(HV, **f32) if bias_f is not None else None
+                a.g, a.A_log, a.dt_bias = gf.data_ptr(), A_log_f.data_ptr(), _lib.ptr(bias_f)
+                a.gate_partials, a.dA_log, a.ddt_bias = gate_partials.data_ptr(), dA_log.data_ptr(), _lib.ptr(ddt_bias)
             _lib.call('b200gdn_chunk_bwd', a, _stream(qb))
         qd, kd, vd, gd, bd = in_dtypes
-        return dq.to(qd), dk.to(kd), dv.to(vd), dg.to(gd), dbeta.to(bd), None, dh0, None, None, None
+        if dA_log is not None:
+            dA_log = dA_log.to(A_dtype)
+        if ddt_bias is not None:
+            ddt_bias = ddt_bias.to(bias_dtype)
+        return (dq.to(qd), dk.to(kd), dv.to(vd), dg.to(gd), dbeta.to(bd), None, dh0, None, None, None,
+                dA_log, ddt_bias, None)
 
 
 def chunk_gated_delta_rule(
@@ -296,11 +317,16 @@ def chunk_gated_delta_rule(
     # chunk kernels, one after their backward.
     flags = ((_lib.PREP_L2NORM if use_qk_l2norm_in_kernel else 0) | (_lib.PREP_GATE if use_gate_in_kernel else 0)
              | (_lib.PREP_BETA_SIGMOID if use_beta_sigmoid_in_kernel else 0) | (_lib.PREP_NEG_EIGVAL if allow_neg_eigval else 0))
-    if flags & (_lib.PREP_L2NORM | _lib.PREP_GATE | _lib.PREP_BETA_SIGMOID):
-        if use_gate_in_kernel and A_log.numel() != v.shape[2]:
-            raise ValueError(f"A_log must have HV={v.shape[2]} elements, got {A_log.numel()}.")
-        q, k, g, beta = LayerOptionsFunction.apply(q, k, g, beta, A_log if use_gate_in_kernel else None,
-                                                   dt_bias if use_gate_in_kernel else None, flags)
+    if use_gate_in_kernel and A_log.numel() != v.shape[2]:
+        raise ValueError(f"A_log must have HV={v.shape[2]} elements, got {A_log.numel()}.")
+    use_cp = cp_context is not None and getattr(cp_context, 'group', None) is not None
+    # The gate and beta activations are fused into the first forward and the last backward kernel; the L2 norm (and,
+    # under context parallelism, all three) runs as a pass of its own before / after the chunk kernels.
+    fused = 0 if use_cp else flags & (_lib.PREP_GATE | _lib.PREP_BETA_SIGMOID | _lib.PREP_NEG_EIGVAL)
+    pre = flags & ~fused
+    if pre & (_lib.PREP_L2NORM | _lib.PREP_GATE | _lib.PREP_BETA_SIGMOID):
+        q, k, g, beta = LayerOptionsFunction.apply(q, k, g, beta, A_log if pre & _lib.PREP_GATE else None,
+                                                   dt_bias if pre & _lib.PREP_GATE else None, pre)
     if state_v_first and initial_state is not None:
         initial_state = initial_state.transpose(-1, -2)
 
@@ -310,7 +336,8 @@ def chunk_gated_delta_rule(
         return o, None
 
     o, final_state = ChunkGatedDeltaRuleFunction.apply(
-        q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, cu_seqlens_cpu)
+        q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, cu_seqlens_cpu,
+        A_log if fused & _lib.PREP_GATE else None, dt_bias if fused & _lib.PREP_GATE else None, fused)
     if final_state is not None and state_v_first:
         final_state = final_state.transpose(-1, -2).contiguous()
     return o, final_state

@@ -94,7 +94,10 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
   float* c_vb = c_kbg + 4 * BT;  // [4][64] colsum(A . dU V^T)
   float* c_m2 = c_vb + 4 * BT;   // [4][64] colsum(M2 . K K^T)
   float* r_mk = c_m2 + 4 * BT;   // rowsum(M . K K^T), two column halves
-  uint64_t* bar = reinterpret_cast<uint64_t*>(r_mk + 2 * BT);
+  float* sgm = r_mk + 2 * BT;    // fused beta option: sigmoid(raw beta), for its derivative
+  float* gx = sgm + BT;          // fused gate option: raw g + dt_bias
+  float* gred = gx + BT;         // [4] partial sums of the gate-parameter gradients (two warps)
+  uint64_t* bar = reinterpret_cast<uint64_t*>(gred + 4);
   uint64_t* bar_ld = bar + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_ld + 1);
 
@@ -161,7 +164,15 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
     }
     if (tid < BT) {
       const bool ok = tid < cm.len;
-      bet[tid] = ok ? a.beta[(row0 + tid) * a.HV + hv] : 0.f;
+      float b = ok ? a.beta[(row0 + tid) * a.HV + hv] : 0.f;
+      if (a.options & B200GDN_PREP_BETA_SIGMOID) {   // raw beta: the kernels work with (1|2) sigmoid(beta)
+        const float sg = 1.f / (1.f + expf(-b));
+        sgm[tid] = sg;
+        b = ok ? ((a.options & B200GDN_PREP_NEG_EIGVAL) ? 2.f : 1.f) * sg : 0.f;
+      }
+      bet[tid] = b;
+      if (a.options & B200GDN_PREP_GATE)
+        gx[tid] = (ok ? a.g[(row0 + tid) * a.HV + hv] : 0.f) + (a.dt_bias ? a.dt_bias[hv] : 0.f);
       dGin[tid] = ok ? a.dG[(row0 + tid) * a.HV + hv] : 0.f;
     }
     if (!tc5::mbar_wait(bar_ld, gi & 1)) failed = true;
@@ -417,7 +428,12 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
       const float cvb = (c_vb[i] + c_vb[BT + i]) + (c_vb[2 * BT + i] + c_vb[3 * BT + i]);
       const float cm2 = (c_m2[i] + c_m2[BT + i]) + (c_m2[2 * BT + i] + c_m2[3 * BT + i]);
       float x = ckbg * bge[i] + bet[i] * rmk - cm2 + dGin[i];
-      if (i < cm.len) a.dbeta[(row0 + i) * a.HV + hv] = ckbg * eg[i] + cvb + rmk;
+      if (i < cm.len) {
+        float db = ckbg * eg[i] + cvb + rmk;
+        if (a.options & B200GDN_PREP_BETA_SIGMOID)   // chain rule through (1|2) sigmoid
+          db *= ((a.options & B200GDN_PREP_NEG_EIGVAL) ? 2.f : 1.f) * sgm[i] * (1.f - sgm[i]);
+        a.dbeta[(row0 + i) * a.HV + hv] = db;
+      }
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const float y = __shfl_down_sync(0xffffffffu, x, o);
@@ -426,7 +442,37 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
       dGs[i] = x;   // suffix sum inside the warp
     }
     if (__syncthreads_or(!ph.wait())) { failed = true; break; }
-    if (tid < cm.len) a.dg[(row0 + tid) * a.HV + hv] = dGs[tid] + (tid < 32 ? dGs[32] : 0.f);
+    if (!(a.options & B200GDN_PREP_GATE)) {
+      if (tid < cm.len) a.dg[(row0 + tid) * a.HV + hv] = dGs[tid] + (tid < 32 ? dGs[32] : 0.f);
+    } else {
+      // fused gate: g = -exp(A_log) softplus(x), x = g_raw + dt_bias.  dg_raw = dg (-exp(A_log)) sigmoid(x);
+      // dA_log += dg g and ddt_bias += dg_raw, summed over the chunk here and over the chunks by a second kernel
+      if (tid < BT) {
+        float sA = 0.f, sB = 0.f;
+        if (tid < cm.len) {
+          const float dgi = dGs[tid] + (tid < 32 ? dGs[32] : 0.f);
+          const float x = gx[tid], negA = -expf(a.A_log[hv]);
+          const float draw = dgi * negA / (1.f + expf(-x));
+          a.dg[(row0 + tid) * a.HV + hv] = draw;
+          sA = dgi * negA * (x > 20.f ? x : log1pf(expf(x)));
+          sB = draw;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          sA += __shfl_xor_sync(0xffffffffu, sA, o);
+          sB += __shfl_xor_sync(0xffffffffu, sB, o);
+        }
+        if (lane == 0) {
+          gred[2 * warp] = sA;
+          gred[2 * warp + 1] = sB;
+        }
+      }
+      __syncthreads();
+      if (tid == 0) {
+        a.gate_partials[((int64_t)c * a.HV + hv) * 2 + 0] = gred[0] + gred[2];
+        a.gate_partials[((int64_t)c * a.HV + hv) * 2 + 1] = gred[1] + gred[3];
+      }
+    }
 
     // ---- epilogue 5: dk = accumulator + part from the dq/dk kernel (group-accumulated in fp32)
     {
@@ -483,6 +529,19 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
   if (warp == 1) tc5::tmem_dealloc(tm, 256);
 }
 
+// dA_log[hv] = sum over chunks of the per-chunk partials (fixed order: reproducible); same for ddt_bias
+__global__ void gate_param_reduce_kernel(const b200gdn_chunk_args a) {
+  const int hv = blockIdx.x * blockDim.x + threadIdx.x;
+  if (hv >= a.HV) return;
+  float sA = 0.f, sB = 0.f;
+  for (int c = 0; c < a.n_chunks; ++c) {
+    sA += a.gate_partials[((int64_t)c * a.HV + hv) * 2 + 0];
+    sB += a.gate_partials[((int64_t)c * a.HV + hv) * 2 + 1];
+  }
+  a.dA_log[hv] = sA;
+  if (a.ddt_bias) a.ddt_bias[hv] = sB;
+}
+
 template <int DK, int DV, bool GROUPED>
 int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
   using S = WyTcSmem<DK, DV>;
@@ -500,12 +559,19 @@ int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
   if (rc != 0) return set_error(B200GDN_ERR_CUDA, "bwd_wy: cuTensorMapEncodeTiled failed (%d)", rc);
   dim3 grid(a.n_chunks, a.H);
   bwd_wy_kernel<DK, DV, GROUPED><<<grid, NTHREADS, S::bytes, st>>>(a, m);
-  return check_launch("bwd_wy");
+  if (int e = check_launch("bwd_wy")) return e;
+  if (a.options & B200GDN_PREP_GATE) {
+    gate_param_reduce_kernel<<<(a.HV + 63) / 64, 64, 0, st>>>(a);
+    return check_launch("gate_param_reduce");
+  }
+  return 0;
 }
 
 }  // namespace
 
 int launch_bwd_wy(const b200gdn_chunk_args& a, cudaStream_t st) {
+  if ((a.options & B200GDN_PREP_GATE) && (a.g == nullptr || a.A_log == nullptr || a.gate_partials == nullptr || a.dA_log == nullptr))
+    return set_error(B200GDN_ERR_BAD_ARGUMENT, "bwd_wy: the fused gate needs g (raw), A_log, gate_partials and dA_log");
   if (a.HV > a.H && a.dk_part == nullptr) return set_error(B200GDN_ERR_BAD_ARGUMENT, "bwd_wy: dk_part is required when HV > H");
   const bool grouped = a.HV > a.H;
   if (a.K == 128 && a.V == 128) return grouped ? launch<128, 128, true>(a, st) : launch<128, 128, false>(a, st);

@@ -150,6 +150,14 @@ __global__ void __launch_bounds__(NTHREADS, 4) intra_fwd_kernel(const b200gdn_ch
   if (tid < BT) {
     // inclusive scan of g over the chunk: shuffle scan inside each of the two warps, carry added below
     cp_async_wait<0>();   // this thread's own g and beta
+    if (a.options != 0 && tid < cm.len) {   // the layer's gate / beta activations, fused (rows past the end stay 0)
+      if (a.options & B200GDN_PREP_GATE) {
+        const float x = graw[tid] + (a.dt_bias ? a.dt_bias[hv] : 0.f);
+        graw[tid] = -expf(a.A_log[hv]) * (x > 20.f ? x : log1pf(expf(x)));
+      }
+      if (a.options & B200GDN_PREP_BETA_SIGMOID)
+        bet[tid] = ((a.options & B200GDN_PREP_NEG_EIGVAL) ? 2.f : 1.f) / (1.f + expf(-bet[tid]));
+    }
     float s = graw[tid];
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -387,6 +395,8 @@ int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
 }  // namespace
 
 int launch_intra_fwd(const b200gdn_chunk_args& a, cudaStream_t st) {
+  if ((a.options & B200GDN_PREP_GATE) && a.A_log == nullptr)
+    return set_error(B200GDN_ERR_BAD_ARGUMENT, "intra_fwd: the fused gate needs A_log");
   if (a.K == 128 && a.V == 128) return launch<128, 128>(a, st);
   if (a.K == 64 && a.V == 64) return launch<64, 64>(a, st);
   return set_error(B200GDN_ERR_UNSUPPORTED, "intra_fwd: K=%d V=%d not built (64/64 and 128/128 are)", a.K, a.V);

@@ -50,6 +50,11 @@ typedef enum b200gdn_status {
 #define B200GDN_BWD_DQKWG 4u     /* dq, dk (local part), dG <- q, k, v_new, gamma, h, dv2, do, dh */
 #define B200GDN_BWD_WY 8u        /* dk, dv, dbeta, dg      <- k, v, beta, gamma, A, h, dv2, dk (local part), dG */
 
+/* option bits shared by b200gdn_chunk_args.options and b200gdn_prep_args.flags (described with those structs) */
+#define B200GDN_PREP_L2NORM 1u
+#define B200GDN_PREP_GATE 2u
+#define B200GDN_PREP_BETA_SIGMOID 4u
+#define B200GDN_PREP_NEG_EIGVAL 8u
 typedef struct b200gdn_chunk_args {
   int32_t struct_bytes;          /* = sizeof(b200gdn_chunk_args), checked */
   int32_t rows, H, HV, K, V;
@@ -94,6 +99,17 @@ typedef struct b200gdn_chunk_args {
   float* dk_part;                /* [rows,H,K], only read/written when HV > H (fp32 sum over a group's heads) */
   float* dG;                     /* [rows,HV] */
   float* dq_acc;                 /* [rows,H,K], only read/written when HV > H */
+  /* The gate and beta options of the layer, fused (fla/ops/gated_delta_rule/gate.py:63-158, fla/ops/common/gate.py:18-50):
+   * with B200GDN_PREP_GATE in `options`, g is the raw pre-activation and the kernels use
+   * -exp(A_log) softplus(g + dt_bias); with B200GDN_PREP_BETA_SIGMOID (and B200GDN_PREP_NEG_EIGVAL), beta is raw and
+   * the kernels use (1|2) sigmoid(beta).  dg / dbeta are then gradients w.r.t. the raw tensors, and the backward
+   * also gives dA_log and ddt_bias.  options = 0: g and beta are used as they are. */
+  uint32_t options;
+  const float* A_log;            /* [HV] (GATE) */
+  const float* dt_bias;          /* [HV] or NULL */
+  float* gate_partials;          /* workspace fp32 [n_chunks,HV,2] (GATE, backward) */
+  float* dA_log;                 /* out [HV] (GATE, backward) */
+  float* ddt_bias;               /* out [HV] or NULL */
 } b200gdn_chunk_args;
 
 /* Replaces chunk_gated_delta_rule_fwd (fla/ops/gated_delta_rule/chunk.py:33-123):
@@ -177,10 +193,6 @@ int b200gdn_affine_apply(const b200gdn_affine_args* args, void* stream);
  *                 (fused_beta_sigmoid_fwd/bwd_kernel, fla/ops/common/gate.py:18-50)
  * Outputs the chunk entry points consume directly: q, k in bf16, g and beta in fp32.  An option that is off leaves
  * its outputs untouched (pass the raw tensor to the chunk call instead). */
-#define B200GDN_PREP_L2NORM 1u
-#define B200GDN_PREP_GATE 2u
-#define B200GDN_PREP_BETA_SIGMOID 4u
-#define B200GDN_PREP_NEG_EIGVAL 8u
 #define B200GDN_PREP_PART_ROWS 128       /* rows of g reduced by one CTA of the backward pass */
 typedef struct b200gdn_prep_args {
   int32_t struct_bytes;

@@ -382,3 +382,38 @@ def test_extreme_gates(gscale):
             O.assert_close(f'{n}', fwd[n].float(), out[n], tol)
     for n, tol in BWD_TOL.items():
         O.assert_close(f'{n}', bwd[n].float(), out[n], tol)
+
+
+def test_fused_gate_and_beta_equal_the_separate_passes():
+    """The gate / beta activations fused into the first forward and the last backward kernel against the same
+    activations run as separate passes (LayerOptionsFunction) around the plain op: identical outputs, gradients
+    equal to fp32 rounding (the two evaluate sigmoid in a different order)."""
+    from b200gdn import _lib, chunk_gated_delta_rule
+    from b200gdn.chunk import LayerOptionsFunction
+    dev = 'cuda'
+    B, T, H, HV, K, V = 2, 200, 2, 4, 128, 128
+    q, k, v, _, _, do = _inputs(B, T, H, HV, K, V, seed=21)
+    gen = torch.Generator(device=dev).manual_seed(22)
+    graw = torch.randn(B, T, HV, device=dev, generator=gen) * 2
+    braw = torch.randn(B, T, HV, device=dev, generator=gen)
+    A_log = torch.randn(HV, device=dev, generator=gen) * 0.3
+    dt_bias = torch.randn(HV, device=dev, generator=gen) * 0.3
+
+    def run(fused):
+        leaves = [x.clone().requires_grad_(True) for x in (q, k, v, graw, braw, A_log, dt_bias)]
+        q_, k_, v_, g_, b_, A_, dt_ = leaves
+        if fused:
+            o, _ = chunk_gated_delta_rule(q_, k_, v_, g_, b_, use_gate_in_kernel=True, A_log=A_, dt_bias=dt_,
+                                          use_beta_sigmoid_in_kernel=True, allow_neg_eigval=True)
+        else:
+            flags = _lib.PREP_GATE | _lib.PREP_BETA_SIGMOID | _lib.PREP_NEG_EIGVAL
+            _, _, g2, b2 = LayerOptionsFunction.apply(q_, k_, g_, b_, A_, dt_, flags)
+            o, _ = chunk_gated_delta_rule(q_, k_, v_, g2, b2)
+        o.backward(do)
+        return [o] + [x.grad for x in leaves]
+    a, b = run(True), run(False)
+    assert torch.equal(a[0], b[0])
+    for i in (1, 2, 3):
+        assert torch.equal(a[i], b[i]), i            # dq, dk, dv do not pass through the activations
+    for i, name in ((4, 'dg'), (5, 'dbeta'), (6, 'dA_log'), (7, 'ddt_bias')):
+        O.assert_close(name, b[i].float().cpu(), a[i].float().cpu(), 1e-5)
