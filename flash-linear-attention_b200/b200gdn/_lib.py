@@ -43,7 +43,7 @@ class RecurrentArgs(C.Structure):
         ('K', C.c_int32), ('V', C.c_int32), ('n_seq', C.c_int32), ('scale', C.c_float), ('flags', C.c_uint32),
         ('qkv_dtype', C.c_int32),
         ('cu_seqlens', _p), ('q', _p), ('k', _p), ('v', _p), ('g', _p), ('beta', _p), ('A_log', _p),
-        ('dt_bias', _p), ('h0', _p), ('o', _p), ('ht', _p), ('state_indices', _p),
+        ('dt_bias', _p), ('h0', _p), ('o', _p), ('ht', _p), ('state_indices', _p), ('n_slots', C.c_int32),
     ]
 
 
@@ -74,7 +74,7 @@ EXPORTS = (
     'b200gdn_chunk_fwd', 'b200gdn_chunk_bwd', 'b200gdn_recurrent_fwd', 'b200gdn_affine_apply',
     'b200gdn_saved_bytes', 'b200gdn_bwd_workspace_bytes', 'b200gdn_last_launch_count',
     'b200gdn_abi_version', 'b200gdn_last_error', 'b200gdn_device_status', 'b200gdn_prep_fwd', 'b200gdn_prep_bwd',
-    'b200gdn_selftest_wait_expiry',
+    'b200gdn_selftest_wait_expiry', 'b200gdn_chunk_fwd_static',
 )
 
 _lib = None
@@ -99,7 +99,7 @@ def load():
                 '(or __graft_entry__.build()). There is no fallback path.')
         lib = C.CDLL(LIB_PATH)
         for name in ('b200gdn_chunk_fwd', 'b200gdn_chunk_bwd', 'b200gdn_recurrent_fwd', 'b200gdn_affine_apply',
-                     'b200gdn_prep_fwd', 'b200gdn_prep_bwd'):
+                     'b200gdn_prep_fwd', 'b200gdn_prep_bwd', 'b200gdn_chunk_fwd_static'):
             fn = getattr(lib, name)
             fn.restype = C.c_int
             fn.argtypes = [C.c_void_p, C.c_void_p]

@@ -79,8 +79,10 @@ class B200GDNBackend(_Base):
     ) -> Tuple[bool, Optional[str]]:
         if not q.is_cuda:
             return False, 'inputs are not on a CUDA device'
-        if q.dtype not in (torch.bfloat16, torch.float16, torch.float32):
-            return False, f'unsupported dtype {q.dtype}'
+        # the tensor-core kernels compute on bf16 operands; other dtypes go to the reference's own path, which keeps
+        # their precision (the direct function would round them to bf16)
+        if not (q.dtype == k.dtype == v.dtype == torch.bfloat16):
+            return False, f'q/k/v dtypes {q.dtype}/{k.dtype}/{v.dtype}: only bf16 is served'
         if (q.shape[-1], v.shape[-1]) not in _SUPPORTED_HEAD_DIMS:
             return False, f'head dims K={q.shape[-1]} V={v.shape[-1]} not built'
         if q.ndim != 4 or v.ndim != 4 or g.ndim != 3 or beta.ndim != 3:

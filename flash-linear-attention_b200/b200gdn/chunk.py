@@ -139,16 +139,40 @@ def new_chunk_args(q, k, v, scale, tables) -> _lib.ChunkArgs:
     return a
 
 
+def carve(dev, zero, *specs):
+    """One device allocation cut into tensors: ``specs`` are (shape, dtype) pairs, every tensor starts on a 256-byte
+    boundary.  A forward + backward pass needs about twenty intermediates; one allocation per pass instead of one per
+    tensor keeps the host-side cost of a step small.  ``zero`` fills the allocation with zeros (needed when the packed
+    buffer has rows that belong to no sequence: the kernels never write them)."""
+    offs, total = [], 0
+    for shape, dtype in specs:
+        n = 1
+        for x in shape:
+            n *= int(x)
+        offs.append(total)
+        total += (n * dtype.itemsize + 255) // 256 * 256
+    buf = (torch.zeros if zero else torch.empty)(max(total, 256), dtype=torch.uint8, device=dev)
+    out = []
+    for (shape, dtype), off in zip(specs, offs):
+        n = 1
+        for x in shape:
+            n *= int(x)
+        nbytes = n * dtype.itemsize
+        out.append(buf[off:off + nbytes].view(dtype).view(*shape))
+    return out
+
+
 class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     """Autograd node around b200gdn_chunk_fwd / b200gdn_chunk_bwd
     (the role of fla/ops/gated_delta_rule/chunk.py:253-392)."""
 
     @staticmethod
     def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, cu_seqlens_cpu,
-                A_log=None, dt_bias=None, options=0):
+                A_log=None, dt_bias=None, options=0, out_dtype=None):
         # options: _lib.PREP_GATE / PREP_BETA_SIGMOID / PREP_NEG_EIGVAL bits; g / beta are then the raw pre-activations
         # and the kernels apply (and differentiate) the activations themselves
         in_dtypes = (q.dtype, k.dtype, v.dtype, g.dtype, beta.dtype)
+        out_dtype = out_dtype or q.dtype
         dev = q.device
         with torch.cuda.device(dev):
             qb, kb, vb = (x.to(torch.bfloat16).contiguous() for x in (q, k, v))
@@ -160,16 +184,14 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             n_chunks, n_seq = tables[2]
             rows = B * T
             a = new_chunk_args(qb, kb, vb, scale, tables)
-            bf16 = dict(dtype=torch.bfloat16, device=dev)
-            f32 = dict(dtype=torch.float32, device=dev)
-            o = torch.empty(B, T, HV, V, **bf16)
-            ht = torch.empty(n_seq, HV, K, V, **f32) if output_final_state else None
-            gamma = torch.empty(n_chunks, HV, 64, **f32)
-            A = torch.empty(rows, HV, 64, **bf16)
-            w = torch.empty(rows, HV, K, **bf16)
-            u = torch.empty(rows, HV, V, **bf16)
-            h = torch.empty(n_chunks, HV, K, V, **bf16)
-            v_new = torch.empty(rows, HV, V, **bf16)
+            bf16, f32 = torch.bfloat16, torch.float32
+            need_grad = any(ctx.needs_input_grad[:5]) or ctx.needs_input_grad[6]
+            zero = not tables.covered
+            o = (torch.zeros if zero else torch.empty)(B, T, HV, V, dtype=bf16, device=dev)
+            ht = torch.empty(n_seq, HV, K, V, dtype=f32, device=dev) if output_final_state else None
+            gamma, A, w, u, v_new, h = carve(
+                dev, zero, ((n_chunks, HV, 64), f32), ((rows, HV, 64), bf16), ((rows, HV, K), bf16), ((rows, HV, V), bf16),
+                ((rows, HV, V), bf16), ((n_chunks, HV, K, V), bf16))
             a.g, a.beta, a.h0 = gf.data_ptr(), bf.data_ptr(), _lib.ptr(h0)
             A_log_f = A_log.detach().float().contiguous() if (options & _lib.PREP_GATE) else None
             bias_f = dt_bias.detach().float().contiguous() if (options & _lib.PREP_GATE) and dt_bias is not None else None
@@ -177,16 +199,17 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             a.o, a.ht = o.data_ptr(), _lib.ptr(ht)
             a.gamma, a.A, a.w, a.u, a.h, a.v_new = (x.data_ptr() for x in (gamma, A, w, u, h, v_new))
             _lib.call('b200gdn_chunk_fwd', a, _stream(qb))
-        ctx.save_for_backward(qb, kb, vb, bf, gamma, A, w, h, v_new, tables[0], tables[1],
-                              gf if (options & _lib.PREP_GATE) else None, A_log_f, bias_f)
+        if need_grad:
+            ctx.save_for_backward(qb, kb, vb, bf, gamma, A, w, h, v_new, tables[0], tables[1],
+                                  gf if (options & _lib.PREP_GATE) else None, A_log_f, bias_f)
         ctx.meta = (scale, n_chunks, n_seq, initial_state is not None, in_dtypes, options,
-                    None if A_log is None else A_log.dtype, None if dt_bias is None else dt_bias.dtype)
-        return o.to(q.dtype), ht
+                    None if A_log is None else A_log.dtype, None if dt_bias is None else dt_bias.dtype, zero)
+        return o.to(out_dtype), ht
 
     @staticmethod
     def backward(ctx, do, dht):
         qb, kb, vb, bf, gamma, A, w, h, v_new, chunk_meta, seq_meta, gf, A_log_f, bias_f = ctx.saved_tensors
-        scale, n_chunks, n_seq, has_h0, in_dtypes, options, A_dtype, bias_dtype = ctx.meta
+        scale, n_chunks, n_seq, has_h0, in_dtypes, options, A_dtype, bias_dtype, zero = ctx.meta
         dev = qb.device
         dA_log = ddt_bias = None
         with torch.cuda.device(dev):
@@ -196,19 +219,26 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             dob = do.to(torch.bfloat16).contiguous()
             dhtf = None if dht is None else dht.float().contiguous()
             a = new_chunk_args(qb, kb, vb, scale, (chunk_meta, seq_meta, (n_chunks, n_seq)))
-            bf16 = dict(dtype=torch.bfloat16, device=dev)
-            f32 = dict(dtype=torch.float32, device=dev)
-            dq = torch.empty(B, T, H, K, **bf16)
-            dk = torch.empty(B, T, H, K, **bf16)
-            dv = torch.empty(B, T, HV, V, **bf16)
-            dg = torch.empty(B, T, HV, **f32)
-            dbeta = torch.empty(B, T, HV, **f32)
-            dh0 = torch.empty(n_seq, HV, K, V, **f32) if has_h0 else None
-            dh = torch.empty(n_chunks, HV, K, V, **bf16)
-            dv2 = torch.empty(rows, HV, V, **bf16)
-            dk_part = torch.empty(rows, H, K, **f32) if HV > H else None
-            dG = torch.empty(rows, HV, **f32)
-            dq_acc = torch.empty(rows, H, K, **f32) if HV > H else None
+            bf16, f32 = torch.bfloat16, torch.float32
+            grouped = HV > H
+            gate = bool(options & _lib.PREP_GATE)
+            # results first (they outlive the call), then the workspace
+            dq, dk, dv, dg, dbeta, dh0, dh, dv2, dG, dk_part, dq_acc, gate_partials, dA_log, ddt_bias = carve(
+                dev, zero,
+                ((B, T, H, K), bf16), ((B, T, H, K), bf16), ((B, T, HV, V), bf16), ((B, T, HV), f32), ((B, T, HV), f32),
+                ((n_seq, HV, K, V) if has_h0 else (0,), f32),
+                ((n_chunks, HV, K, V), bf16), ((rows, HV, V), bf16), ((rows, HV), f32),
+                ((rows, H, K) if grouped else (0,), f32), ((rows, H, K) if grouped else (0,), f32),
+                ((n_chunks, HV, 2) if gate else (0,), f32), ((HV,) if gate else (0,), f32),
+                ((HV,) if gate and bias_f is not None else (0,), f32))
+            if not has_h0:
+                dh0 = None
+            if not grouped:
+                dk_part = dq_acc = None
+            if not gate:
+                gate_partials = dA_log = None
+            if not (gate and bias_f is not None):
+                ddt_bias = None
             a.beta, a.gamma, a.A, a.w, a.h, a.v_new = (x.data_ptr() for x in (bf, gamma, A, w, h, v_new))
             a.d_o, a.dht = dob.data_ptr(), _lib.ptr(dhtf)
             a.dq, a.dk, a.dv, a.dg, a.dbeta, a.dh0 = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dg.data_ptr(), \
@@ -216,10 +246,7 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             a.dh, a.dv2, a.dk_part, a.dG, a.dq_acc = dh.data_ptr(), dv2.data_ptr(), \
                 _lib.ptr(dk_part), dG.data_ptr(), _lib.ptr(dq_acc)
             a.options = options
-            if options & _lib.PREP_GATE:
-                gate_partials = torch.empty(n_chunks, HV, 2, **f32)
-                dA_log = torch.empty(HV, **f32)
-                ddt_bias = torch.empty(HV, **f32) if bias_f is not None else None
+            if gate:
                 a.g, a.A_log, a.dt_bias = gf.data_ptr(), A_log_f.data_ptr(), _lib.ptr(bias_f)
                 a.gate_partials, a.dA_log, a.ddt_bias = gate_partials.data_ptr(), dA_log.data_ptr(), _lib.ptr(ddt_bias)
             _lib.call('b200gdn_chunk_bwd', a, _stream(qb))
@@ -229,7 +256,7 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
         if ddt_bias is not None:
             ddt_bias = ddt_bias.to(bias_dtype)
         return (dq.to(qd), dk.to(kd), dv.to(vd), dg.to(gd), dbeta.to(bd), None, dh0, None, None, None,
-                dA_log, ddt_bias, None)
+                dA_log, ddt_bias, None, None)
 
 
 def chunk_gated_delta_rule(
@@ -261,7 +288,16 @@ def chunk_gated_delta_rule(
     ``chunk_size`` (16/32/64 accepted; the result does not depend on it and 64 is always used) and the
     deprecated ``transpose_state_layout`` are honoured; ``head_first`` raises as in the reference.
     ``chunk_indices`` is accepted and ignored (the chunk tables are rebuilt from ``cu_seqlens``).
+
+    Precision: the tensor-core kernels compute on bf16 q, k, v (fp32 accumulation, fp32 gates and states).  fp16 /
+    fp32 q, k, v are accepted, ROUNDED TO BF16 on entry, and ``o`` and the gradients are cast back to the caller's
+    dtypes: the result has bf16 accuracy (the reference's own fp32 test uses the bf16-level tolerance 0.005,
+    tests/ops/test_gdn.py:203-278).  Callers that need fp32 arithmetic use the reference's Triton path:
+    ``B200GDNBackend``'s verifier declines non-bf16 inputs so that the dispatcher falls through to it.
+    A packed buffer may have padding rows before ``cu_seqlens[0]`` or after ``cu_seqlens[-1]``; their outputs and
+    gradients are zero, and their q / k / v / do values must be finite.
     """
+    out_dtype = q.dtype
     if 'transpose_state_layout' in kwargs:
         if state_v_first:
             raise ValueError("Cannot pass both `state_v_first` and the deprecated `transpose_state_layout`.")
@@ -333,11 +369,11 @@ def chunk_gated_delta_rule(
     if cp_context is not None and getattr(cp_context, 'group', None) is not None:
         from .cp import chunk_gated_delta_rule_cp
         o = chunk_gated_delta_rule_cp(q, k, v, g, beta, scale, cp_context)
-        return o, None
+        return o.to(out_dtype), None
 
     o, final_state = ChunkGatedDeltaRuleFunction.apply(
         q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, cu_seqlens_cpu,
-        A_log if fused & _lib.PREP_GATE else None, dt_bias if fused & _lib.PREP_GATE else None, fused)
+        A_log if fused & _lib.PREP_GATE else None, dt_bias if fused & _lib.PREP_GATE else None, fused, out_dtype)
     if final_state is not None and state_v_first:
         final_state = final_state.transpose(-1, -2).contiguous()
     return o, final_state

@@ -54,10 +54,13 @@ class FusedRecurrentFunction(torch.autograd.Function):
                     raise ValueError(f"`state_indices` must have one entry per sequence ({n_seq}), got {state_indices.numel()}.")
                 idx32 = state_indices.to(device=dev, dtype=torch.int32).contiguous()
                 a.state_indices = idx32.data_ptr()
+                a.n_slots = initial_state.shape[0]
                 ht = initial_state
+                ctx.mark_dirty(initial_state)   # the pool is updated in place and returned
             elif output_final_state:
                 if inplace_state and h0 is not None and h0.data_ptr() == initial_state.data_ptr():
                     ht = initial_state
+                    ctx.mark_dirty(initial_state)
                 else:
                     shape = (n_seq, HV, V, K) if flags & _lib.REC_STATE_V_FIRST else (n_seq, HV, K, V)
                     ht = torch.empty(shape, dtype=torch.float32, device=dev)
@@ -101,7 +104,9 @@ def fused_recurrent_gated_delta_rule(
     ``inplace_state=True`` writes the final state over ``initial_state`` (fp32, contiguous) instead of
     allocating a new tensor.  The extra keyword ``state_indices [N]`` (no counterpart in the reference) makes
     ``initial_state`` a pool of state slots ``[n_slots,HV,K,V]``: sequence ``n`` reads and updates slot
-    ``state_indices[n]`` in place (distinct slots per call), and the pool is returned as the final state.
+    ``state_indices[n]`` in place (distinct slots per call), and the pool is returned as the final state.  An index
+    outside ``[0, n_slots)`` (a serving engine's ``-1`` padding) marks a padding sequence: its slot is left untouched
+    and its output row is meaningless.
     """
     if 'transpose_state_layout' in kwargs:
         if state_v_first:

@@ -11,6 +11,13 @@ CHUNK = 64
 _cache: dict = {}
 
 
+class Tables(tuple):
+    """(chunk_meta, seq_meta, (n_chunks, n_seq)) plus ``covered``: False when token rows before the first or after
+    the last sequence belong to no sequence (a padded packed buffer).  The kernels never write such rows, so the
+    caller zero-fills its intermediates then."""
+    covered = True
+
+
 def build_tables(bounds: Sequence[Tuple[int, int]]):
     """chunk_meta [n_chunks,4] = (sequence, first row, valid rows, index inside the sequence) and
     seq_meta [n_seq,2] = (first chunk, number of chunks), as int32 numpy arrays.  Chunking restarts at
@@ -32,7 +39,7 @@ def build_tables(bounds: Sequence[Tuple[int, int]]):
 
 
 def tables_for(B: int, T: int, cu_seqlens: Optional[torch.Tensor], cu_seqlens_cpu: Optional[torch.Tensor],
-               device: torch.device):
+               device: torch.device) -> Tables:
     """Device tables for a dense [B,T] batch or a packed batch; memoised by shape / by the identity of
     ``cu_seqlens`` (the reference memoises its index tensors the same way, fla/utils/_decorators.py:33-80).
     A packed batch without ``cu_seqlens_cpu`` costs one device-to-host copy on first use."""
@@ -40,19 +47,22 @@ def tables_for(B: int, T: int, cu_seqlens: Optional[torch.Tensor], cu_seqlens_cp
         key = ('dense', B, T, str(device))
         hit = _cache.get(key)
         if hit is not None:
-            return hit
+            return hit[0]
         bounds = [(b * T, (b + 1) * T) for b in range(B)]
     else:
-        key = ('varlen', id(cu_seqlens), str(device))
+        key = ('varlen', id(cu_seqlens), B * T, str(device))
         hit = _cache.get(key)
-        if hit is not None and hit[3] is cu_seqlens:
-            return hit[:3]
+        if hit is not None and hit[1] is cu_seqlens:
+            return hit[0]
         cpu = cu_seqlens_cpu if cu_seqlens_cpu is not None else cu_seqlens.cpu()
         cu = cpu.to(torch.int64).tolist()
         bounds = [(cu[i], cu[i + 1]) for i in range(len(cu) - 1)]
+        if cu and (cu[0] < 0 or cu[-1] > B * T):
+            raise ValueError(f'cu_seqlens [{cu[0]}, {cu[-1]}] reaches outside the {B * T} token rows')
     cm, sm = build_tables(bounds)
-    out = (torch.from_numpy(cm).to(device), torch.from_numpy(sm).to(device), (cm.shape[0], sm.shape[0]))
+    out = Tables((torch.from_numpy(cm).to(device), torch.from_numpy(sm).to(device), (cm.shape[0], sm.shape[0])))
+    out.covered = bool(bounds) and bounds[0][0] == 0 and bounds[-1][1] == B * T
     if len(_cache) > 64:
         _cache.clear()
-    _cache[key] = out if cu_seqlens is None else out + (cu_seqlens,)
+    _cache[key] = (out, cu_seqlens)
     return out

@@ -18,6 +18,8 @@ int set_error(int code, const char* fmt, ...) {
   return code;
 }
 
+void reset_launch_count() { g_launches = 0; }
+
 int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(B200GDN_ERR_CUDA, "%s launch: %s", what, cudaGetErrorString(e));

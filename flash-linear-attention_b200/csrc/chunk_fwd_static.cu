@@ -11,8 +11,11 @@
 // Nothing here calls cudaMalloc, cudaFree or any allocating library routine.
 //
 // The array is shared by every call on a device and keeps whatever the previous call left in it.  Nothing
-// in the forward pass needs it to start at zero: each stage writes every element that a later stage reads
-// (rows beyond a ragged chunk's length are neither written nor read), so no clearing pass is run.  Two
+// in the forward pass needs it to start at zero: each stage writes every element of a valid token row that a
+// later stage uses.  (Full 64-row tile loads do touch rows beyond a ragged chunk's length: those are the next
+// sequence's rows, or zero fill past the end of the tensor, and the kernels select them away.  This holds when
+// the sequences of the chunk tables cover all `rows` token rows, which is a precondition of this entry point.)
+// No clearing pass is run.  Two
 // calls whose kernels can overlap on one GPU (different streams or different threads) race on the array
 // and give wrong results: keep calls on a device in stream order.
 //
@@ -30,7 +33,25 @@ static __device__ __align__(256) unsigned char g_static_scratch[B200GDN_STATIC_S
 
 constexpr int kMaxDevices = 64;
 void* g_scratch_addr[kMaxDevices] = {};
+void* g_scratch_ctx[kMaxDevices] = {};   // the CUDA context the cached address belongs to
 std::mutex g_scratch_mutex;
+
+// The current driver context (a second context on the same device has its own copy of the library image and
+// therefore its own array); nullptr when the driver entry point cannot be resolved.
+void* current_context() {
+  typedef int (*CtxFn)(void**);
+  static CtxFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuCtxGetCurrent", &p, cudaEnableDefault, &q) == cudaSuccess) fn = reinterpret_cast<CtxFn>(p);
+    tried = true;
+  }
+  void* ctx = nullptr;
+  if (fn == nullptr || fn(&ctx) != 0) return nullptr;
+  return ctx;
+}
 
 // Device address of the scratch array on the current device; looked up once per device.
 int static_scratch_base(unsigned char** base) {
@@ -40,13 +61,15 @@ int static_scratch_base(unsigned char** base) {
   if (dev < 0 || dev >= kMaxDevices)
     return gdn::set_error(B200GDN_ERR_UNSUPPORTED, "chunk_fwd_static: device index %d outside [0,%d)", dev, kMaxDevices);
   std::lock_guard<std::mutex> lock(g_scratch_mutex);
-  if (g_scratch_addr[dev] == nullptr) {
+  void* ctx = current_context();
+  if (g_scratch_addr[dev] == nullptr || g_scratch_ctx[dev] != ctx) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_static_scratch);
     if (e != cudaSuccess || p == nullptr)
       return gdn::set_error(B200GDN_ERR_CUDA, "chunk_fwd_static: cudaGetSymbolAddress on device %d: %s", dev,
                             cudaGetErrorString(e));
     g_scratch_addr[dev] = p;
+    g_scratch_ctx[dev] = ctx;
   }
   *base = static_cast<unsigned char*>(g_scratch_addr[dev]);
   return 0;
@@ -59,6 +82,7 @@ inline size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255);
 extern "C" int b200gdn_chunk_fwd_static(const b200gdn_chunk_args* a, void* stream) {
   using namespace gdn;
   const char* who = "chunk_fwd_static";
+  reset_launch_count();
   if (a == nullptr) return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: args is NULL", who);
   if (a->struct_bytes != (int32_t)sizeof(b200gdn_chunk_args))
     return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: struct_bytes %d != %zu (ABI mismatch)", who, a->struct_bytes,

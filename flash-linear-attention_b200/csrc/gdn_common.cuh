@@ -94,6 +94,7 @@ int bwd_dqk_timeout_flag();
 int bwd_wy_timeout_flag();
 int set_error(int code, const char* fmt, ...);
 int check_launch(const char* what);
+void reset_launch_count();
 
 template <typename Kern>
 int ensure_smem(Kern kern, size_t bytes) {

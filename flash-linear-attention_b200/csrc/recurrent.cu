@@ -31,6 +31,20 @@ __device__ __forceinline__ void st_elem(void* p, int64_t i, int dtype, float x) 
 }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
+// Slot of the state pool that sequence n uses.  With a pool (state_indices) and a known pool size, an index outside
+// [0, n_slots) marks a padding sequence (serving engines use -1): it reads slot 0, its output is meaningless and its
+// state is not written back (`*writeback` = false), so no access leaves the pool.
+__device__ __forceinline__ int64_t state_slot(const b200gdn_recurrent_args& a, int n, bool* writeback) {
+  *writeback = true;
+  if (a.state_indices == nullptr) return n;
+  const int64_t slot = a.state_indices[n];
+  if (a.n_slots > 0 && (slot < 0 || slot >= a.n_slots)) {
+    *writeback = false;
+    return 0;
+  }
+  return slot;
+}
+
 template <int DK, bool VFIRST>
 __global__ void __launch_bounds__(NTHREADS, (DK <= 128 ? 8 : 4)) recurrent_kernel(const b200gdn_recurrent_args a) {
   __shared__ __align__(16) float qs[DK];
@@ -58,9 +72,10 @@ __global__ void __launch_bounds__(NTHREADS, (DK <= 128 ? 8 : 4)) recurrent_kerne
   constexpr int NF = DK / 16;  // float4 per lane in both layouts
   float4 st[NF];
   const int l8 = lane & 7, lg = lane >> 3;
-  const int64_t slot = a.state_indices ? a.state_indices[n] : n;   // which state of the pool this sequence uses
+  bool writeback;
+  const int64_t slot = state_slot(a, n, &writeback);   // which state of the pool this sequence uses
   const float* h0 = a.h0 ? a.h0 + (slot * a.HV + hv) * DK * DV : nullptr;
-  float* ht = a.ht ? a.ht + (slot * a.HV + hv) * DK * DV : nullptr;
+  float* ht = (a.ht && writeback) ? a.ht + (slot * a.HV + hv) * DK * DV : nullptr;
   auto st_index = [&](int i) -> int64_t {
     if (!VFIRST) {
       int r = warp * (DK / 4) + 4 * i + lg;
@@ -232,9 +247,10 @@ __global__ void __launch_bounds__(256, 2) recurrent_rows_kernel(const b200gdn_re
     len = a.T;
   }
   float4 st[RW];
-  const int64_t slot = a.state_indices ? a.state_indices[n] : n;   // which state of the pool this sequence uses
+  bool writeback;
+  const int64_t slot = state_slot(a, n, &writeback);   // which state of the pool this sequence uses
   const float* h0 = a.h0 ? a.h0 + (slot * a.HV + hv) * DK * DV : nullptr;
-  float* ht = a.ht ? a.ht + (slot * a.HV + hv) * DK * DV : nullptr;
+  float* ht = (a.ht && writeback) ? a.ht + (slot * a.HV + hv) * DK * DV : nullptr;
   const int col = 4 * lane, r0 = warp * RW;
 #pragma unroll
   for (int i = 0; i < RW; ++i)
@@ -376,13 +392,16 @@ __global__ void __launch_bounds__(288, 1) decode_stream_kernel(const b200gdn_rec
         if (jj >= NS) {
           const int item = (int)blockIdx.x + (jj - NS) * (int)gridDim.x;
           if (!tc5::mbar_wait(&done[s], ((jj - NS) / NS) & 1)) { failed = true; break; }
-          const int64_t slot = a.state_indices ? a.state_indices[item / a.HV] : item / a.HV;
-          float* ht = a.ht + (slot * a.HV + item % a.HV) * DK * DV;
-          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(ht), "r"(tc5::smem_addr(stg)),
-                       "r"((uint32_t)S::state_bytes)
-                       : "memory");
-          tma::store_commit();
-          tma::store_wait_read<0>();   // the stage may be refilled once the copy has read it
+          bool writeback;
+          const int64_t slot = state_slot(a, item / a.HV, &writeback);
+          if (writeback) {
+            float* ht = a.ht + (slot * a.HV + item % a.HV) * DK * DV;
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(ht), "r"(tc5::smem_addr(stg)),
+                         "r"((uint32_t)S::state_bytes)
+                         : "memory");
+            tma::store_commit();
+            tma::store_wait_read<0>();   // the stage may be refilled once the copy has read it
+          }
         }
         if (jj < n_local) {
           const int item = (int)blockIdx.x + jj * (int)gridDim.x;
@@ -403,7 +422,8 @@ __global__ void __launch_bounds__(288, 1) decode_stream_kernel(const b200gdn_rec
           sc[1] = bb;
           const uint32_t qk_bytes = (uint32_t)(DK * esz), v_bytes = (uint32_t)(DV * esz);
           tc5::mbar_expect_tx(&full[s], (uint32_t)S::state_bytes + 2 * qk_bytes + v_bytes);
-          const int64_t slot = a.state_indices ? a.state_indices[n] : n;
+          bool writeback_unused;
+          const int64_t slot = state_slot(a, n, &writeback_unused);
           tma::load_1d(stg, a.h0 + (slot * a.HV + hv) * DK * DV, (uint32_t)S::state_bytes, &full[s]);
           tma::load_1d(stg + S::o_q, static_cast<const char*>(a.q) + (row * a.H + hq) * DK * esz, qk_bytes, &full[s]);
           tma::load_1d(stg + S::o_k, static_cast<const char*>(a.k) + (row * a.H + hq) * DK * esz, qk_bytes, &full[s]);

@@ -42,8 +42,6 @@ struct ScanBwdMaps {
   CUtensorMap q, k, w, d_o, dv2, dh;
 };
 
-__device__ __forceinline__ void bar_epi_b() { asm volatile("bar.sync 1, %0;\n" ::"n"(NEPI) : "memory"); }
-
 template <int DK, int DV, int NSTAGE>
 __global__ void __launch_bounds__(NTHREADS) scan_bwd_kernel(const b200gdn_chunk_args a, const __grid_constant__ ScanBwdMaps maps) {
   using S = ScanBwdSmem<DK, NSTAGE>;
@@ -113,7 +111,7 @@ __global__ void __launch_bounds__(NTHREADS) scan_bwd_kernel(const b200gdn_chunk_
   } else if (warp == WARP_MMA) {
     // ================= MMA thread =================
     if (lane == 0) {
-      ChunkMeta cm_next = load_chunk_meta(a.chunk_meta, nc > 0 ? c_last : c_first);
+      ChunkMeta cm_next = nc > 0 ? load_chunk_meta(a.chunk_meta, c_last) : ChunkMeta{0, 0, 0, 0};   // an empty sequence owns no chunk
       for (int ic = 0; ic < nc; ++ic) {
         const int c = c_last - ic, s = ic % NSTAGE, buf = ic & 1;
         const ChunkMeta cm = cm_next;
@@ -255,17 +253,15 @@ __global__ void __launch_bounds__(NTHREADS) scan_bwd_kernel(const b200gdn_chunk_
       __syncwarp();
       if (lane == 0) tc5::mbar_arrive(vt_ready);
 
-      if (cm.len < BT) {   // ragged chunk: predicated stores of the valid dv2 rows
-        bar_epi_b();
-        __nv_bfloat16* vg = reinterpret_cast<__nv_bfloat16*>(a.dv2) + ((int64_t)cm.row * a.HV + hv) * DV + v0;
-        for (int idx = tid; idx < BT * 8; idx += NEPI) {
-          const int r = idx >> 3, ch = idx & 7;
-          if (r < cm.len) {
-            uint4 val;
-            const uint32_t addr = swz_chunk_addr(d2_tile, BT, r, ch * 8);
-            asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];\n" : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w) : "r"(addr));
-            *reinterpret_cast<uint4*>(vg + (int64_t)r * a.HV * DV + ch * 8) = val;
-          }
+      if (cm.len < BT) {
+        // ragged chunk: every warp writes the valid rows of its own block straight from its registers (no CTA-wide
+        // barrier here: a warp whose bounded wait expired has left the loop and would never arrive at one)
+        __nv_bfloat16* vg = reinterpret_cast<__nv_bfloat16*>(a.dv2) + ((int64_t)cm.row * a.HV + hv) * DV + v0 + 32 * hc + 2 * t;
+        const int64_t vstride = (int64_t)a.HV * DV;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (r_lo < cm.len) *reinterpret_cast<uint32_t*>(vg + r_lo * vstride + 8 * i) = fs_d2.lo[i];
+          if (r_hi < cm.len) *reinterpret_cast<uint32_t*>(vg + r_hi * vstride + 8 * i) = fs_d2.hi[i];
         }
       }
     }

@@ -50,8 +50,6 @@ struct ScanFwdMaps {
   CUtensorMap w, k, u, h, vn;
 };
 
-__device__ __forceinline__ void bar_epi() { asm volatile("bar.sync 1, %0;\n" ::"n"(NEPI) : "memory"); }
-
 template <int DK, int DV, int NSTAGE>
 __global__ void __launch_bounds__(NTHREADS) scan_fwd_kernel(const b200gdn_chunk_args a, const __grid_constant__ ScanFwdMaps maps) {
   using S = ScanFwdSmem<DK, NSTAGE>;
@@ -119,7 +117,7 @@ __global__ void __launch_bounds__(NTHREADS) scan_fwd_kernel(const b200gdn_chunk_
     // ================= MMA warp: one thread issues the contractions and the TMA stores =================
     if (lane == 0) {
       const uint32_t vt_addr = tc5::smem_addr(smem + S::o_vt);
-      ChunkMeta cm_next = load_chunk_meta(a.chunk_meta, c_first);
+      ChunkMeta cm_next = nc > 0 ? load_chunk_meta(a.chunk_meta, c_first) : ChunkMeta{0, 0, 0, 0};   // an empty sequence owns no chunk
       for (int ic = 0; ic < nc; ++ic) {
         const int c = c_first + ic, s = ic % NSTAGE, buf = ic & 1;
         const ChunkMeta cm = cm_next;
@@ -231,8 +229,10 @@ __global__ void __launch_bounds__(NTHREADS) scan_fwd_kernel(const b200gdn_chunk_
           u_hi[i] = has_u ? fu.hi2(i) : make_float2(0.f, 0.f);
         }
       }
-      const float e_lo = r_lo < cm.len ? fast_exp2(glast - gs[r_lo]) : 0.f;   // rows past the chunk's end contribute nothing
-      const float e_hi = r_hi < cm.len ? fast_exp2(glast - gs[r_hi]) : 0.f;
+      // rows past the chunk's end contribute nothing: they are selected away (not multiplied by zero, their tiles may
+      // hold anything, NaN bit patterns included)
+      const bool ok_lo = r_lo < cm.len, ok_hi = r_hi < cm.len;
+      const float e_lo = fast_exp2(glast - gs[r_lo]), e_hi = fast_exp2(glast - gs[r_hi]);
       if (!tc5::mbar_wait(v_ready, ic & 1)) { failed = true; break; }
       tc5::fence_after_sync();
       float acc[16];
@@ -241,8 +241,8 @@ __global__ void __launch_bounds__(NTHREADS) scan_fwd_kernel(const b200gdn_chunk_
       FragStore fs_vn, fs_vt;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float v00 = u_lo[i].x - acc[4 * i], v01 = u_lo[i].y - acc[4 * i + 1];
-        const float v10 = u_hi[i].x - acc[4 * i + 2], v11 = u_hi[i].y - acc[4 * i + 3];
+        const float v00 = ok_lo ? u_lo[i].x - acc[4 * i] : 0.f, v01 = ok_lo ? u_lo[i].y - acc[4 * i + 1] : 0.f;
+        const float v10 = ok_hi ? u_hi[i].x - acc[4 * i + 2] : 0.f, v11 = ok_hi ? u_hi[i].y - acc[4 * i + 3] : 0.f;
         fs_vn.set(i, v00, v01, v10, v11);
         fs_vt.set(i, v00 * e_lo, v01 * e_lo, v10 * e_hi, v11 * e_hi);
       }
@@ -253,17 +253,15 @@ __global__ void __launch_bounds__(NTHREADS) scan_fwd_kernel(const b200gdn_chunk_
       __syncwarp();
       if (lane == 0) tc5::mbar_arrive(vt_ready);
 
-      if (a.v_new != nullptr && cm.len < BT) {   // ragged chunk: predicated stores of the valid rows
-        bar_epi();
-        __nv_bfloat16* vg = reinterpret_cast<__nv_bfloat16*>(a.v_new) + ((int64_t)cm.row * a.HV + hv) * DV + v0;
-        for (int idx = tid; idx < BT * 8; idx += NEPI) {
-          const int r = idx >> 3, ch = idx & 7;
-          if (r < cm.len) {
-            uint4 val;
-            const uint32_t addr = swz_chunk_addr(vn_tile, BT, r, ch * 8);
-            asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];\n" : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w) : "r"(addr));
-            *reinterpret_cast<uint4*>(vg + (int64_t)r * a.HV * DV + ch * 8) = val;
-          }
+      if (a.v_new != nullptr && cm.len < BT) {
+        // ragged chunk: every warp writes the valid rows of its own block straight from its registers (no CTA-wide
+        // barrier here: a warp whose bounded wait expired has left the loop and would never arrive at one)
+        __nv_bfloat16* vg = reinterpret_cast<__nv_bfloat16*>(a.v_new) + ((int64_t)cm.row * a.HV + hv) * DV + v0 + 32 * hc + 2 * t;
+        const int64_t vstride = (int64_t)a.HV * DV;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (r_lo < cm.len) *reinterpret_cast<uint32_t*>(vg + r_lo * vstride + 8 * i) = fs_vn.lo[i];
+          if (r_hi < cm.len) *reinterpret_cast<uint32_t*>(vg + r_hi * vstride + 8 * i) = fs_vn.hi[i];
         }
       }
     }

@@ -19,6 +19,11 @@
  *    host builds once per shape (fla/ops/utils/index.py:155-172 computes the same information):
  *      chunk_meta[n_chunks][4] = { sequence id, first row, valid rows (1..64), chunk index inside its sequence }
  *      seq_meta  [n_seq][2]    = { first chunk (global index), number of chunks }
+ *  - the kernels move whole 64-row tiles: rows of a tile that lie past the end of a sequence are another
+ *    sequence's rows or zero fill past the end of the tensor, and are selected away on chip.  Token rows that NO
+ *    sequence covers (padding before the first or after the last sequence) are never written; when such rows
+ *    exist the caller zero-fills the saved / workspace tensors once (w, u, v_new, dv2, A) and keeps the padding
+ *    rows of q, k, v, do finite, because a tile load may bring them next to valid rows.
  */
 #ifndef B200GDN_H_
 #define B200GDN_H_
@@ -124,6 +129,7 @@ int b200gdn_chunk_fwd(const b200gdn_chunk_args* args, void* stream);
  * Limit: align256(n_chunks*HV*256) + align256(rows*HV*128) + align256(rows*HV*K*2) + 2*align256(rows*HV*V*2)
  *        + align256(n_chunks*HV*K*V*2)  <=  B200GDN_STATIC_SCRATCH_BYTES
  * (e.g. 2048 tokens x 16 heads at K = V = 128); larger problems return B200GDN_ERR_TOO_LARGE and launch nothing.
+ * Precondition (as for every chunk entry point): the sequences of the chunk tables cover all `rows` token rows.
  * Makes no allocating call.  The first call on each device looks up the array's address and should come before
  * any stream capture.  All calls on a device share the array (it keeps the previous call's contents; no stage
  * needs it cleared), so calls that can overlap on the GPU race: issue them in stream order. */
@@ -157,6 +163,9 @@ typedef struct b200gdn_recurrent_args {
                                     pools of state slots [n_slots,HV,K,V] and sequence n uses slot state_indices[n]
                                     (the slots of one call must be distinct), as a serving engine's state cache
                                     addresses them; without it sequence n uses slot n */
+  int32_t n_slots;               /* slots in the pool (with state_indices); an index outside [0, n_slots) marks a
+                                    padding sequence: its state is neither taken from its slot nor written back and its
+                                    output row is meaningless.  0 = unknown, indices are then trusted */
 } b200gdn_recurrent_args;
 
 #define B200GDN_REC_L2NORM 1u         /* q, k <- x * rsqrt(sum x^2 + 1e-6) */

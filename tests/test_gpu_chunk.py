@@ -417,3 +417,171 @@ def test_fused_gate_and_beta_equal_the_separate_passes():
         assert torch.equal(a[i], b[i]), i            # dq, dk, dv do not pass through the activations
     for i, name in ((4, 'dg'), (5, 'dbeta'), (6, 'dA_log'), (7, 'ddt_bias')):
         O.assert_close(name, b[i].float().cpu(), a[i].float().cpu(), 1e-5)
+
+
+def _record(name, ratios):
+    """Keep the measured err-ratios of the full-size checks next to the other outputs of a GPU run (when that
+    folder exists); the assertions themselves do not depend on it."""
+    import json
+    out = os.path.join(os.path.dirname(__file__), '..', 'gpurun_out')
+    if os.path.isdir(out):
+        with open(os.path.join(out, f'parity_{name}.json'), 'w') as f:
+            json.dump({k: float(v) for k, v in ratios.items()}, f, indent=1)
+
+
+# err-ratio bounds of the reference's own tests (tests/ops/test_gdn.py:108-200)
+REF_TOL = dict(o=0.005, ht=0.005, dq=0.008, dk=0.008, dv=0.008, dh0=0.008, dg=0.02, dbeta=0.02)
+
+
+def test_full_size_backward_against_oracle_one_head():
+    """Headline shape B4 T4096 H16 K=V=128, forward AND backward (with an initial state and a gradient on the final
+    state): heads and batch rows are independent, so one (batch row, head) slice of the full-size run is compared
+    with the fp64 token-by-token oracle and its autograd gradients over the full 4096 tokens."""
+    from b200gdn import chunk_gated_delta_rule
+    dev = 'cuda'
+    B, T, H, K = 4, 4096, 16, 128
+    gen = torch.Generator().manual_seed(0)
+    nrm = torch.nn.functional.normalize
+    q = nrm(torch.randn(B, T, H, K, generator=gen), dim=-1).to(torch.bfloat16)
+    k = nrm(torch.randn(B, T, H, K, generator=gen), dim=-1).to(torch.bfloat16)
+    v = torch.randn(B, T, H, K, generator=gen).to(torch.bfloat16)
+    g = torch.nn.functional.logsigmoid(torch.randn(B, T, H, generator=gen))
+    beta = torch.sigmoid(torch.randn(B, T, H, generator=gen))
+    h0 = torch.randn(B, H, K, K, generator=gen) * 0.1
+    do = torch.randn(B, T, H, K, generator=gen).to(torch.bfloat16)
+    dht = torch.randn(B, H, K, K, generator=gen) * 0.1
+    leaves = [x.to(dev).requires_grad_(True) for x in (q, k, v, g, beta, h0)]
+    o, ht = chunk_gated_delta_rule(*leaves[:5], initial_state=leaves[5], output_final_state=True)
+    torch.autograd.backward([o, ht], [do.to(dev), dht.to(dev)])
+    b, h = 2, 5
+    sl = lambda x: x[b:b + 1, :, h:h + 1].float()
+    ro, rht, rg = O.naive_with_grads(sl(q), sl(k), sl(v), sl(g), sl(beta), K ** -0.5, h0[b:b + 1, h:h + 1],
+                                     sl(do), dht[b:b + 1, h:h + 1])
+    got = dict(o=o[b:b + 1, :, h:h + 1].float().cpu(), ht=ht[b:b + 1, h:h + 1].cpu())
+    for n, leaf in zip(('dq', 'dk', 'dv', 'dg', 'dbeta'), leaves[:5]):
+        got[n] = leaf.grad[b:b + 1, :, h:h + 1].float().cpu()
+    got['dh0'] = leaves[5].grad[b:b + 1, h:h + 1].cpu()
+    want = dict(o=ro, ht=rht, **rg)
+    ratios = {n: O.err_ratio(want[n].float(), got[n]) for n in REF_TOL}
+    _record('headline_one_head', ratios)
+    for n, tol in REF_TOL.items():
+        O.assert_close(f'headline (b={b}, h={h}) {n}', want[n].float(), got[n], tol)
+
+
+def test_full_size_varlen_gva_backward_against_oracle_one_sequence():
+    """Packed GVA configuration at full size (16 q/k heads, 32 value heads, 16 sequences, 65536 tokens): one
+    sequence and one value head of the packed forward + backward against the fp64 oracle over that whole sequence
+    (outputs, final state, all gradients incl. dh0).  dq / dk of a q/k head sum over its group of value heads, so
+    they are compared on a run whose other value head of the group receives a zero output gradient."""
+    from b200gdn import chunk_gated_delta_rule
+    dev = 'cuda'
+    cu = O.random_cu_seqlens(16, 65536, 256, 8192, seed=0)
+    H, HV, K, V, total = 16, 32, 128, 128, 65536
+    gen = torch.Generator().manual_seed(1)
+    nrm = torch.nn.functional.normalize
+    q = nrm(torch.randn(1, total, H, K, generator=gen), dim=-1).to(torch.bfloat16)
+    k = nrm(torch.randn(1, total, H, K, generator=gen), dim=-1).to(torch.bfloat16)
+    v = torch.randn(1, total, HV, V, generator=gen).to(torch.bfloat16)
+    g = torch.nn.functional.logsigmoid(torch.randn(1, total, HV, generator=gen))
+    beta = torch.sigmoid(torch.randn(1, total, HV, generator=gen))
+    h0 = torch.randn(16, HV, K, V, generator=gen) * 0.1
+    do = torch.randn(1, total, HV, V, generator=gen).to(torch.bfloat16)
+    dht = torch.randn(16, HV, K, V, generator=gen) * 0.1
+    # the shortest sequence that still spans several chunks keeps the oracle's run time in seconds
+    lens = [cu[i + 1] - cu[i] for i in range(16)]
+    n = min(range(16), key=lambda i: lens[i])
+    s, e = cu[n], cu[n + 1]
+    hv = 11
+    hq = hv // (HV // H)
+    other = hq * (HV // H) + (1 - hv % (HV // H))
+    do = do.clone()
+    do[:, s:e, other] = 0          # the group's other value head contributes nothing to dq / dk of this sequence
+    dht = dht.clone()
+    dht[n, other] = 0
+    leaves = [x.to(dev).requires_grad_(True) for x in (q, k, v, g, beta, h0)]
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=dev)
+    o, ht = chunk_gated_delta_rule(*leaves[:5], initial_state=leaves[5], output_final_state=True, cu_seqlens=cu_t)
+    torch.autograd.backward([o, ht], [do.to(dev), dht.to(dev)])
+    ro, rht, rg = O.naive_with_grads(q[:, s:e, hq:hq + 1].float(), k[:, s:e, hq:hq + 1].float(), v[:, s:e, hv:hv + 1].float(),
+                                     g[:, s:e, hv:hv + 1], beta[:, s:e, hv:hv + 1], K ** -0.5, h0[n:n + 1, hv:hv + 1],
+                                     do[:, s:e, hv:hv + 1].float(), dht[n:n + 1, hv:hv + 1])
+    got = dict(o=o[:, s:e, hv:hv + 1].float().cpu(), ht=ht[n:n + 1, hv:hv + 1].cpu(),
+               dq=leaves[0].grad[:, s:e, hq:hq + 1].float().cpu(), dk=leaves[1].grad[:, s:e, hq:hq + 1].float().cpu(),
+               dv=leaves[2].grad[:, s:e, hv:hv + 1].float().cpu(), dg=leaves[3].grad[:, s:e, hv:hv + 1].cpu(),
+               dbeta=leaves[4].grad[:, s:e, hv:hv + 1].cpu(), dh0=leaves[5].grad[n:n + 1, hv:hv + 1].cpu())
+    want = dict(o=ro, ht=rht, **rg)
+    ratios = {nme: O.err_ratio(want[nme].float(), got[nme]) for nme in REF_TOL}
+    ratios['sequence_length'] = e - s
+    _record('varlen_gva_one_sequence', ratios)
+    for nme, tol in REF_TOL.items():
+        O.assert_close(f'packed GVA (sequence {n}, value head {hv}) {nme}', want[nme].float(), got[nme], tol)
+
+
+def test_padding_rows_outside_cu_seqlens():
+    """A packed buffer with rows before cu_seqlens[0] and after cu_seqlens[-1] (a serving buffer padded to a fixed
+    size): the valid rows must equal the run on the unpadded buffer bit for bit, and nothing may turn NaN, although
+    the kernels load whole 64-row tiles that reach into the padding."""
+    lead, trail = 70, 45
+    cu = [0, 37, 101, 165, 300]
+    q, k, v, g, beta, do = _inputs(1, 300, 2, 4, 128, 128, seed=11)
+    cu_t = torch.tensor(cu, dtype=torch.int32, device='cuda')
+    ref = _fwd_bwd(q, k, v, g, beta, do, cu_seqlens=cu_t)
+
+    def pad(x):
+        shape = list(x.shape)
+        a, b = shape.copy(), shape.copy()
+        a[1], b[1] = lead, trail
+        # finite but large padding values: they must never reach a valid row
+        return torch.cat([torch.full(a, 3.0, dtype=x.dtype, device=x.device), x,
+                          torch.full(b, -2.0, dtype=x.dtype, device=x.device)], 1)
+    cu_p = torch.tensor([c + lead for c in cu], dtype=torch.int32, device='cuda')
+    out = _fwd_bwd(pad(q), pad(k), pad(v), pad(g), pad(beta), pad(do), cu_seqlens=cu_p)
+    for nme, a, p in zip(('o', 'ht', 'dq', 'dk', 'dv', 'dg', 'dbeta'), ref, out):
+        assert not torch.isnan(p).any(), nme
+        got = p if nme == 'ht' else p[:, lead:lead + 300]
+        assert torch.equal(a, got), f'{nme} of the valid rows changed with padding around them'
+
+
+def test_trailing_empty_sequence():
+    """cu_seqlens ending in an empty sequence (and one in the middle): it owns no chunk, its final state is its
+    initial state and its dh0 is the gradient of the final state."""
+    from b200gdn import chunk_gated_delta_rule
+    dev = 'cuda'
+    cu = [0, 100, 100, 230, 230]
+    d = O.make_inputs(1, 230, 2, 2, 128, 128, seed=13, cu_seqlens=cu)
+    leaves = [d[n].to(dev).to(torch.bfloat16).requires_grad_(True) for n in ('q', 'k', 'v')]
+    leaves += [d[n].to(dev).requires_grad_(True) for n in ('g', 'beta', 'h0')]
+    o, ht = chunk_gated_delta_rule(*leaves[:5], initial_state=leaves[5], output_final_state=True,
+                                   cu_seqlens=torch.tensor(cu, device=dev))
+    torch.autograd.backward([o, ht], [d['do'].to(dev).to(torch.bfloat16), d['dht'].to(dev)])
+    ro, rht, rg = O.naive_with_grads(*(d[n].to(torch.bfloat16).float() for n in ('q', 'k', 'v')), d['g'], d['beta'],
+                                     128 ** -0.5, d['h0'], d['do'].to(torch.bfloat16).float(), d['dht'], cu_seqlens=cu)
+    O.assert_close('o', ro.float(), o.float().cpu(), 0.005)
+    O.assert_close('ht', rht.float(), ht.cpu(), 0.005)
+    assert torch.equal(ht[1].cpu(), d['h0'][1]) and torch.equal(ht[3].cpu(), d['h0'][3])
+    O.assert_close('dh0', rg['dh0'].float(), leaves[5].grad.cpu(), 0.008)
+    assert torch.equal(leaves[5].grad[3].cpu(), d['dht'][3])
+    import b200gdn
+    b200gdn.device_status()
+
+
+def test_fp32_and_fp16_inputs_are_rounded_to_bf16_and_keep_their_dtype():
+    """q, k, v in fp32 / fp16: the result is the bf16 computation on the rounded inputs (documented), returned in
+    the caller's dtype, gradients in each input's dtype."""
+    from b200gdn import chunk_gated_delta_rule
+    dev = 'cuda'
+    d = O.make_inputs(2, 130, 2, 2, 128, 128, seed=17)
+    for dt in (torch.float32, torch.float16):
+        x = [d[n].to(dev).to(dt).requires_grad_(True) for n in ('q', 'k', 'v')]
+        gb = [d[n].to(dev).requires_grad_(True) for n in ('g', 'beta')]
+        o, _ = chunk_gated_delta_rule(*x, *gb, use_qk_l2norm_in_kernel=(dt == torch.float32))
+        o.float().square().sum().backward()
+        assert o.dtype == dt and all(t.grad.dtype == dt for t in x)
+        y = [t.detach().to(torch.bfloat16).requires_grad_(True) for t in x]
+        gb2 = [t.detach().clone().requires_grad_(True) for t in gb]
+        o2, _ = chunk_gated_delta_rule(*y, *gb2, use_qk_l2norm_in_kernel=(dt == torch.float32))
+        assert o2.dtype == torch.bfloat16
+        if dt == torch.float16:   # without the norm pass both runs see identical bf16 operands
+            assert torch.equal(o.float(), o2.float())
+        else:
+            O.assert_close('o fp32 inputs vs bf16 inputs', o2.float().cpu(), o.float().cpu(), 0.005)

@@ -135,3 +135,68 @@ def test_exchange_and_fold_two_ranks_gloo():
     assert (pre0, post0, pre1, post1) == (0, 1, 1, 0)
     assert x0 is None
     assert torch.allclose(x1, g0[0, :, :, 4:])      # one predecessor: its h_ext
+
+
+def test_backend_verifier_serves_bf16_only():
+    """fp16 / fp32 q, k, v are declined so that the dispatcher falls through to the reference's own path, which
+    keeps their precision (the kernels here compute on bf16 operands)."""
+    be = B200GDNBackend()
+
+    class FakeCuda(torch.Tensor):
+        is_cuda = True
+    g = torch.zeros(1, 64, 2)
+    for dt, want in ((torch.bfloat16, True), (torch.float16, False), (torch.float32, False)):
+        q = torch.zeros(1, 64, 2, 128, dtype=dt).as_subclass(FakeCuda)
+        ok, why = be.chunk_gated_delta_rule_verifier(q, q, q, g, g)
+        assert ok is want, (dt, why)
+        if not want:
+            assert 'bf16' in why
+    q = torch.zeros(1, 64, 2, 96, dtype=torch.bfloat16).as_subclass(FakeCuda)
+    ok, why = be.chunk_gated_delta_rule_verifier(q, q, q, g, g)
+    assert not ok and 'not built' in why
+
+
+REF_INSTALL = os.path.join(os.path.dirname(__file__), '..', 'baseline', '_ref')
+
+_INSTALL_PROBE = r'''
+import sys
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[2])
+import fla
+import fla.layers.gated_deltanet as layer_mod
+import fla.ops.gated_delta_rule as op_mod
+from fla.ops.gated_delta_rule.backends import gdr_registry
+import b200gdn
+from b200gdn.backend import B200GDNBackend
+stock_layer, stock_op = layer_mod.fused_recurrent_gated_delta_rule, op_mod.fused_recurrent_gated_delta_rule
+gdr_registry._ensure_initialized() if hasattr(gdr_registry, '_ensure_initialized') else None
+before = set(gdr_registry._backends)
+assert b200gdn.install() is True
+assert 'b200_gdn' in gdr_registry._backends and isinstance(gdr_registry._backends['b200_gdn'], B200GDNBackend)
+assert layer_mod.fused_recurrent_gated_delta_rule is b200gdn.fused_recurrent_gated_delta_rule
+assert op_mod.fused_recurrent_gated_delta_rule is b200gdn.fused_recurrent_gated_delta_rule
+# without a B200 the backend reports itself unavailable, so the registry must not select it here
+import torch
+if not torch.cuda.is_available():
+    assert not B200GDNBackend.is_available()
+b200gdn.install()   # idempotent: the saved stock functions survive a second call
+b200gdn.uninstall()
+assert set(gdr_registry._backends) == before
+assert layer_mod.fused_recurrent_gated_delta_rule is stock_layer
+assert op_mod.fused_recurrent_gated_delta_rule is stock_op
+b200gdn.uninstall()  # and a second uninstall is harmless
+print('install-ok', fla.__version__)
+'''
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF_INSTALL, 'fla')), reason='no reference install under baseline/_ref')
+def test_install_and_uninstall_against_the_reference_registry():
+    """install() registers the backend in the reference's own registry object and rebinds the decode function in
+    the two modules that import it by name; uninstall() restores all three (fla/ops/backends/__init__.py:96-157,
+    fla/ops/gated_delta_rule/backends/__init__.py:14-17)."""
+    import subprocess
+    import sys
+    pkg = os.path.join(os.path.dirname(__file__), '..', 'flash-linear-attention_b200')
+    out = subprocess.run([sys.executable, '-c', _INSTALL_PROBE, os.path.abspath(pkg), os.path.abspath(REF_INSTALL)],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert 'install-ok 0.5.2' in out.stdout
