@@ -34,6 +34,7 @@ class ChunkArgs(C.Structure):
         ('dq', _p), ('dk', _p), ('dv', _p), ('dg', _p), ('dbeta', _p), ('dh0', _p),
         ('dh', _p), ('dv2', _p), ('dw', _p), ('dk_part', _p), ('dG', _p), ('dq_acc', _p),
         ('options', C.c_uint32), ('A_log', _p), ('dt_bias', _p), ('gate_partials', _p), ('dA_log', _p), ('ddt_bias', _p),
+        ('cp_M', _p), ('cp_dM', _p), ('qk', _p),
     ]
 
 
@@ -70,11 +71,19 @@ class AffineArgs(C.Structure):
     ]
 
 
+class FoldArgs(C.Structure):
+    _fields_ = [
+        ('struct_bytes', C.c_int32), ('HV', C.c_int32), ('K', C.c_int32), ('V', C.c_int32),
+        ('first', C.c_int32), ('count', C.c_int32), ('step', C.c_int32),
+        ('gathered', _p), ('out', _p),
+    ]
+
+
 EXPORTS = (
     'b200gdn_chunk_fwd', 'b200gdn_chunk_bwd', 'b200gdn_recurrent_fwd', 'b200gdn_affine_apply',
     'b200gdn_saved_bytes', 'b200gdn_bwd_workspace_bytes', 'b200gdn_last_launch_count',
     'b200gdn_abi_version', 'b200gdn_last_error', 'b200gdn_device_status', 'b200gdn_prep_fwd', 'b200gdn_prep_bwd',
-    'b200gdn_selftest_wait_expiry', 'b200gdn_chunk_fwd_static',
+    'b200gdn_selftest_wait_expiry', 'b200gdn_chunk_fwd_static', 'b200gdn_cp_fold',
 )
 
 _lib = None
@@ -99,7 +108,7 @@ def load():
                 '(or __graft_entry__.build()). There is no fallback path.')
         lib = C.CDLL(LIB_PATH)
         for name in ('b200gdn_chunk_fwd', 'b200gdn_chunk_bwd', 'b200gdn_recurrent_fwd', 'b200gdn_affine_apply',
-                     'b200gdn_prep_fwd', 'b200gdn_prep_bwd', 'b200gdn_chunk_fwd_static'):
+                     'b200gdn_prep_fwd', 'b200gdn_prep_bwd', 'b200gdn_chunk_fwd_static', 'b200gdn_cp_fold'):
             fn = getattr(lib, name)
             fn.restype = C.c_int
             fn.argtypes = [C.c_void_p, C.c_void_p]

@@ -189,18 +189,22 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             zero = not tables.covered
             o = (torch.zeros if zero else torch.empty)(B, T, HV, V, dtype=bf16, device=dev)
             ht = torch.empty(n_seq, HV, K, V, dtype=f32, device=dev) if output_final_state else None
-            gamma, A, w, u, v_new, h = carve(
-                dev, zero, ((n_chunks, HV, 64), f32), ((rows, HV, 64), bf16), ((rows, HV, K), bf16), ((rows, HV, V), bf16),
-                ((rows, HV, V), bf16), ((n_chunks, HV, K, V), bf16))
+            # h and v_new are only read by the backward pass: without one they are not even written
+            gamma, A, qk, w, u, v_new, h = carve(
+                dev, zero, ((n_chunks, HV, 64), f32), ((rows, HV, 64), bf16), ((rows, HV, 64), bf16), ((rows, HV, K), bf16),
+                ((rows, HV, V), bf16), ((rows, HV, V) if need_grad else (0,), bf16),
+                ((n_chunks, HV, K, V) if need_grad else (0,), bf16))
+            if not need_grad:
+                v_new = h = None
             a.g, a.beta, a.h0 = gf.data_ptr(), bf.data_ptr(), _lib.ptr(h0)
             A_log_f = A_log.detach().float().contiguous() if (options & _lib.PREP_GATE) else None
             bias_f = dt_bias.detach().float().contiguous() if (options & _lib.PREP_GATE) and dt_bias is not None else None
             a.options, a.A_log, a.dt_bias = options, _lib.ptr(A_log_f), _lib.ptr(bias_f)
             a.o, a.ht = o.data_ptr(), _lib.ptr(ht)
-            a.gamma, a.A, a.w, a.u, a.h, a.v_new = (x.data_ptr() for x in (gamma, A, w, u, h, v_new))
+            a.gamma, a.A, a.qk, a.w, a.u, a.h, a.v_new = (_lib.ptr(x) for x in (gamma, A, qk, w, u, h, v_new))
             _lib.call('b200gdn_chunk_fwd', a, _stream(qb))
         if need_grad:
-            ctx.save_for_backward(qb, kb, vb, bf, gamma, A, w, h, v_new, tables[0], tables[1],
+            ctx.save_for_backward(qb, kb, vb, bf, gamma, A, qk, w, h, v_new, tables[0], tables[1],
                                   gf if (options & _lib.PREP_GATE) else None, A_log_f, bias_f)
         ctx.meta = (scale, n_chunks, n_seq, initial_state is not None, in_dtypes, options,
                     None if A_log is None else A_log.dtype, None if dt_bias is None else dt_bias.dtype, zero)
@@ -208,7 +212,7 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, do, dht):
-        qb, kb, vb, bf, gamma, A, w, h, v_new, chunk_meta, seq_meta, gf, A_log_f, bias_f = ctx.saved_tensors
+        qb, kb, vb, bf, gamma, A, qk, w, h, v_new, chunk_meta, seq_meta, gf, A_log_f, bias_f = ctx.saved_tensors
         scale, n_chunks, n_seq, has_h0, in_dtypes, options, A_dtype, bias_dtype, zero = ctx.meta
         dev = qb.device
         dA_log = ddt_bias = None
@@ -239,7 +243,7 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
                 gate_partials = dA_log = None
             if not (gate and bias_f is not None):
                 ddt_bias = None
-            a.beta, a.gamma, a.A, a.w, a.h, a.v_new = (x.data_ptr() for x in (bf, gamma, A, w, h, v_new))
+            a.beta, a.gamma, a.A, a.qk, a.w, a.h, a.v_new = (x.data_ptr() for x in (bf, gamma, A, qk, w, h, v_new))
             a.d_o, a.dht = dob.data_ptr(), _lib.ptr(dhtf)
             a.dq, a.dk, a.dv, a.dg, a.dbeta, a.dh0 = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dg.data_ptr(), \
                 dbeta.data_ptr(), _lib.ptr(dh0)

@@ -125,7 +125,8 @@ def exchange(local: torch.Tensor, group) -> torch.Tensor:
 
 def fold_prefix(gathered: torch.Tensor, rank: int, num: int, K: int, forward: bool,
                 apply: Callable[[torch.Tensor, torch.Tensor, torch.Tensor, bool], torch.Tensor]) -> Optional[torch.Tensor]:
-    """Compose the affine maps of the ``num`` neighbouring ranks.
+    """Compose the affine maps of the ``num`` neighbouring ranks, one step per call of ``apply`` (the host-side
+    statement of the fold; on the GPU the whole chain is one launch, ``fold_on_device``).
 
     forward:  x = 0; for j = rank-num .. rank-1:  x = M_j x + h_j      (start state of the first local sequence)
     backward: x = 0; for j = rank+num .. rank+1:  x = M_j^T x + dh_j   (gradient at the end of the last local
@@ -144,7 +145,8 @@ def fold_prefix(gathered: torch.Tensor, rank: int, num: int, K: int, forward: bo
     return x
 
 
-def _affine_apply(M: torch.Tensor, x: torch.Tensor, b: torch.Tensor, transpose: bool) -> torch.Tensor:
+def affine_apply(M: torch.Tensor, x: torch.Tensor, b: Optional[torch.Tensor], transpose: bool = False) -> torch.Tensor:
+    """One fold step on the device, ``M x + b`` (``M^T x + b``) per head in fp32 (b200gdn_affine_apply)."""
     a = _lib.AffineArgs()
     a.HV, a.K, a.V = M.shape[0], M.shape[1], x.shape[2]
     a.transpose_m = int(transpose)
@@ -154,13 +156,55 @@ def _affine_apply(M: torch.Tensor, x: torch.Tensor, b: torch.Tensor, transpose: 
     return out
 
 
+def fold_on_device(gathered: torch.Tensor, rank: int, num: int, K: int, forward: bool, out: torch.Tensor) -> None:
+    """The same fold in one kernel launch (b200gdn_cp_fold), written into ``out [HV,K,V]``."""
+    a = _lib.FoldArgs()
+    a.HV, a.K, a.V = gathered.shape[1], K, gathered.shape[3] - K
+    a.first, a.count, a.step = (rank - num, num, 1) if forward else (rank + num, num, -1)
+    a.gathered, a.out = gathered.data_ptr(), out.data_ptr()
+    _lib.call('b200gdn_cp_fold', a, torch.cuda.current_stream(gathered.device).cuda_stream)
+
+
+# Optional phase timing for benchmarks: set PHASE_TIMES = {} and every forward / backward appends CUDA-event pairs
+# per phase; collect_phase_times() synchronises and returns the mean milliseconds per phase and call.
+PHASE_TIMES = None
+
+
+class _Phase:
+    def __init__(self, name, dev):
+        self.name, self.dev = name, dev
+
+    def __enter__(self):
+        if PHASE_TIMES is not None:
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e0.record(torch.cuda.current_stream(self.dev))
+
+    def __exit__(self, *exc):
+        if PHASE_TIMES is not None:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record(torch.cuda.current_stream(self.dev))
+            PHASE_TIMES.setdefault(self.name, []).append((self.e0, e1))
+
+
+def collect_phase_times():
+    if not PHASE_TIMES:
+        return None
+    torch.cuda.synchronize()
+    return {n: sum(a.elapsed_time(b) for a, b in ev) / len(ev) for n, ev in PHASE_TIMES.items()}
+
+
 class ChunkGatedDeltaRuleCPFunction(torch.autograd.Function):
     """Forward and backward of the op on one rank's shard, with the prefix exchange in between the
-    intra-chunk stage and the scan (fla/ops/gated_delta_rule/chunk.py:82-93, 183-200)."""
+    intra-chunk stage and the scan (fla/ops/gated_delta_rule/chunk.py:82-93, 183-200).
+
+    Per direction: ONE pre-scan launch gives the (h_ext, M) pair of the rank's boundary sequence (value slices and
+    transition-matrix slices side by side in the grid, as the reference's pre-process kernel does,
+    fla/ops/cp/chunk_delta_h.py:41-315), one all-gather exchanges the pairs, ONE launch folds the pairs of the
+    neighbouring ranks, and the regular (fused) scan runs from the folded state."""
 
     @staticmethod
     def forward(ctx, q, k, v, g, beta, scale, cp_context):
-        from .chunk import new_chunk_args, _stream
+        from .chunk import carve, new_chunk_args, _stream
         in_dtypes = (q.dtype, k.dtype, v.dtype, g.dtype, beta.dtype)
         dev = q.device
         group = cp_context.group
@@ -173,63 +217,56 @@ class ChunkGatedDeltaRuleCPFunction(torch.autograd.Function):
             tables = tables_for(B, T, cp_context.cu_seqlens, cp_context.cu_seqlens_cpu, dev)
             chunk_meta, seq_meta, (n_chunks, n_seq) = tables
             rows = B * T
-            bf16 = dict(dtype=torch.bfloat16, device=dev)
-            f32 = dict(dtype=torch.float32, device=dev)
-            o = torch.empty(B, T, HV, V, **bf16)
-            gamma = torch.empty(n_chunks, HV, 64, **f32)
-            A = torch.empty(rows, HV, 64, **bf16)
-            w = torch.empty(rows, HV, K, **bf16)
-            u = torch.empty(rows, HV, V, **bf16)
-            h = torch.empty(n_chunks, HV, K, V, **bf16)
-            v_new = torch.empty(rows, HV, V, **bf16)
+            bf16, f32 = torch.bfloat16, torch.float32
+            zero = not tables.covered
+            o = (torch.zeros if zero else torch.empty)(B, T, HV, V, dtype=bf16, device=dev)
+            gamma, A, qk, w, u, v_new, h = carve(
+                dev, zero, ((n_chunks, HV, 64), f32), ((rows, HV, 64), bf16), ((rows, HV, 64), bf16), ((rows, HV, K), bf16),
+                ((rows, HV, V), bf16), ((rows, HV, V), bf16), ((n_chunks, HV, K, V), bf16))
             st = _stream(qb)
 
             a = new_chunk_args(qb, kb, vb, scale, tables)
             a.g, a.beta = gf.data_ptr(), bf.data_ptr()
-            a.gamma, a.A, a.w, a.u = gamma.data_ptr(), A.data_ptr(), w.data_ptr(), u.data_ptr()
+            a.gamma, a.A, a.qk, a.w, a.u = gamma.data_ptr(), A.data_ptr(), qk.data_ptr(), w.data_ptr(), u.data_ptr()
             a.stage_mask = _lib.FWD_INTRA
-            _lib.call('b200gdn_chunk_fwd', a, st)
+            with _Phase('fwd_intra', dev):
+                _lib.call('b200gdn_chunk_fwd', a, st)
 
             # (M, h_ext) of the last local sequence, zero start state; zeros when nothing continues
-            hm = torch.zeros(HV, K, K + V, **f32)
-            if not cp_context.is_last_rank:
-                last = seq_meta[n_seq - 1:n_seq]
-                h_ext = torch.empty(1, HV, K, V, **f32)
-                p = new_chunk_args(qb, kb, vb, scale, (chunk_meta, last, (n_chunks, 1)))
-                p.gamma, p.w, p.u, p.ht = gamma.data_ptr(), w.data_ptr(), u.data_ptr(), h_ext.data_ptr()
-                p.stage_mask = _lib.FWD_SCAN
-                _lib.call('b200gdn_chunk_fwd', p, st)
-                eye = torch.eye(K, **f32).expand(1, HV, K, K).contiguous()
-                M = torch.empty(1, HV, K, K, **f32)
-                p = new_chunk_args(qb, kb, vb, scale, (chunk_meta, last, (n_chunks, 1)))
-                p.V = K
-                p.gamma, p.w, p.h0, p.ht = gamma.data_ptr(), w.data_ptr(), eye.data_ptr(), M.data_ptr()
-                p.stage_mask = _lib.FWD_SCAN
-                _lib.call('b200gdn_chunk_fwd', p, st)
-                hm[:, :, :K] = M[0]
-                hm[:, :, K:] = h_ext[0]
-            gathered = exchange(hm, group)
-            h0_first = fold_prefix(gathered, rank, cp_context.pre_num_ranks, K, True, _affine_apply)
+            with _Phase('fwd_prescan', dev):
+                if cp_context.is_last_rank:
+                    hm = torch.zeros(HV, K, K + V, dtype=f32, device=dev)
+                else:
+                    h_ext, M = carve(dev, False, ((1, HV, K, V), f32), ((1, HV, K, K), f32))
+                    p = new_chunk_args(qb, kb, vb, scale, (chunk_meta, seq_meta[n_seq - 1:n_seq], (n_chunks, 1)))
+                    p.gamma, p.w, p.u, p.ht, p.cp_M = gamma.data_ptr(), w.data_ptr(), u.data_ptr(), h_ext.data_ptr(), M.data_ptr()
+                    p.stage_mask = _lib.FWD_SCAN
+                    _lib.call('b200gdn_chunk_fwd', p, st)
+                    hm = torch.cat([M[0], h_ext[0]], dim=-1)
+            with _Phase('fwd_exchange', dev):
+                gathered = exchange(hm, group)
             h0 = None
-            if h0_first is not None:
-                h0 = torch.zeros(n_seq, HV, K, V, **f32)
-                h0[0] = h0_first
+            with _Phase('fwd_fold', dev):
+                if cp_context.pre_num_ranks > 0:
+                    h0 = torch.zeros(n_seq, HV, K, V, dtype=f32, device=dev)
+                    fold_on_device(gathered, rank, cp_context.pre_num_ranks, K, True, h0[0])
 
             a.h0 = _lib.ptr(h0)
             a.q = qb.data_ptr()
             a.h, a.v_new, a.o = h.data_ptr(), v_new.data_ptr(), o.data_ptr()
             a.stage_mask = _lib.FWD_SCAN | _lib.FWD_OUT
-            _lib.call('b200gdn_chunk_fwd', a, st)
-        ctx.save_for_backward(qb, kb, vb, bf, gamma, A, w, h, v_new, chunk_meta, seq_meta)
-        ctx.meta = (scale, n_chunks, n_seq, in_dtypes)
+            with _Phase('fwd_scan_out', dev):
+                _lib.call('b200gdn_chunk_fwd', a, st)
+        ctx.save_for_backward(qb, kb, vb, bf, gamma, A, qk, w, h, v_new, chunk_meta, seq_meta)
+        ctx.meta = (scale, n_chunks, n_seq, in_dtypes, zero)
         ctx.cp_context = cp_context
         return o.to(q.dtype)
 
     @staticmethod
     def backward(ctx, do):
-        from .chunk import new_chunk_args, _stream
-        qb, kb, vb, bf, gamma, A, w, h, v_new, chunk_meta, seq_meta = ctx.saved_tensors
-        scale, n_chunks, n_seq, in_dtypes = ctx.meta
+        from .chunk import carve, new_chunk_args, _stream
+        qb, kb, vb, bf, gamma, A, qk, w, h, v_new, chunk_meta, seq_meta = ctx.saved_tensors
+        scale, n_chunks, n_seq, in_dtypes, zero = ctx.meta
         cp_context = ctx.cp_context
         group = cp_context.group
         rank = dist.get_rank(group=group)
@@ -239,64 +276,47 @@ class ChunkGatedDeltaRuleCPFunction(torch.autograd.Function):
             HV, V = vb.shape[2], vb.shape[3]
             rows = B * T
             dob = do.to(torch.bfloat16).contiguous()
-            bf16 = dict(dtype=torch.bfloat16, device=dev)
-            f32 = dict(dtype=torch.float32, device=dev)
-            dq = torch.empty(B, T, H, K, **bf16)
-            dk = torch.empty(B, T, H, K, **bf16)
-            dv = torch.empty(B, T, HV, V, **bf16)
-            dg = torch.empty(B, T, HV, **f32)
-            dbeta = torch.empty(B, T, HV, **f32)
-            dh = torch.empty(n_chunks, HV, K, V, **bf16)
-            dv2 = torch.empty(rows, HV, V, **bf16)
-            dk_part = torch.empty(rows, H, K, **f32) if HV > H else None
-            dG = torch.empty(rows, HV, **f32)
-            dq_acc = torch.empty(rows, H, K, **f32) if HV > H else None
+            bf16, f32 = torch.bfloat16, torch.float32
+            grouped = HV > H
+            dq, dk, dv, dg, dbeta, dh, dv2, dG, dk_part, dq_acc = carve(
+                dev, zero, ((B, T, H, K), bf16), ((B, T, H, K), bf16), ((B, T, HV, V), bf16), ((B, T, HV), f32), ((B, T, HV), f32),
+                ((n_chunks, HV, K, V), bf16), ((rows, HV, V), bf16), ((rows, HV), f32),
+                ((rows, H, K) if grouped else (0,), f32), ((rows, H, K) if grouped else (0,), f32))
+            if not grouped:
+                dk_part = dq_acc = None
             st = _stream(qb)
             tables = (chunk_meta, seq_meta, (n_chunks, n_seq))
 
+            # (M^T, dh_ext) of the first local sequence, zero end gradient; zeros when nothing precedes.  The pre-scan
+            # forms dv_local on chip and stores neither dv2 nor dh.
+            with _Phase('bwd_prescan', dev):
+                if cp_context.is_first_rank:
+                    dhm = torch.zeros(HV, K, K + V, dtype=f32, device=dev)
+                else:
+                    dh_ext, dM = carve(dev, False, ((1, HV, K, V), f32), ((1, HV, K, K), f32))
+                    p = new_chunk_args(qb, kb, vb, scale, (chunk_meta, seq_meta[0:1], (n_chunks, 1)))
+                    p.gamma, p.w, p.qk, p.d_o = gamma.data_ptr(), w.data_ptr(), qk.data_ptr(), dob.data_ptr()
+                    p.dh0, p.cp_dM = dh_ext.data_ptr(), dM.data_ptr()
+                    p.stage_mask = _lib.BWD_DVLOCAL | _lib.BWD_SCAN
+                    _lib.call('b200gdn_chunk_bwd', p, st)
+                    dhm = torch.cat([dM[0], dh_ext[0]], dim=-1)
+            with _Phase('bwd_exchange', dev):
+                gathered = exchange(dhm, group)
+            dht = None
+            with _Phase('bwd_fold', dev):
+                if cp_context.post_num_ranks > 0:
+                    dht = torch.zeros(n_seq, HV, K, V, dtype=f32, device=dev)
+                    fold_on_device(gathered, rank, cp_context.post_num_ranks, K, False, dht[n_seq - 1])
+
             a = new_chunk_args(qb, kb, vb, scale, tables)
-            a.beta, a.gamma, a.A, a.w, a.h, a.v_new = (x.data_ptr() for x in (bf, gamma, A, w, h, v_new))
-            a.d_o = dob.data_ptr()
+            a.beta, a.gamma, a.A, a.qk, a.w, a.h, a.v_new = (x.data_ptr() for x in (bf, gamma, A, qk, w, h, v_new))
+            a.d_o, a.dht = dob.data_ptr(), _lib.ptr(dht)
             a.dq, a.dk, a.dv, a.dg, a.dbeta = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dg.data_ptr(), dbeta.data_ptr()
             a.dh, a.dv2, a.dk_part, a.dG, a.dq_acc = dh.data_ptr(), dv2.data_ptr(), \
                 _lib.ptr(dk_part), dG.data_ptr(), _lib.ptr(dq_acc)
-            a.stage_mask = _lib.BWD_DVLOCAL
-            _lib.call('b200gdn_chunk_bwd', a, st)
-
-            # (M^T, dh_ext) of the first local sequence, zero end gradient; zeros when nothing precedes
-            dhm = torch.zeros(HV, K, K + V, **f32)
-            if not cp_context.is_first_rank:
-                first = seq_meta[0:1]
-                len0 = int(cp_context.cu_seqlens_cpu[1])
-                # the scan completes dv2 in place; keep dv_local intact.  Full-size copies: the kernels' tensor
-                # maps span all `rows` rows even though only the first sequence is scanned
-                tmp = dv2.clone()
-                dh_ext = torch.empty(1, HV, K, V, **f32)
-                p = new_chunk_args(qb, kb, vb, scale, (chunk_meta, first, (n_chunks, 1)))
-                p.gamma, p.w, p.d_o, p.dv2, p.dh0 = gamma.data_ptr(), w.data_ptr(), dob.data_ptr(), tmp.data_ptr(), \
-                    dh_ext.data_ptr()
-                p.stage_mask = _lib.BWD_SCAN
-                _lib.call('b200gdn_chunk_bwd', p, st)
-                eye = torch.eye(K, **f32).expand(1, HV, K, K).contiguous()
-                zeros = torch.zeros(rows, HV, K, **bf16)
-                dM = torch.empty(1, HV, K, K, **f32)
-                p = new_chunk_args(qb, kb, vb, scale, (chunk_meta, first, (n_chunks, 1)))
-                p.V = K
-                p.gamma, p.w, p.dv2, p.dht, p.dh0 = gamma.data_ptr(), w.data_ptr(), zeros.data_ptr(), eye.data_ptr(), \
-                    dM.data_ptr()
-                p.stage_mask = _lib.BWD_SCAN
-                _lib.call('b200gdn_chunk_bwd', p, st)
-                dhm[:, :, :K] = dM[0]
-                dhm[:, :, K:] = dh_ext[0]
-            gathered = exchange(dhm, group)
-            dht_last = fold_prefix(gathered, rank, cp_context.post_num_ranks, K, False, _affine_apply)
-            dht = None
-            if dht_last is not None:
-                dht = torch.zeros(n_seq, HV, K, V, **f32)
-                dht[n_seq - 1] = dht_last
-            a.dht = _lib.ptr(dht)
-            a.stage_mask = _lib.BWD_SCAN | _lib.BWD_DQKWG | _lib.BWD_WY
-            _lib.call('b200gdn_chunk_bwd', a, st)
+            a.stage_mask = 0
+            with _Phase('bwd_main', dev):
+                _lib.call('b200gdn_chunk_bwd', a, st)
         qd, kd, vd, gd, bd = in_dtypes
         return dq.to(qd), dk.to(kd), dv.to(vd), dg.to(gd), dbeta.to(bd), None, None
 

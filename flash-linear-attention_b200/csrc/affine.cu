@@ -58,7 +58,62 @@ __global__ void __launch_bounds__(256) affine_kernel(const b200gdn_affine_args a
     }
 }
 
+// The whole prefix fold of a rank in one launch: x = b_first; then x = M_j x + b_j for the following `count - 1`
+// ranks j = first + step, first + 2 step, ... of the gathered pairs [world][HV][K][K + V] (M in columns [0, K), the
+// state part in [K, K + V)), written to out [HV][K][V].  A CTA owns one head and CS value columns (the chain of a
+// column slice is independent of the other columns) and keeps its x slice in shared memory; 2 threads per row.
+constexpr int CS = 32;
+
+__global__ void cp_fold_kernel(const b200gdn_fold_args a) {
+  extern __shared__ float xs[];   // [2][K][CS]
+  const int K = a.K, V = a.V, hv = blockIdx.y, c0 = blockIdx.x * CS;
+  const int64_t stride = K + V;
+  const int tid = threadIdx.x, r = tid >> 1, ch = (tid & 1) * (CS / 2);
+  auto pair = [&](int j) { return a.gathered + ((int64_t)j * a.HV + hv) * K * stride; };
+  const float* P = pair(a.first);
+  float acc[CS / 2];
+#pragma unroll
+  for (int c = 0; c < CS / 2; ++c) {
+    acc[c] = P[r * stride + K + c0 + ch + c];
+    xs[r * CS + ch + c] = acc[c];
+  }
+  __syncthreads();
+  int cur = 0;
+  for (int i = 1; i < a.count; ++i) {
+    P = pair(a.first + i * a.step);
+    const float* x = xs + cur * K * CS;
+#pragma unroll
+    for (int c = 0; c < CS / 2; ++c) acc[c] = P[r * stride + K + c0 + ch + c];
+    for (int m = 0; m < K; m += 4) {
+      const float4 mv = *reinterpret_cast<const float4*>(&P[r * stride + m]);
+      const float mm[4] = {mv.x, mv.y, mv.z, mv.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+#pragma unroll
+        for (int c = 0; c < CS / 2; ++c) acc[c] += mm[e] * x[(m + e) * CS + ch + c];
+    }
+    float* y = xs + (cur ^ 1) * K * CS;
+#pragma unroll
+    for (int c = 0; c < CS / 2; ++c) y[r * CS + ch + c] = acc[c];
+    __syncthreads();
+    cur ^= 1;
+  }
+#pragma unroll
+  for (int c = 0; c < CS / 2; ++c) a.out[((int64_t)hv * K + r) * V + c0 + ch + c] = acc[c];
+}
+
 }  // namespace
+
+int launch_cp_fold(const b200gdn_fold_args& a, cudaStream_t st) {
+  const size_t smem = (size_t)2 * a.K * CS * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(cp_fold_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return set_error(B200GDN_ERR_CUDA, "cp_fold: %s", cudaGetErrorString(e));
+  }
+  dim3 grid(a.V / CS, a.HV);
+  cp_fold_kernel<<<grid, 2 * a.K, smem, st>>>(a);
+  return check_launch("cp_fold");
+}
 
 int launch_affine(const b200gdn_affine_args& a, cudaStream_t st) {
   dim3 grid((a.V + TN - 1) / TN, (a.K + TM - 1) / TM, a.HV);

@@ -83,6 +83,14 @@ int b200gdn_chunk_fwd(const b200gdn_chunk_args* a, void* stream) {
     REQUIRE(a->gamma, "chunk_fwd"); REQUIRE(a->A, "chunk_fwd"); REQUIRE(a->w, "chunk_fwd"); REQUIRE(a->u, "chunk_fwd");
     if (int e = launch_intra_fwd(*a, st)) return e;
   }
+  if ((m & B200GDN_FWD_SCAN) && (m & B200GDN_FWD_OUT)) {
+    // the scan forms the output itself from the tiles it holds on chip: h and v_new are written for the backward
+    // pass only (either may be NULL when no backward pass follows)
+    REQUIRE(a->k, "chunk_fwd"); REQUIRE(a->w, "chunk_fwd"); REQUIRE(a->gamma, "chunk_fwd");
+    REQUIRE(a->q, "chunk_fwd"); REQUIRE(a->o, "chunk_fwd");
+    if (int e = launch_scan_out_fwd(*a, st)) return e;
+    return 0;
+  }
   if (m & B200GDN_FWD_SCAN) {
     REQUIRE(a->k, "chunk_fwd"); REQUIRE(a->w, "chunk_fwd"); REQUIRE(a->gamma, "chunk_fwd");
     if (int e = launch_scan_fwd(*a, st)) return e;
@@ -102,15 +110,22 @@ int b200gdn_chunk_bwd(const b200gdn_chunk_args* a, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const uint32_t m =
       a->stage_mask ? a->stage_mask : (B200GDN_BWD_DVLOCAL | B200GDN_BWD_SCAN | B200GDN_BWD_DQKWG | B200GDN_BWD_WY);
-  if (m & B200GDN_BWD_DVLOCAL) {
-    REQUIRE(a->q, "chunk_bwd"); REQUIRE(a->k, "chunk_bwd"); REQUIRE(a->gamma, "chunk_bwd"); REQUIRE(a->d_o, "chunk_bwd");
-    REQUIRE(a->dv2, "chunk_bwd");
-    if (int e = launch_dv_local(*a, st)) return e;
-  }
-  if (m & B200GDN_BWD_SCAN) {
+  if ((m & B200GDN_BWD_DVLOCAL) && (m & B200GDN_BWD_SCAN)) {
+    // the reverse scan forms the chunk-local part of dv itself from the tiles it holds on chip; dv2 is an output only
+    // (NULL: not stored, e.g. when only dh0 of a shard is wanted)
     REQUIRE(a->q, "chunk_bwd"); REQUIRE(a->k, "chunk_bwd"); REQUIRE(a->w, "chunk_bwd"); REQUIRE(a->gamma, "chunk_bwd");
-    REQUIRE(a->dv2, "chunk_bwd");
-    if (int e = launch_scan_bwd(*a, st)) return e;
+    REQUIRE(a->d_o, "chunk_bwd");
+    if (int e = launch_scan_dvl_bwd(*a, st)) return e;
+  } else {
+    if (m & B200GDN_BWD_DVLOCAL) {
+      REQUIRE(a->q, "chunk_bwd"); REQUIRE(a->k, "chunk_bwd"); REQUIRE(a->gamma, "chunk_bwd"); REQUIRE(a->d_o, "chunk_bwd");
+      REQUIRE(a->dv2, "chunk_bwd");
+      if (int e = launch_dv_local(*a, st)) return e;
+    }
+    if (m & B200GDN_BWD_SCAN) {
+      REQUIRE(a->k, "chunk_bwd"); REQUIRE(a->w, "chunk_bwd"); REQUIRE(a->gamma, "chunk_bwd");
+      if (int e = launch_scan_bwd(*a, st)) return e;
+    }
   }
   if (m & B200GDN_BWD_DQKWG) {
     REQUIRE(a->q, "chunk_bwd"); REQUIRE(a->k, "chunk_bwd"); REQUIRE(a->v_new, "chunk_bwd"); REQUIRE(a->gamma, "chunk_bwd");
@@ -158,11 +173,26 @@ int b200gdn_affine_apply(const b200gdn_affine_args* a, void* stream) {
   return launch_affine(*a, static_cast<cudaStream_t>(stream));
 }
 
+int b200gdn_cp_fold(const b200gdn_fold_args* a, void* stream) {
+  using namespace gdn;
+  g_launches = 0;
+  if (a == nullptr) return set_error(B200GDN_ERR_BAD_ARGUMENT, "cp_fold: args is NULL");
+  if (a->struct_bytes != (int32_t)sizeof(b200gdn_fold_args))
+    return set_error(B200GDN_ERR_BAD_ARGUMENT, "cp_fold: struct_bytes %d != %zu (ABI mismatch)", a->struct_bytes,
+                     sizeof(b200gdn_fold_args));
+  if (a->HV <= 0 || a->count < 1 || a->first < 0 || (a->step != 1 && a->step != -1) || a->first + (a->count - 1) * a->step < 0)
+    return set_error(B200GDN_ERR_BAD_ARGUMENT, "cp_fold: bad sizes (HV=%d first=%d count=%d step=%d)", a->HV, a->first, a->count, a->step);
+  if ((a->K != 64 && a->K != 128 && a->K != 256) || a->V <= 0 || a->V % 32 != 0)
+    return set_error(B200GDN_ERR_UNSUPPORTED, "cp_fold: K=%d V=%d (K in {64,128,256}, V a multiple of 32)", a->K, a->V);
+  REQUIRE(a->gathered, "cp_fold"); REQUIRE(a->out, "cp_fold");
+  return launch_cp_fold(*a, static_cast<cudaStream_t>(stream));
+}
+
 int64_t b200gdn_saved_bytes(int32_t rows, int32_t H, int32_t HV, int32_t K, int32_t V, int32_t n_chunks) {
   (void)H;
   int64_t r = rows, hv = HV;
   return (int64_t)n_chunks * hv * 64 * 4  /* gamma */
-         + r * hv * 64 * 2               /* A */
+         + r * hv * 64 * 2 * 2           /* A, qk */
          + r * hv * K * 2                /* w */
          + r * hv * V * 2 * 2            /* u, v_new */
          + (int64_t)n_chunks * hv * K * V * 2; /* h */

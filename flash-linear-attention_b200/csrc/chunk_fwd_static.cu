@@ -1,6 +1,6 @@
 // b200gdn_chunk_fwd_static: the forward pass for hosts that cannot allocate device memory.
 //
-// b200gdn_chunk_fwd needs six intermediate tensors (gamma, A, w, u, h, v_new) that its caller has to
+// b200gdn_chunk_fwd needs intermediate tensors (gamma, A, qk, w, u, and for a backward pass h, v_new) that its caller has to
 // allocate.  Some callers have no way to do that at call time: an inference server that handed all free
 // device memory to its own pool at start-up and now finds cudaMalloc failing, a plug-in running inside
 // another program's CUDA context with no agreed allocator, or a plain C host that only owns its input and
@@ -96,14 +96,14 @@ extern "C" int b200gdn_chunk_fwd_static(const b200gdn_chunk_args* a, void* strea
   if (!a->chunk_meta || !a->seq_meta || !a->q || !a->k || !a->v || !a->g || !a->beta || !a->o)
     return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: q, k, v, g, beta, o and both chunk tables are required", who);
 
-  // carve the array: gamma | A | w | u | v_new | h, each region 256-byte aligned
+  // carve the array: gamma | A | qk | w | u, each region 256-byte aligned (h and v_new are only read by a backward
+  // pass, which this entry point does not serve: the scan does not write them)
   const size_t rh = (size_t)a->rows * a->HV;
   const size_t sz_gamma = align256((size_t)a->n_chunks * a->HV * B200GDN_CHUNK * sizeof(float));
   const size_t sz_A = align256(rh * B200GDN_CHUNK * 2);
   const size_t sz_w = align256(rh * a->K * 2);
   const size_t sz_u = align256(rh * a->V * 2);
-  const size_t sz_h = align256((size_t)a->n_chunks * a->HV * a->K * a->V * 2);
-  const size_t need = sz_gamma + sz_A + sz_w + 2 * sz_u + sz_h;
+  const size_t need = sz_gamma + 2 * sz_A + sz_w + sz_u;
   if (need > (size_t)B200GDN_STATIC_SCRATCH_BYTES)
     return set_error(B200GDN_ERR_TOO_LARGE,
                      "%s: this problem needs %zu bytes of intermediates but the built-in array holds %zu; "
@@ -117,13 +117,13 @@ extern "C" int b200gdn_chunk_fwd_static(const b200gdn_chunk_args* a, void* strea
   unsigned char* p = base;
   b.gamma = reinterpret_cast<float*>(p); p += sz_gamma;
   b.A = p; p += sz_A;
+  b.qk = p; p += sz_A;
   b.w = p; p += sz_w;
-  b.u = p; p += sz_u;
-  b.v_new = p; p += sz_u;
-  b.h = p;
+  b.u = p;
+  b.v_new = nullptr;
+  b.h = nullptr;
   b.stage_mask = 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (int e = launch_intra_fwd(b, st)) return e;
-  if (int e = launch_scan_fwd(b, st)) return e;
-  return launch_out_fwd(b, st);
+  return launch_scan_out_fwd(b, st);
 }

@@ -76,13 +76,16 @@ __device__ __forceinline__ bool successor_cta(int dist, int& c2, int& h2) {
 namespace gdn {
 int launch_intra_fwd(const b200gdn_chunk_args& a, cudaStream_t st);
 int launch_scan_fwd(const b200gdn_chunk_args& a, cudaStream_t st);
+int launch_scan_out_fwd(const b200gdn_chunk_args& a, cudaStream_t st);
 int launch_out_fwd(const b200gdn_chunk_args& a, cudaStream_t st);
 int launch_dv_local(const b200gdn_chunk_args& a, cudaStream_t st);
 int launch_scan_bwd(const b200gdn_chunk_args& a, cudaStream_t st);
+int launch_scan_dvl_bwd(const b200gdn_chunk_args& a, cudaStream_t st);
 int launch_bwd_dqk(const b200gdn_chunk_args& a, cudaStream_t st);
 int launch_bwd_wy(const b200gdn_chunk_args& a, cudaStream_t st);
 int launch_recurrent(const b200gdn_recurrent_args& a, cudaStream_t st);
 int launch_affine(const b200gdn_affine_args& a, cudaStream_t st);
+int launch_cp_fold(const b200gdn_fold_args& a, cudaStream_t st);
 int launch_prep(const b200gdn_prep_args& a, cudaStream_t st, bool bwd);
 int decode_timeout_flag();
 int intra_fwd_timeout_flag();

@@ -1,5 +1,8 @@
 // Intra-chunk forward: gamma = cumsum(g) log2(e);  A = (I + strict_tril(beta_i <k_i,k_j> 2^(gamma_i-gamma_j)))^-1;
-// W = A (K beta 2^gamma);  U = A (V beta).   One CTA of eight warps per (chunk, value head).
+// W = A (K beta 2^gamma);  U = A (V beta);  and (when q and a qk buffer are given)
+// qk = tril(<q_i,k_j> 2^(gamma_i-gamma_j)), the chunk-local attention tile of chunk_fwd_kernel_o /
+// chunk_bwd_kernel_dv_local (fla/ops/common/chunk_o.py:115-127, 505-520), which shares K, gamma and the gate factors
+// with L.   One CTA of eight warps per (chunk, value head).
 //
 // Replaces chunk_local_cumsum (fla/ops/utils/cumsum.py:33-68), the fused K K^T + triangular solve
 // (fla/ops/gated_delta_rule/chunk_fwd.py:40-328) and recompute_w_u_fwd (gated_delta_rule/wy_fast.py:43-106).
@@ -44,7 +47,7 @@ struct IntraSmem {
 };
 
 struct IntraMaps {
-  CUtensorMap k, v, w, u;
+  CUtensorMap k, v, w, u, q;
 };
 
 // T = L21 * A11 ;  A21 = -A22 * T   for an N x N off-diagonal block whose top-left corner is (r0, c0).
@@ -117,14 +120,19 @@ __global__ void __launch_bounds__(NTHREADS, 4) intra_fwd_kernel(const b200gdn_ch
   const int64_t row0 = cm.row;
   const int r_lo = q * 16 + g, r_hi = r_lo + 8;
   const int cs = hc * 32;
+  // with q and a qk buffer the kernel also emits the gated causal q k^T tile that the scans use for the chunk-local
+  // parts of o and dv (so that they neither form nor mask it on their serial chain)
+  const bool with_qk = a.qk != nullptr && a.q != nullptr;
+  unsigned char* Qs = smem + S::o_l;
 
   if (tid == 0) {
     tc5::mbar_init(bar, 1);
     tc5::mbar_init(bar_k, 1);
     tc5::mbar_init(bar_v, 1);
     tc5::fence_mbar_init();
-    tc5::mbar_expect_tx(bar_k, (uint32_t)(BT * DK * 2));
+    tc5::mbar_expect_tx(bar_k, (uint32_t)((with_qk ? 2 : 1) * BT * DK * 2));
     tma::load_3d(Ks, &maps.k, cm.row, (hq * DK) / 64, bar_k);
+    if (with_qk) tma::load_3d(Qs, &maps.q, cm.row, (hq * DK) / 64, bar_k);   // lives where L will be written
     tma::prefetch_3d(&maps.v, cm.row, (hv * DV) / 64);   // V is loaded late (it reuses L's place): have it in L2 by then
   }
   if (warp == 1) tc5::tmem_alloc(tmem_slot, 128);
@@ -190,12 +198,15 @@ __global__ void __launch_bounds__(NTHREADS, 4) intra_fwd_kernel(const b200gdn_ch
     if (tid == 0) {
       tc5::fence_after_sync();
       issue_mma_t<DK / 16>(tm, Operand{tc5::smem_addr(Ks), BT, 0}, Operand{tc5::smem_addr(Ks), BT, 0}, 64, 64, 0);
+      if (with_qk) issue_mma_t<DK / 16>(tm + 64, Operand{tc5::smem_addr(Qs), BT, 0}, Operand{tc5::smem_addr(Ks), BT, 0}, 64, 64, 0);
       ph.commit();
     }
     if (tid < BT) graw[tid] = (gam[tid] + (tid >= 32 ? gam[31] : 0.f)) * 1.4426950216f;
     __syncthreads();
     if (tid < BT) {
-      const float gm = graw[tid];
+      // entries past a ragged chunk's end repeat the last valid value exactly (the scan sums zeros there, but in an
+      // order that depends on the lane, so its result may differ in the last bit)
+      const float gm = graw[tid < cm.len ? tid : cm.len - 1];
       gam[tid] = gm;
       bge[tid] = bet[tid] * fast_exp2(gm);
       a.gamma[((int64_t)c * a.HV + hv) * BT + tid] = gm;   // padded rows carry the last valid value (their g is 0)
@@ -204,23 +215,42 @@ __global__ void __launch_bounds__(NTHREADS, 4) intra_fwd_kernel(const b200gdn_ch
   }
 
   if (!failed) {
-    // ---- L = strict_tril(beta_i <k_i,k_j> 2^(gamma_i - gamma_j)) in fp32
-    if (q * 16 + 15 > cs) {   // a block entirely above the diagonal is never read by the solve
-      float r[16];
-      acc_ld32q(tm, q, cs, r);
-      tc5::tmem_ld_wait();
-      const float g_lo = gam[r_lo], g_hi = gam[r_hi], b_lo = bet[r_lo], b_hi = bet[r_hi];
+    // ---- L = strict_tril(beta_i <k_i,k_j> 2^(gamma_i - gamma_j)) in fp32 (over the Q tile, which is dead by now), and
+    //      qk = tril(<q_i,k_j> 2^(gamma_i - gamma_j)) with the same gate factors, as bf16 straight to global memory
+    //      (rows past a ragged chunk's end are another sequence's rows and are not written)
+    {
+      __nv_bfloat16* Pg = reinterpret_cast<__nv_bfloat16*>(a.qk) + (row0 * a.HV + hv) * BT + cs + 2 * t;
+      const int64_t pstride = (int64_t)a.HV * BT;
+      if (q * 16 + 15 >= cs) {   // a block entirely above the diagonal is never read by the solve and is zero in qk
+        float r[16], pq[16];
+        acc_ld32q(tm, q, cs, r);
+        if (with_qk) acc_ld32q(tm + 64, q, cs, pq);
+        tc5::tmem_ld_wait();
+        const float g_lo = gam[r_lo], g_hi = gam[r_hi], b_lo = bet[r_lo], b_hi = bet[r_hi];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int j0 = cs + i * 8 + 2 * t;
-        float v[4];
+        for (int i = 0; i < 4; ++i) {
+          const int j0 = cs + i * 8 + 2 * t;
+          float v[4], w4[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int ii = (e & 2) ? r_hi : r_lo, jj = j0 + (e & 1);
-          v[e] = (ii > jj) ? r[4 * i + e] * ((e & 2) ? b_hi : b_lo) * fast_exp2(((e & 2) ? g_hi : g_lo) - gam[jj]) : 0.f;
+          for (int e = 0; e < 4; ++e) {
+            const int ii = (e & 2) ? r_hi : r_lo, jj = j0 + (e & 1);
+            const float f = fast_exp2(((e & 2) ? g_hi : g_lo) - gam[jj]);
+            v[e] = (ii > jj) ? r[4 * i + e] * ((e & 2) ? b_hi : b_lo) * f : 0.f;
+            w4[e] = (with_qk && ii >= jj) ? pq[4 * i + e] * f : 0.f;
+          }
+          *reinterpret_cast<float2*>(&Lf[r_lo * LDF + j0]) = make_float2(v[0], v[1]);
+          *reinterpret_cast<float2*>(&Lf[r_hi * LDF + j0]) = make_float2(v[2], v[3]);
+          if (with_qk) {
+            if (r_lo < cm.len) *reinterpret_cast<uint32_t*>(Pg + r_lo * pstride + i * 8) = pack_bf16(w4[0], w4[1]);
+            if (r_hi < cm.len) *reinterpret_cast<uint32_t*>(Pg + r_hi * pstride + i * 8) = pack_bf16(w4[2], w4[3]);
+          }
         }
-        *reinterpret_cast<float2*>(&Lf[r_lo * LDF + j0]) = make_float2(v[0], v[1]);
-        *reinterpret_cast<float2*>(&Lf[r_hi * LDF + j0]) = make_float2(v[2], v[3]);
+      } else if (with_qk) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (r_lo < cm.len) *reinterpret_cast<uint32_t*>(Pg + r_lo * pstride + i * 8) = 0u;
+          if (r_hi < cm.len) *reinterpret_cast<uint32_t*>(Pg + r_hi * pstride + i * 8) = 0u;
+        }
       }
     }
     tc5::fence_before_sync();
@@ -386,6 +416,7 @@ int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
   rc |= tma::encode_bf16_panels(&m.v, a.v, a.rows, pv, pv, BT, DV / 64);
   rc |= tma::encode_bf16_panels(&m.w, a.w, a.rows, pw, pw, BT, DK / 64);
   rc |= tma::encode_bf16_panels(&m.u, a.u, a.rows, pv, pv, BT, DV / 64);
+  if (a.q) rc |= tma::encode_bf16_panels(&m.q, a.q, a.rows, pk, pk, BT, DK / 64); else m.q = m.k;
   if (rc != 0) return set_error(B200GDN_ERR_CUDA, "intra_fwd: cuTensorMapEncodeTiled failed (%d)", rc);
   dim3 grid(a.n_chunks, a.HV);
   intra_fwd_kernel<DK, DV><<<grid, NTHREADS, S::bytes, st>>>(a, m, resident_ctas(intra_fwd_kernel<DK, DV>, NTHREADS, S::bytes));

@@ -47,7 +47,7 @@ typedef enum b200gdn_status {
 } b200gdn_status;
 
 /* stage masks: run only some kernels of a pass (unit tests and profiling); 0 means all */
-#define B200GDN_FWD_INTRA 1u     /* gamma, A, w, u         <- k, v, g, beta */
+#define B200GDN_FWD_INTRA 1u     /* gamma, A, w, u, qk     <- k, v, g, beta (, q) */
 #define B200GDN_FWD_SCAN 2u      /* h, v_new, ht           <- k, w, u, gamma, h0 */
 #define B200GDN_FWD_OUT 4u       /* o                      <- q, k, v_new, h, gamma */
 #define B200GDN_BWD_DVLOCAL 1u   /* dv2 (local part)       <- q, k, gamma, do */
@@ -115,6 +115,15 @@ typedef struct b200gdn_chunk_args {
   float* gate_partials;          /* workspace fp32 [n_chunks,HV,2] (GATE, backward) */
   float* dA_log;                 /* out [HV] (GATE, backward) */
   float* ddt_bias;               /* out [HV] or NULL */
+  /* Context parallelism (fla/ops/cp/chunk_delta_h.py:41-315, 478-744): with cp_M, the forward scan stage run alone
+   * (B200GDN_FWD_SCAN) also gives, per scanned sequence, the K x K transition matrix M of S_end = M S_start + h_ext
+   * (h_ext is what ht receives for a zero start state); with cp_dM the reverse scan gives the backward counterpart
+   * next to dh0.  Both [n_seq,HV,K,K] fp32, NULL otherwise. */
+  float* cp_M;
+  float* cp_dM;
+  /* written by the forward pass (intra stage, needs q), read by the fused scan stages of both passes:
+   * bf16 [rows,HV,64], row i of a chunk holds <q_i,k_j> 2^(gamma_i - gamma_j) for j <= i, zero for j > i */
+  void* qk;
 } b200gdn_chunk_args;
 
 /* Replaces chunk_gated_delta_rule_fwd (fla/ops/gated_delta_rule/chunk.py:33-123):
@@ -123,12 +132,12 @@ int b200gdn_chunk_fwd(const b200gdn_chunk_args* args, void* stream);
 
 /* No counterpart in the reference.  Same result as b200gdn_chunk_fwd (o and, when ht != NULL, the final state)
  * for callers that cannot allocate device memory (a server whose own pool already owns all of it, a plug-in
- * inside a foreign CUDA context, a C host that owns only inputs and outputs): the six intermediate tensors live
+ * inside a foreign CUDA context, a C host that owns only inputs and outputs): the intermediate tensors live
  * in one array built into the library, B200GDN_STATIC_SCRATCH_BYTES bytes per GPU that loads the library, held
- * until exit.  The gamma/A/w/u/h/v_new fields of `args` are ignored and nothing is saved for a backward pass.
- * Limit: align256(n_chunks*HV*256) + align256(rows*HV*128) + align256(rows*HV*K*2) + 2*align256(rows*HV*V*2)
- *        + align256(n_chunks*HV*K*V*2)  <=  B200GDN_STATIC_SCRATCH_BYTES
- * (e.g. 2048 tokens x 16 heads at K = V = 128); larger problems return B200GDN_ERR_TOO_LARGE and launch nothing.
+ * until exit.  The gamma/A/qk/w/u/h/v_new fields of `args` are ignored and nothing is saved for a backward pass.
+ * Limit: align256(n_chunks*HV*256) + 2*align256(rows*HV*128) + align256(rows*HV*K*2) + align256(rows*HV*V*2)
+ *        <=  B200GDN_STATIC_SCRATCH_BYTES
+ * (e.g. 4096 tokens x 16 heads at K = V = 128); larger problems return B200GDN_ERR_TOO_LARGE and launch nothing.
  * Precondition (as for every chunk entry point): the sequences of the chunk tables cover all `rows` token rows.
  * Makes no allocating call.  The first call on each device looks up the array's address and should come before
  * any stream capture.  All calls on a device share the array (it keeps the previous call's contents; no stage
@@ -190,6 +199,20 @@ typedef struct b200gdn_affine_args {
   float* out;                    /* [HV,K,V] */
 } b200gdn_affine_args;
 int b200gdn_affine_apply(const b200gdn_affine_args* args, void* stream);
+
+/* The prefix fold of one rank in a single launch (the chain of merges of fla/ops/cp/chunk_delta_h.py:332-460 over the
+ * gathered pairs): x = b_first, then x = M_j x + b_j for j = first + step, ..., first + (count - 1) step, where rank
+ * j's pair is gathered[j] = [HV, K, K + V] fp32 (M in columns [0, K), the state part b in [K, K + V)).
+ * forward: first = rank - pre_num_ranks, step = +1;  backward (the pairs hold M^T): first = rank + post_num_ranks,
+ * step = -1.  K in {64, 128, 256}, V a multiple of 32, count >= 1. */
+typedef struct b200gdn_fold_args {
+  int32_t struct_bytes;
+  int32_t HV, K, V;
+  int32_t first, count, step;
+  const float* gathered;         /* [world, HV, K, K + V] */
+  float* out;                    /* [HV, K, V] */
+} b200gdn_fold_args;
+int b200gdn_cp_fold(const b200gdn_fold_args* args, void* stream);
 
 /* The three options fla.layers.GatedDeltaNet turns on (fla/layers/gated_deltanet.py:309-325), as one pass before the
  * chunk kernels and one pass after their backward:

@@ -290,12 +290,31 @@ def stage_out(q, k, v_new, h, gam, scale, bounds, emulate_bf16=False):
     return o
 
 
+def stage_qk(q, k, gam, HV, bounds):
+    """The chunk-local attention tile of the output and of dv_local, without the scale:
+    qk[i, j] = <q_i, k_j> 2^(gam_i - gam_j) for j <= i, else 0  (fla/ops/common/chunk_o.py:115-127, 505-520);
+    one row of 64 entries per (token, value head)."""
+    R, H, K = q.shape
+    G = HV // H
+    out = torch.zeros(R, HV, BT, dtype=q.dtype)
+    lower = torch.tril(torch.ones(BT, BT, dtype=torch.bool))
+    for (_, s, L) in chunk_table(bounds):
+        qc = _tile(q, s, L).repeat_interleave(G, dim=1).transpose(0, 1)
+        kc = _tile(k, s, L).repeat_interleave(G, dim=1).transpose(0, 1)
+        gm = _tile(gam, s, L).transpose(0, 1).clone()
+        gm[:, L:] = gm[:, L - 1:L]
+        D = torch.exp2((gm[:, :, None] - gm[:, None, :]).masked_fill(~lower, 0.0))
+        P = ((qc @ kc.transpose(1, 2)) * D).masked_fill(~lower, 0.0)
+        out[s:s + L] = P.transpose(0, 1)[:L]
+    return out
+
+
 def chunk_fwd(q, k, v, g, beta, scale, h0, bounds, emulate_bf16=False):
     """All forward stages chained (fla/ops/gated_delta_rule/chunk.py:33-123)."""
     gam, A, w, u = stage_intra(k, v, g, beta, bounds, emulate_bf16)
     h, v_new, ht = stage_scan_fwd(k, w, u, gam, h0, bounds, emulate_bf16)
     o = stage_out(q, k, v_new, h, gam, scale, bounds, emulate_bf16)
-    return dict(gamma=gam, A=A, w=w, u=u, h=h, v_new=v_new, ht=ht, o=o)
+    return dict(gamma=gam, A=A, w=w, u=u, h=h, v_new=v_new, ht=ht, o=o, qk=stage_qk(q, k, gam, HV=v.shape[1], bounds=bounds))
 
 
 # --------------------------------------------------------------------------- backward stages

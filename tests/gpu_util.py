@@ -68,6 +68,7 @@ def run_abi(d, dev='cuda', fwd_mask=0, bwd_mask=0, overrides=None, do_bwd=True):
     t = dict(
         o=torch.full((rows, HV, V), nan, **bf), ht=torch.full((n_seq, HV, K, V), nan, **f32),
         gamma=torch.full((n_chunks, HV, 64), nan, **f32), A=torch.full((rows, HV, 64), nan, **bf),
+        qk=torch.full((rows, HV, 64), nan, **bf),
         w=torch.full((rows, HV, K), nan, **bf), u=torch.full((rows, HV, V), nan, **bf),
         h=torch.full((n_chunks, HV, K, V), nan, **bf), v_new=torch.full((rows, HV, V), nan, **bf),
         dq=torch.full((rows, H, K), nan, **bf), dk=torch.full((rows, H, K), nan, **bf),

@@ -63,7 +63,7 @@ def test_argument_errors_without_gpu():
     assert lib.b200gdn_prep_fwd(ctypes.byref(p), None) == -2 and b'are built' in lib.b200gdn_last_error()
     p.K, p.flags = 128, _lib.PREP_GATE
     assert lib.b200gdn_prep_bwd(ctypes.byref(p), None) == -1 and b'is NULL' in lib.b200gdn_last_error()
-    assert lib.b200gdn_saved_bytes(16384, 16, 16, 128, 128, 256) == 16384 * 16 * (4 + 128 + 256 * 3) + 256 * 16 * 32768
+    assert lib.b200gdn_saved_bytes(16384, 16, 16, 128, 128, 256) == 16384 * 16 * (4 + 256 + 256 * 3) + 256 * 16 * 32768
     assert lib.b200gdn_bwd_workspace_bytes(64, 2, 4, 128, 128, 1) > 0
 
 

@@ -99,3 +99,26 @@ def test_context_parallel_matches_single_gpu(name):
         # same tolerance as the reference's CP test (assert_close ratio 3e-3 .. 5e-3 against its own single-GPU run)
         for n, e in errs.items():
             assert e < 0.005, f'{name} rank {rank} {n}: {e}'
+
+
+def test_fold_kernels_match_the_host_fold():
+    """The single-launch prefix fold and the one-step affine kernel against the host statement of the fold in fp64
+    (forward and backward direction, every possible number of neighbouring ranks)."""
+    from b200gdn.cp import affine_apply, fold_on_device, fold_prefix
+    W, HV, K, V = 8, 3, 128, 128
+    gen = torch.Generator().manual_seed(5)
+    gathered = torch.randn(W, HV, K, K + V, generator=gen)
+    gathered[..., :K] *= K ** -0.5   # keep the chained products O(1)
+    dev_g = gathered.cuda()
+
+    def host(M, x, b, transpose):
+        return (M.double().transpose(-1, -2) if transpose else M.double()) @ x.double() + b.double()
+    for rank, num, fwd in [(7, 7, True), (3, 1, True), (5, 2, True), (0, 7, False), (4, 3, False), (6, 1, False)]:
+        want = fold_prefix(gathered, rank, num, K, fwd, host).float()
+        out = torch.empty(HV, K, V, device='cuda')
+        fold_on_device(dev_g, rank, num, K, fwd, out)
+        assert torch.allclose(out.cpu(), want, rtol=1e-4, atol=1e-4), (rank, num, fwd, float((out.cpu() - want).abs().max()))
+        got = fold_prefix(dev_g, rank, num, K, fwd, affine_apply)
+        assert torch.allclose(got.cpu(), want, rtol=1e-4, atol=1e-4)
+    M, x, b = dev_g[0, :, :, :K].contiguous(), dev_g[1, :, :, K:].contiguous(), dev_g[2, :, :, K:].contiguous()
+    assert torch.allclose(affine_apply(M, x, b, True).cpu(), host(M.cpu(), x.cpu(), b.cpu(), True).float(), rtol=1e-4, atol=1e-4)

@@ -59,7 +59,7 @@ def test_static_scratch_forward_matches_regular_forward_twice():
         # regular entry point with caller-allocated intermediates
         o_ref = torch.empty(rows, HV, V, **bf)
         ht_ref = torch.empty(n_seq, HV, K, V, **f32)
-        scratch = dict(gamma=torch.empty(n_chunks, HV, 64, **f32), A=torch.empty(rows, HV, 64, **bf),
+        scratch = dict(gamma=torch.empty(n_chunks, HV, 64, **f32), A=torch.empty(rows, HV, 64, **bf), qk=torch.empty(rows, HV, 64, **bf),
                        w=torch.empty(rows, HV, K, **bf), u=torch.empty(rows, HV, V, **bf),
                        h=torch.empty(n_chunks, HV, K, V, **bf), v_new=torch.empty(rows, HV, V, **bf))
         a.o, a.ht = o_ref.data_ptr(), ht_ref.data_ptr()
