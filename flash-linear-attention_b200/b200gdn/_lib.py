@@ -71,6 +71,29 @@ class AffineArgs(C.Structure):
     ]
 
 
+class ConvArgs(C.Structure):
+    _fields_ = [
+        ('struct_bytes', C.c_int32), ('rows', C.c_int32), ('D', C.c_int32), ('W', C.c_int32),
+        ('n_seq', C.c_int32), ('n_tiles', C.c_int32), ('flags', C.c_uint32), ('dtype', C.c_int32),
+        ('tile_meta', _p), ('seq_meta', _p), ('x', _p), ('weight', _p), ('bias', _p), ('residual', _p),
+        ('initial_state', _p), ('y', _p), ('final_state', _p),
+        ('dy', _p), ('dx', _p), ('dweight', _p), ('dbias', _p), ('dinitial_state', _p), ('partials', _p),
+    ]
+
+
+class NormGateArgs(C.Structure):
+    _fields_ = [
+        ('struct_bytes', C.c_int32), ('D', C.c_int32), ('rows', C.c_int64), ('flags', C.c_uint32),
+        ('dtype', C.c_int32), ('eps', C.c_float),
+        ('x', _p), ('g', _p), ('weight', _p), ('bias', _p), ('y', _p), ('rstd', _p),
+        ('dy', _p), ('dx', _p), ('dg', _p), ('dweight', _p), ('dbias', _p), ('partials', _p),
+    ]
+
+
+CONV_SILU = 1
+NORM_GATE_SIGMOID = 1
+
+
 class FoldArgs(C.Structure):
     _fields_ = [
         ('struct_bytes', C.c_int32), ('HV', C.c_int32), ('K', C.c_int32), ('V', C.c_int32),
@@ -84,6 +107,7 @@ EXPORTS = (
     'b200gdn_saved_bytes', 'b200gdn_bwd_workspace_bytes', 'b200gdn_last_launch_count',
     'b200gdn_abi_version', 'b200gdn_last_error', 'b200gdn_device_status', 'b200gdn_prep_fwd', 'b200gdn_prep_bwd',
     'b200gdn_selftest_wait_expiry', 'b200gdn_chunk_fwd_static', 'b200gdn_cp_fold',
+    'b200gdn_conv_fwd', 'b200gdn_conv_bwd', 'b200gdn_norm_gate_fwd', 'b200gdn_norm_gate_bwd', 'b200gdn_norm_gate_ctas',
 )
 
 _lib = None
@@ -108,7 +132,8 @@ def load():
                 '(or __graft_entry__.build()). There is no fallback path.')
         lib = C.CDLL(LIB_PATH)
         for name in ('b200gdn_chunk_fwd', 'b200gdn_chunk_bwd', 'b200gdn_recurrent_fwd', 'b200gdn_affine_apply',
-                     'b200gdn_prep_fwd', 'b200gdn_prep_bwd', 'b200gdn_chunk_fwd_static', 'b200gdn_cp_fold'):
+                     'b200gdn_prep_fwd', 'b200gdn_prep_bwd', 'b200gdn_chunk_fwd_static', 'b200gdn_cp_fold',
+                     'b200gdn_conv_fwd', 'b200gdn_conv_bwd', 'b200gdn_norm_gate_fwd', 'b200gdn_norm_gate_bwd'):
             fn = getattr(lib, name)
             fn.restype = C.c_int
             fn.argtypes = [C.c_void_p, C.c_void_p]
@@ -116,6 +141,8 @@ def load():
             fn = getattr(lib, name)
             fn.restype = C.c_int64
             fn.argtypes = [C.c_int32] * 6
+        lib.b200gdn_norm_gate_ctas.restype = C.c_int
+        lib.b200gdn_norm_gate_ctas.argtypes = [C.c_int64]
         lib.b200gdn_last_launch_count.restype = C.c_int
         lib.b200gdn_device_status.restype = C.c_int
         lib.b200gdn_device_status.argtypes = []

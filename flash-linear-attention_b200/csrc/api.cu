@@ -249,6 +249,68 @@ int b200gdn_prep_bwd(const b200gdn_prep_args* a, void* stream) {
   return gdn::launch_prep(*a, static_cast<cudaStream_t>(stream), true);
 }
 
+static int check_conv_args(const b200gdn_conv_args* a, const char* who, bool bwd) {
+  using namespace gdn;
+  if (a == nullptr) return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: args is NULL", who);
+  if (a->struct_bytes != (int32_t)sizeof(b200gdn_conv_args))
+    return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: struct_bytes %d != %zu (ABI mismatch)", who, a->struct_bytes,
+                     sizeof(b200gdn_conv_args));
+  if (a->rows <= 0 || a->D <= 0 || a->n_seq <= 0 || a->n_tiles <= 0)
+    return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: empty problem (rows=%d D=%d n_seq=%d n_tiles=%d)", who, a->rows, a->D, a->n_seq, a->n_tiles);
+  if (a->D % 8 != 0) return set_error(B200GDN_ERR_UNSUPPORTED, "%s: D=%d is not a multiple of 8", who, a->D);
+  if (a->W < 2 || a->W > 4) return set_error(B200GDN_ERR_UNSUPPORTED, "%s: kernel size %d (2, 3 and 4 are built)", who, a->W);
+  if (a->dtype < 0 || a->dtype > 2) return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: dtype code %d", who, a->dtype);
+  REQUIRE(a->tile_meta, who); REQUIRE(a->seq_meta, who); REQUIRE(a->x, who); REQUIRE(a->weight, who);
+  if (!bwd) { REQUIRE(a->y, who); }
+  else {
+    REQUIRE(a->dy, who); REQUIRE(a->dx, who);
+    if (a->dweight != nullptr) REQUIRE(a->partials, who);
+  }
+  return 0;
+}
+
+int b200gdn_conv_fwd(const b200gdn_conv_args* a, void* stream) {
+  gdn::g_launches = 0;
+  if (int e = check_conv_args(a, "conv_fwd", false)) return e;
+  return gdn::launch_conv(*a, static_cast<cudaStream_t>(stream), false);
+}
+
+int b200gdn_conv_bwd(const b200gdn_conv_args* a, void* stream) {
+  gdn::g_launches = 0;
+  if (int e = check_conv_args(a, "conv_bwd", true)) return e;
+  return gdn::launch_conv(*a, static_cast<cudaStream_t>(stream), true);
+}
+
+static int check_norm_gate_args(const b200gdn_norm_gate_args* a, const char* who, bool bwd) {
+  using namespace gdn;
+  if (a == nullptr) return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: args is NULL", who);
+  if (a->struct_bytes != (int32_t)sizeof(b200gdn_norm_gate_args))
+    return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: struct_bytes %d != %zu (ABI mismatch)", who, a->struct_bytes,
+                     sizeof(b200gdn_norm_gate_args));
+  if (a->rows <= 0) return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: empty problem", who);
+  if (a->D != 64 && a->D != 128 && a->D != 256 && a->D != 512)
+    return set_error(B200GDN_ERR_UNSUPPORTED, "%s: D=%d (64, 128, 256 and 512 are built)", who, a->D);
+  if (a->dtype < 0 || a->dtype > 2) return set_error(B200GDN_ERR_BAD_ARGUMENT, "%s: dtype code %d", who, a->dtype);
+  REQUIRE(a->x, who); REQUIRE(a->g, who); REQUIRE(a->rstd, who);
+  if (!bwd) { REQUIRE(a->y, who); }
+  else { REQUIRE(a->dy, who); REQUIRE(a->dx, who); REQUIRE(a->dg, who); REQUIRE(a->partials, who); }
+  return 0;
+}
+
+int b200gdn_norm_gate_fwd(const b200gdn_norm_gate_args* a, void* stream) {
+  gdn::g_launches = 0;
+  if (int e = check_norm_gate_args(a, "norm_gate_fwd", false)) return e;
+  return gdn::launch_norm_gate(*a, static_cast<cudaStream_t>(stream), false);
+}
+
+int b200gdn_norm_gate_bwd(const b200gdn_norm_gate_args* a, void* stream) {
+  gdn::g_launches = 0;
+  if (int e = check_norm_gate_args(a, "norm_gate_bwd", true)) return e;
+  return gdn::launch_norm_gate(*a, static_cast<cudaStream_t>(stream), true);
+}
+
+int b200gdn_norm_gate_ctas(int64_t rows) { return gdn::norm_gate_grid(rows); }
+
 int b200gdn_selftest_wait_expiry(void* stream) {
   gdn::g_launches = 0;
   gdn::selftest_wait_expiry_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(2000u);

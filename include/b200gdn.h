@@ -260,6 +260,69 @@ typedef struct b200gdn_prep_args {
 int b200gdn_prep_fwd(const b200gdn_prep_args* args, void* stream);
 int b200gdn_prep_bwd(const b200gdn_prep_args* args, void* stream);
 
+/* Short causal depthwise convolution (+ SiLU) on token-major activations, the step in front of the mixer
+ * (fla/layers/gated_deltanet.py:247-300; causal_conv1d of fla/modules/conv/causal_conv1d.py:17-160 with the Triton
+ * kernels of fla/modules/conv/triton/ops.py):  y[t,d] = act(bias[d] + sum_w weight[d,w] x[t-(W-1)+w, d]) (+ residual)
+ * inside each sequence; x[-k] = initial_state[n,d,W-k] for k = 1..W-1 (zero without a cache); final_state[n,d,:] =
+ * the last W inputs.  Tiles of up to 64 tokens of one sequence are described by the same two tables as the mixer's
+ * chunks.  D a multiple of 8, W in {2,3,4}. */
+#define B200GDN_CONV_SILU 1u
+typedef struct b200gdn_conv_args {
+  int32_t struct_bytes;
+  int32_t rows, D, W;
+  int32_t n_seq, n_tiles;
+  uint32_t flags;                /* B200GDN_CONV_SILU */
+  int32_t dtype;                 /* 0 = bf16, 1 = fp16, 2 = fp32: x, y, residual, states, dy, dx */
+  const int32_t* tile_meta;      /* device [n_tiles][4], as chunk_meta */
+  const int32_t* seq_meta;       /* device [n_seq][2], as seq_meta */
+  const void* x;                 /* [rows, D] */
+  const float* weight;           /* [D, W] */
+  const float* bias;             /* [D] or NULL */
+  const void* residual;          /* [rows, D] or NULL (forward) */
+  const void* initial_state;     /* [n_seq, D, W] or NULL */
+  void* y;                       /* [rows, D] (forward) */
+  void* final_state;             /* [n_seq, D, W] or NULL (forward) */
+  /* backward */
+  const void* dy;                /* [rows, D] */
+  void* dx;                      /* [rows, D] */
+  float* dweight;                /* [D, W] or NULL */
+  float* dbias;                  /* [D] or NULL */
+  void* dinitial_state;          /* [n_seq, D, W] or NULL */
+  float* partials;               /* workspace fp32 [n_tiles, D, W + 1]; required with dweight */
+} b200gdn_conv_args;
+int b200gdn_conv_fwd(const b200gdn_conv_args* args, void* stream);
+int b200gdn_conv_bwd(const b200gdn_conv_args* args, void* stream);
+
+/* Gated RMS norm over the head dimension, the step behind the mixer (fla/layers/gated_deltanet.py:355-357;
+ * rms_norm_gated of fla/modules/fused_norm_gate.py:861-884 without residual):
+ *   rstd = 1/sqrt(mean(x^2) + eps);  y = (x rstd weight + bias) act(g),  act = g sigmoid(g), or sigmoid(g) with
+ * B200GDN_NORM_GATE_SIGMOID.  rows = tokens x heads, D in {64,128,256,512}.  The backward pass needs `partials`
+ * of b200gdn_norm_gate_ctas(rows) x 2 x D floats. */
+#define B200GDN_NORM_GATE_SIGMOID 1u
+typedef struct b200gdn_norm_gate_args {
+  int32_t struct_bytes;
+  int32_t D;
+  int64_t rows;
+  uint32_t flags;
+  int32_t dtype;                 /* 0 = bf16, 1 = fp16, 2 = fp32: x, g, y, dy, dx, dg */
+  float eps;
+  const void* x;                 /* [rows, D] */
+  const void* g;                 /* [rows, D] */
+  const float* weight;           /* [D] or NULL */
+  const float* bias;             /* [D] or NULL */
+  void* y;                       /* [rows, D] (forward) */
+  float* rstd;                   /* [rows]: written by the forward pass, read by the backward pass */
+  const void* dy;
+  void* dx;
+  void* dg;
+  float* dweight;                /* [D] or NULL */
+  float* dbias;                  /* [D] or NULL */
+  float* partials;
+} b200gdn_norm_gate_args;
+int b200gdn_norm_gate_fwd(const b200gdn_norm_gate_args* args, void* stream);
+int b200gdn_norm_gate_bwd(const b200gdn_norm_gate_args* args, void* stream);
+int b200gdn_norm_gate_ctas(int64_t rows);
+
 /* Bytes of forward-saved tensors and of backward workspace for a problem (what the caller allocates). */
 int64_t b200gdn_saved_bytes(int32_t rows, int32_t H, int32_t HV, int32_t K, int32_t V, int32_t n_chunks);
 int64_t b200gdn_bwd_workspace_bytes(int32_t rows, int32_t H, int32_t HV, int32_t K, int32_t V, int32_t n_chunks);

@@ -539,3 +539,49 @@ def random_cu_seqlens(n_seq: int, total: int, lo: int, hi: int, seed: int = 0) -
     for x in lens.tolist():
         cu.append(cu[-1] + int(x))
     return cu
+
+
+# --------------------------------------------------------------------------- the steps either side of the mixer
+def causal_conv1d_ref(x, weight, bias=None, residual=None, initial_state=None, activation=None, cu_seqlens=None,
+                      output_final_state=False):
+    """Short causal depthwise convolution per sequence (the reference's torch statement of it,
+    tests/modules/test_conv.py:31-73, generalised to packed sequences and the ``[N,D,W]`` cache of
+    fla/modules/conv/causal_conv1d.py:17-160): ``y[t,d] = act(bias[d] + sum_w weight[d,w] x[t-(W-1)+w, d])`` with the
+    inputs before a sequence taken from the last W-1 cache entries (zero without a cache); ``final_state[n,d,:]`` =
+    the last W inputs.  x ``[B,T,D]``; differentiable (torch autograd is the gradient oracle)."""
+    B, T, D = x.shape
+    W = weight.shape[-1]
+    xs = x.reshape(B * T, D)
+    bounds = seq_bounds(B, T, cu_seqlens)
+    ys, finals, pos = [], [], 0
+    for n, (s, e) in enumerate(bounds):
+        if s > pos:                                                               # rows that belong to no sequence
+            ys.append(torch.zeros(s - pos, D, dtype=x.dtype))
+        seq = xs[s:e].transpose(0, 1)[None]                                       # [1,D,L]
+        cache = torch.zeros(1, D, W, dtype=x.dtype) if initial_state is None else initial_state[n:n + 1].to(x.dtype)
+        full = torch.cat([cache, seq], dim=-1)                                    # W cache entries, then the sequence
+        out = F.conv1d(full, weight.to(x.dtype)[:, None, :], None if bias is None else bias.to(x.dtype), groups=D)
+        out = out[..., 1:]                                                        # output of token t sits at index t + 1
+        if activation in ('silu', 'swish'):
+            out = F.silu(out)
+        ys.append(out[0].transpose(0, 1))
+        finals.append(full[..., -W:])
+        pos = e
+    if pos < B * T:
+        ys.append(torch.zeros(B * T - pos, D, dtype=x.dtype))
+    y = torch.cat(ys, 0).reshape(B, T, D)
+    if residual is not None:
+        y = y + residual
+    return (y, torch.cat(finals, 0)) if output_final_state else (y, None)
+
+
+def rms_norm_gated_ref(x, g, weight=None, bias=None, activation='swish', eps=1e-6):
+    """``(x rstd weight + bias) act(g)`` over the last dimension, rstd = 1/sqrt(mean(x^2) + eps), act = g sigmoid(g)
+    (swish / silu) or sigmoid(g)  (fla/modules/fused_norm_gate.py:36-124, RMS form without residual)."""
+    rstd = torch.rsqrt(x.square().mean(-1, keepdim=True) + eps)
+    y = x * rstd
+    if weight is not None:
+        y = y * weight
+    if bias is not None:
+        y = y + bias
+    return y * (torch.sigmoid(g) if activation == 'sigmoid' else g * torch.sigmoid(g))

@@ -122,3 +122,64 @@ def test_fold_kernels_match_the_host_fold():
         assert torch.allclose(got.cpu(), want, rtol=1e-4, atol=1e-4)
     M, x, b = dev_g[0, :, :, :K].contiguous(), dev_g[1, :, :, K:].contiguous(), dev_g[2, :, :, K:].contiguous()
     assert torch.allclose(affine_apply(M, x, b, True).cpu(), host(M.cpu(), x.cpu(), b.cpu(), True).float(), rtol=1e-4, atol=1e-4)
+
+
+def _conv_worker(rank, world, port, q):
+    import torch.distributed as dist
+    from b200gdn import build_cp_context
+    from b200gdn.modules import causal_conv1d
+    torch.cuda.set_device(rank)
+    dev = torch.device('cuda', rank)
+    dist.init_process_group('nccl', init_method=f'tcp://127.0.0.1:{port}', rank=rank, world_size=world, device_id=dev)
+    try:
+        T, D, W = 512, 192, 4
+        cu = [0, 100, 255, 258, 512]   # sequences cut by the shard boundary, and one that starts 2 tokens before it
+        gen = torch.Generator().manual_seed(23)
+        x = torch.randn(1, T, D, generator=gen).to(dev)
+        w = (torch.randn(D, W, generator=gen) * 0.5).to(dev)
+        b = torch.randn(D, generator=gen).to(dev)
+        dy = torch.randn(1, T, D, generator=gen).to(dev)
+        cu_t = torch.tensor(cu, dtype=torch.long, device=dev)
+        ref = [t.clone().requires_grad_(True) for t in (x, w, b)]
+        y_ref, _ = causal_conv1d(*ref, activation='silu', cu_seqlens=cu_t)
+        y_ref.backward(dy)
+        P = T // world
+        sl = slice(rank * P, (rank + 1) * P)
+        ctx = build_cp_context(cu_t, group=dist.group.WORLD, conv1d_kernel_size=W, cu_seqlens_cpu=torch.tensor(cu, dtype=torch.long))
+        loc = [x[:, sl].clone().requires_grad_(True), w.clone().requires_grad_(True), b.clone().requires_grad_(True)]
+        y, _ = causal_conv1d(*loc, activation='silu', cp_context=ctx)
+        y.backward(dy[:, sl])
+        dw, db = loc[1].grad.clone(), loc[2].grad.clone()
+        dist.all_reduce(dw)
+        dist.all_reduce(db)
+        errs = dict(y=float((y - y_ref[:, sl]).abs().max()), dx=float((loc[0].grad - ref[0].grad[:, sl]).abs().max()),
+                    dw=float((dw - ref[1].grad).abs().max() / ref[1].grad.abs().max()),
+                    db=float((db - ref[2].grad).abs().max() / ref[2].grad.abs().max()))
+        q.put((rank, errs))
+    except Exception as e:
+        import traceback
+        q.put((rank, 'ERROR ' + repr(e) + traceback.format_exc()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize('world', [2, 4])
+def test_context_parallel_convolution_matches_single_gpu(world):
+    """The convolution in front of the mixer under context parallelism: every rank's first sequence starts from the
+    previous rank's last W-1 tokens, whose gradient flows back to that rank (tests/context_parallel of the reference
+    checks its conv the same way against a single-GPU run)."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f'needs {world} GPUs')
+    import torch.multiprocessing as mp
+    ctx = mp.get_context('spawn')
+    q = ctx.Queue()
+    port = 29900 + os.getpid() % 90 + world
+    procs = [ctx.Process(target=_conv_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=600) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, errs in res:
+        assert not isinstance(errs, str), f'rank {rank}: {errs}'
+        assert errs['y'] < 1e-5 and errs['dx'] < 1e-5 and errs['dw'] < 1e-5 and errs['db'] < 1e-5, (rank, errs)

@@ -132,3 +132,39 @@ def test_oracle_against_reference_triton_path(name):
         assert O.err_ratio(gr[n], gold[n]) < 0.008, n
     for n in ('dg', 'dbeta'):
         assert O.err_ratio(gr[n], gold[n]) < 0.02, n
+
+
+@pytest.mark.parametrize('name', ['conv_w4_silu', 'conv_w3_plain', 'conv_w2_short'])
+def test_conv_oracle_matches_reference_fixture(name):
+    """The convolution oracle against the reference's own torch statement (fixtures by tests/golden/make_modules_golden.py):
+    outputs, final state and all gradients."""
+    from tests.golden.make_modules_golden import CONV_CASES
+    B, T, D, W, act, has_bias, has_cache = CONV_CASES[name]
+    gold = {k: torch.from_numpy(v) for k, v in np.load(os.path.join(GOLD, name + '.npz')).items()}
+    x = gold['x'].clone().requires_grad_(True)
+    w = gold['w'].clone().requires_grad_(True)
+    b = gold['b'].clone().requires_grad_(True) if has_bias else None
+    cache = None
+    if has_cache:   # the reference's test cache holds W-1 entries; the operator's cache has W (the oldest is unused)
+        c = gold['cache'].clone().requires_grad_(True)
+        cache = torch.cat([torch.zeros(B, D, 1, dtype=c.dtype), c], dim=-1)
+    y, final = O.causal_conv1d_ref(x, w, b, None, cache, act, None, True)
+    (y * gold['dy']).sum().backward()
+    assert torch.allclose(y, gold['y'], atol=1e-10)
+    assert torch.allclose(final[..., 1:], gold['final'], atol=1e-12)
+    assert torch.allclose(x.grad, gold['dx'], atol=1e-10) and torch.allclose(w.grad, gold['dw'], atol=1e-9)
+    if has_bias:
+        assert torch.allclose(b.grad, gold['db'], atol=1e-9)
+    if has_cache:
+        assert torch.allclose(c.grad, gold['dcache'], atol=1e-10)
+
+
+def test_rms_norm_gated_oracle_against_plain_torch():
+    """The gated-norm oracle against torch's own rms_norm and activations, as the reference's test builds its
+    expectation (tests/modules/test_layernorm_gated.py:82-116)."""
+    gen = torch.Generator().manual_seed(3)
+    x, g = torch.randn(5, 7, 128, generator=gen, dtype=torch.float64), torch.randn(5, 7, 128, generator=gen, dtype=torch.float64)
+    w = torch.randn(128, generator=gen, dtype=torch.float64)
+    for act, fn in (('swish', torch.nn.functional.silu), ('sigmoid', torch.sigmoid)):
+        want = torch.nn.functional.rms_norm(x, (128,), w, eps=1e-5) * fn(g)
+        assert torch.allclose(O.rms_norm_gated_ref(x, g, w, None, act, 1e-5), want, atol=1e-12)
