@@ -2,7 +2,7 @@
 """Benchmark of the chunked gated delta rule on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload train|fwd|varlen|heads|cp|decode|layer]
+                    [--workload train|fwd|varlen|heads|cp|decode|layer|modules]
 
 Every run prints ONE JSON line.  The default workload (``train``) is the headline: one "step" is one forward +
 backward pass of chunk_gated_delta_rule over one synthetic batch of B=4, T=4096, H=HV=16, K=V=128 (bf16 q/k/v,
@@ -16,7 +16,8 @@ parallel, checked against a single-GPU run before it is timed).
 The other workloads time the remaining configurations of the specification through the same public API:
 ``fwd`` (forward only), ``varlen`` (16 packed sequences, 16 q/k + 32 value heads, forward + backward), ``heads``
 (strong scaling by heads), ``cp`` (context parallel), ``decode`` (single-token steps, batch 1..256, state in place),
-``layer`` (the headline shape called the way fla.layers.GatedDeltaNet calls the op).
+``layer`` (the headline shape called the way fla.layers.GatedDeltaNet calls the op), ``modules`` (the short convolution
+and the gated RMS norm either side of the mixer).
 
 ``--impl reference`` times the reference's own naive recurrence (from a reference install under baseline/_ref when
 there is one, else its restatement under oracle/) on a bounded sample of the headline workload on the host cores.
@@ -221,7 +222,7 @@ def timed(fn, steps, warmup, dev, barrier):
 
 
 def err_ratio(ref, out):
-    ref, out = ref.float(), out.float()
+    ref, out = ref.detach().float(), out.detach().float()
     return float((ref - out).square().mean().sqrt() / (ref.square().mean().sqrt() + 1e-12))
 
 
@@ -832,13 +833,55 @@ def workload_decode(args, D):
         print(json.dumps(line))
 
 
+def workload_modules(args, D):
+    """The two steps either side of the mixer at the headline shape, forward + backward each: the short causal convolution
+    (kernel 4, SiLU) over the q / k / v projections [4, 4096, 2048] and the gated RMS norm over [4, 4096, 16, 128]; both
+    are HBM streaming, reported as bytes moved (every tensor once per pass) over device time."""
+    from b200gdn.modules import causal_conv1d, rms_norm_gated
+    peaks = load_peaks()
+    dev = D.dev
+    gen = torch.Generator(device=dev).manual_seed(3)
+    Dc, Wc = H * K, 4
+    x = torch.randn(B, T, Dc, device=dev, generator=gen).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(Dc, Wc, device=dev, generator=gen) * 0.5).requires_grad_(True)
+    bias = torch.randn(Dc, device=dev, generator=gen).requires_grad_(True)
+    dy = torch.randn(B, T, Dc, device=dev, generator=gen).to(torch.bfloat16)
+
+    def conv_step():
+        y, _ = causal_conv1d(x, w, bias, activation='silu')
+        y.backward(dy)
+    o = torch.randn(B, T, HV, V, device=dev, generator=gen).to(torch.bfloat16).requires_grad_(True)
+    gate = torch.randn(B, T, HV, V, device=dev, generator=gen).to(torch.bfloat16).requires_grad_(True)
+    nw = torch.ones(V, device=dev, requires_grad=True)
+    do = torch.randn(B, T, HV, V, device=dev, generator=gen).to(torch.bfloat16)
+
+    def norm_step():
+        rms_norm_gated(o, gate, nw, eps=1e-5).backward(do)
+    ms_conv = timed(conv_step, args.steps, args.warmup, dev, D.barrier) / args.steps
+    ms_norm = timed(norm_step, args.steps, args.warmup, dev, D.barrier) / args.steps
+    nb = B * T * Dc * 2
+    conv_bytes = 2 * nb + 3 * nb + (B * T // 64) * Dc * (Wc + 1) * 4 * 2   # x -> y ; x, dy -> dx ; parameter partials
+    norm_bytes = 3 * nb + 5 * nb                                             # x, g -> y ; x, g, dy -> dx, dg
+    if D.rank == 0:
+        line = base_line(args, D, 'tokens/s of the short convolution + gated RMS norm around the mixer, fwd+bwd (B4 T4096 H16 D128 bf16)',
+                         B * T / ((ms_conv * 3 + ms_norm) * 1e-3), ms_conv * 3 + ms_norm, 'weak',
+                         'causal_conv1d (W=4, SiLU, bias) on q, k, v [4,4096,2048] each and rms_norm_gated on [4,4096,16,128], forward + backward',
+                         parallelism='single GPU')
+        line['roofline'] = {'kernel': 'conv_fwd + conv_bwd', 'bound': 'hbm', 'achieved': conv_bytes / (ms_conv * 1e-3) / 1e9, 'peak': peaks['hbm'],
+                            'unit': 'GB/s', 'frac': conv_bytes / (ms_conv * 1e-3) / 1e9 / peaks['hbm'], 'traffic': None, 'peak_source': peaks['source']}
+        line['modules'] = {'conv_fwd_bwd_ms': ms_conv, 'conv_GB/s': conv_bytes / (ms_conv * 1e-3) / 1e9,
+                           'norm_gate_fwd_bwd_ms': ms_norm, 'norm_gate_GB/s': norm_bytes / (ms_norm * 1e-3) / 1e9,
+                           'norm_gate_hbm_frac': norm_bytes / (ms_norm * 1e-3) / 1e9 / peaks['hbm']}
+        print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--workload', default='train', choices=['train', 'fwd', 'varlen', 'heads', 'cp', 'decode', 'layer'])
+    ap.add_argument('--workload', default='train', choices=['train', 'fwd', 'varlen', 'heads', 'cp', 'decode', 'layer', 'modules'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-gpu-baseline', action='store_true')
     ap.add_argument('--worker', default=None, help=argparse.SUPPRESS)
@@ -860,6 +903,8 @@ def main():
         workload_heads(args, D)
     elif args.workload == 'cp':
         workload_cp(args, D)
+    elif args.workload == 'modules':
+        workload_modules(args, D)
     else:
         workload_decode(args, D)
     D.close()

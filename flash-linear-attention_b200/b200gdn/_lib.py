@@ -94,6 +94,14 @@ CONV_SILU = 1
 NORM_GATE_SIGMOID = 1
 
 
+class PrefixArgs(C.Structure):
+    _fields_ = [
+        ('struct_bytes', C.c_int32), ('HV', C.c_int32), ('K', C.c_int32), ('V', C.c_int32),
+        ('n_chains', C.c_int32), ('reverse', C.c_int32), ('identity', C.c_int32),
+        ('table', _p), ('M', _p), ('h', _p), ('x0', _p), ('out', _p), ('last', _p),
+    ]
+
+
 class FoldArgs(C.Structure):
     _fields_ = [
         ('struct_bytes', C.c_int32), ('HV', C.c_int32), ('K', C.c_int32), ('V', C.c_int32),
@@ -106,7 +114,7 @@ EXPORTS = (
     'b200gdn_chunk_fwd', 'b200gdn_chunk_bwd', 'b200gdn_recurrent_fwd', 'b200gdn_affine_apply',
     'b200gdn_saved_bytes', 'b200gdn_bwd_workspace_bytes', 'b200gdn_last_launch_count',
     'b200gdn_abi_version', 'b200gdn_last_error', 'b200gdn_device_status', 'b200gdn_prep_fwd', 'b200gdn_prep_bwd',
-    'b200gdn_selftest_wait_expiry', 'b200gdn_chunk_fwd_static', 'b200gdn_cp_fold',
+    'b200gdn_selftest_wait_expiry', 'b200gdn_chunk_fwd_static', 'b200gdn_cp_fold', 'b200gdn_cp_prefix',
     'b200gdn_conv_fwd', 'b200gdn_conv_bwd', 'b200gdn_norm_gate_fwd', 'b200gdn_norm_gate_bwd', 'b200gdn_norm_gate_ctas',
 )
 
@@ -132,7 +140,7 @@ def load():
                 '(or __graft_entry__.build()). There is no fallback path.')
         lib = C.CDLL(LIB_PATH)
         for name in ('b200gdn_chunk_fwd', 'b200gdn_chunk_bwd', 'b200gdn_recurrent_fwd', 'b200gdn_affine_apply',
-                     'b200gdn_prep_fwd', 'b200gdn_prep_bwd', 'b200gdn_chunk_fwd_static', 'b200gdn_cp_fold',
+                     'b200gdn_prep_fwd', 'b200gdn_prep_bwd', 'b200gdn_chunk_fwd_static', 'b200gdn_cp_fold', 'b200gdn_cp_prefix',
                      'b200gdn_conv_fwd', 'b200gdn_conv_bwd', 'b200gdn_norm_gate_fwd', 'b200gdn_norm_gate_bwd'):
             fn = getattr(lib, name)
             fn.restype = C.c_int

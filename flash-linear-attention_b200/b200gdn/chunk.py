@@ -12,7 +12,7 @@ from typing import Optional
 import torch
 
 from . import _lib
-from .index import tables_for
+from .index import split_plan_for, tables_for
 
 _SUPPORTED_HEAD_DIMS = ((64, 64), (128, 128))
 
@@ -162,6 +162,16 @@ def carve(dev, zero, *specs):
     return out
 
 
+def prefix_chains(plan, M, h, x0, out, K, V, reverse: bool, stream: int, last=None, identity: bool = False) -> None:
+    """b200gdn_cp_prefix over the chains of a split plan: the start state (reverse: the end gradient) of every piece."""
+    a = _lib.PrefixArgs()
+    a.HV, a.K, a.V = M.shape[1], K, V
+    a.n_chains, a.reverse, a.identity = plan.n_chains, int(reverse), int(identity)
+    a.table, a.M, a.h, a.x0 = plan.chains.data_ptr(), M.data_ptr(), _lib.ptr(h), _lib.ptr(x0)
+    a.out, a.last = _lib.ptr(out), _lib.ptr(last)
+    _lib.call('b200gdn_cp_prefix', a, stream)
+
+
 class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     """Autograd node around b200gdn_chunk_fwd / b200gdn_chunk_bwd
     (the role of fla/ops/gated_delta_rule/chunk.py:253-392)."""
@@ -180,8 +190,11 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             h0 = None if initial_state is None else initial_state.float().contiguous()
             B, T, H, K = qb.shape
             HV, V = vb.shape[2], vb.shape[3]
-            tables = tables_for(B, T, cu_seqlens, cu_seqlens_cpu, dev)
-            n_chunks, n_seq = tables[2]
+            # few sequences and heads: long sequences are cut into pieces that are scanned concurrently
+            plan = split_plan_for(B, T, cu_seqlens, cu_seqlens_cpu, dev, HV, V // 64)
+            tables = plan.tables if plan is not None else tables_for(B, T, cu_seqlens, cu_seqlens_cpu, dev)
+            n_chunks, n_seq = tables[2]          # n_seq counts pieces under a split plan
+            n_real = plan.n_chains if plan is not None else n_seq
             rows = B * T
             a = new_chunk_args(qb, kb, vb, scale, tables)
             bf16, f32 = torch.bfloat16, torch.float32
@@ -202,12 +215,31 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             a.options, a.A_log, a.dt_bias = options, _lib.ptr(A_log_f), _lib.ptr(bias_f)
             a.o, a.ht = o.data_ptr(), _lib.ptr(ht)
             a.gamma, a.A, a.qk, a.w, a.u, a.h, a.v_new = (_lib.ptr(x) for x in (gamma, A, qk, w, u, h, v_new))
-            _lib.call('b200gdn_chunk_fwd', a, _stream(qb))
+            st = _stream(qb)
+            if plan is None:
+                _lib.call('b200gdn_chunk_fwd', a, st)
+            else:
+                a.stage_mask = _lib.FWD_INTRA
+                _lib.call('b200gdn_chunk_fwd', a, st)
+                # the affine map (M, h) of every piece but the last of its sequence, from a zero start state
+                h_pre, M_pre, h0_v = carve(dev, False, ((plan.n_pre, HV, K, V), f32), ((plan.n_pre, HV, K, K), f32),
+                                           ((n_seq, HV, K, V), f32))
+                p = new_chunk_args(qb, kb, vb, scale, (tables[0], plan.pre_fwd, (n_chunks, plan.n_pre)))
+                p.gamma, p.w, p.u, p.ht, p.cp_M = gamma.data_ptr(), w.data_ptr(), u.data_ptr(), h_pre.data_ptr(), M_pre.data_ptr()
+                p.stage_mask = _lib.FWD_SCAN
+                _lib.call('b200gdn_chunk_fwd', p, st)
+                prefix_chains(plan, M_pre, h_pre, h0, h0_v, K, V, False, st)
+                a.h0 = h0_v.data_ptr()
+                a.stage_mask = _lib.FWD_SCAN | _lib.FWD_OUT
+                _lib.call('b200gdn_chunk_fwd', a, st)
+                if ht is not None:
+                    ht = ht.index_select(0, plan.last_piece)
         if need_grad:
             ctx.save_for_backward(qb, kb, vb, bf, gamma, A, qk, w, h, v_new, tables[0], tables[1],
                                   gf if (options & _lib.PREP_GATE) else None, A_log_f, bias_f)
         ctx.meta = (scale, n_chunks, n_seq, initial_state is not None, in_dtypes, options,
                     None if A_log is None else A_log.dtype, None if dt_bias is None else dt_bias.dtype, zero)
+        ctx.plan = plan
         return o.to(out_dtype), ht
 
     @staticmethod
@@ -253,7 +285,25 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             if gate:
                 a.g, a.A_log, a.dt_bias = gf.data_ptr(), A_log_f.data_ptr(), _lib.ptr(bias_f)
                 a.gate_partials, a.dA_log, a.ddt_bias = gate_partials.data_ptr(), dA_log.data_ptr(), _lib.ptr(ddt_bias)
-            _lib.call('b200gdn_chunk_bwd', a, _stream(qb))
+            st = _stream(qb)
+            plan = ctx.plan
+            if plan is None:
+                _lib.call('b200gdn_chunk_bwd', a, st)
+            else:
+                # the backward affine map (dM, dh) of every piece but the first of its sequence, from a zero end gradient;
+                # the pre-scan forms dv_local on chip and stores neither dv2 nor dh
+                dh_pre, dM_pre, dht_v = carve(dev, False, ((plan.n_pre, HV, K, V), f32), ((plan.n_pre, HV, K, K), f32),
+                                              ((n_seq, HV, K, V), f32))
+                p = new_chunk_args(qb, kb, vb, scale, (chunk_meta, plan.pre_bwd, (n_chunks, plan.n_pre)))
+                p.gamma, p.w, p.qk, p.d_o = gamma.data_ptr(), w.data_ptr(), qk.data_ptr(), dob.data_ptr()
+                p.dh0, p.cp_dM = dh_pre.data_ptr(), dM_pre.data_ptr()
+                p.stage_mask = _lib.BWD_DVLOCAL | _lib.BWD_SCAN
+                _lib.call('b200gdn_chunk_bwd', p, st)
+                prefix_chains(plan, dM_pre, dh_pre, dhtf, dht_v, K, V, True, st)
+                a.dht = dht_v.data_ptr()
+                _lib.call('b200gdn_chunk_bwd', a, st)
+                if dh0 is not None:
+                    dh0 = dh0.index_select(0, plan.first_piece)
         qd, kd, vd, gd, bd = in_dtypes
         if dA_log is not None:
             dA_log = dA_log.to(A_dtype)

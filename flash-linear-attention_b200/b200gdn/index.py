@@ -66,3 +66,95 @@ def tables_for(B: int, T: int, cu_seqlens: Optional[torch.Tensor], cu_seqlens_cp
         _cache.clear()
     _cache[key] = (out, cu_seqlens)
     return out
+
+
+# ------------------------------------------------------------------------------------------- sequence split
+# The state scans walk a sequence chunk by chunk, one CTA per (sequence, value head, 64 value columns).  With few
+# sequences and heads that leaves most of the GPU idle, so long sequences are cut into pieces that are scanned
+# concurrently (fla/ops/common/intracard_cp.py:139-180 does this for its forward pass): a pre-scan gives every piece
+# its affine map, a prefix chain turns the maps into the start state of every piece, and the regular scan then runs
+# over all pieces at once.  Pieces are whole numbers of chunks, so the chunking (and every chunk-local kernel) is
+# unchanged.
+SM_COUNT = 148
+MIN_PIECE_CHUNKS = 16        # a piece shorter than this does not pay for its pre-scan
+FORCE_PIECES = None          # tests: cut every sequence into (up to) this many pieces regardless of the heuristic
+_split_cache: dict = {}
+
+
+class SplitPlan:
+    """Virtual-sequence tables and the index tensors that tie the pieces of a sequence together."""
+    __slots__ = ('tables', 'n_pieces', 'n_pre', 'chains', 'n_chains', 'pre_fwd', 'pre_bwd', 'first_piece', 'last_piece',
+                 'pieces_per_seq')
+
+
+def piece_counts(chunks_per_seq, HV: int, slices: int):
+    """How many pieces each sequence is cut into: as many as fill the SMs once, in proportion to the sequence lengths."""
+    if FORCE_PIECES is not None:
+        return [max(1, min(int(FORCE_PIECES), int(c))) for c in chunks_per_seq]
+    slots = SM_COUNT // max(1, slices * HV)          # sequences' worth of scan CTAs that fit the device at once
+    n_real = sum(1 for c in chunks_per_seq if c > 0)
+    if slots < 2 or n_real >= slots:
+        return [1] * len(chunks_per_seq)
+    target = max(MIN_PIECE_CHUNKS, -(-sum(chunks_per_seq) // slots))   # chunks per piece
+    return [max(1, min(int(c) // MIN_PIECE_CHUNKS, int(round(c / target)))) if c > 0 else 1 for c in chunks_per_seq]
+
+
+def split_plan(bounds, HV: int, slices: int, device, rows: int) -> Optional[SplitPlan]:
+    """None when no sequence is worth cutting; otherwise the plan (device tensors) for these bounds."""
+    bounds = [(int(s), int(e)) for s, e in bounds]
+    chunks = [(e - s + CHUNK - 1) // CHUNK for s, e in bounds]
+    pieces = piece_counts(chunks, HV, slices)
+    if max(pieces, default=1) <= 1:
+        return None
+    vbounds, chains, pre_fwd, pre_bwd, first_piece, last_piece = [], [], [], [], [], []
+    n_pre = 0
+    for (s, e), c, P in zip(bounds, chunks, pieces):
+        first = len(vbounds)
+        base, rem = divmod(c, P)
+        start = s
+        for p in range(P):
+            n = base + (1 if p < rem else 0)
+            end = min(e, start + n * CHUNK) if p < P - 1 else e
+            vbounds.append((start, end))
+            start = end
+        chains.append((first, P, n_pre))
+        pre_fwd += list(range(first, first + P - 1))
+        pre_bwd += list(range(first + 1, first + P))
+        n_pre += P - 1
+        first_piece.append(first)
+        last_piece.append(first + P - 1)
+    cm, sm = build_tables(vbounds)
+    plan = SplitPlan()
+    tables = Tables((torch.from_numpy(cm).to(device), torch.from_numpy(sm).to(device), (cm.shape[0], sm.shape[0])))
+    tables.covered = bool(bounds) and bounds[0][0] == 0 and bounds[-1][1] == rows
+    plan.tables, plan.n_pieces, plan.n_pre, plan.n_chains = tables, len(vbounds), n_pre, len(bounds)
+    plan.chains = torch.tensor(chains, dtype=torch.int32).to(device)
+    plan.pre_fwd = torch.from_numpy(sm[pre_fwd]).contiguous().to(device)
+    plan.pre_bwd = torch.from_numpy(sm[pre_bwd]).contiguous().to(device)
+    plan.first_piece = torch.tensor(first_piece, dtype=torch.long).to(device)
+    plan.last_piece = torch.tensor(last_piece, dtype=torch.long).to(device)
+    plan.pieces_per_seq = pieces
+    return plan
+
+
+def split_plan_for(B: int, T: int, cu_seqlens, cu_seqlens_cpu, device, HV: int, slices: int) -> Optional[SplitPlan]:
+    """Memoised like tables_for (by shape, or by the identity of ``cu_seqlens``)."""
+    if cu_seqlens is None:
+        key = ('dense', B, T, HV, slices, FORCE_PIECES, str(device))
+        hit = _split_cache.get(key)
+        if hit is not None:
+            return hit[0]
+        bounds = [(b * T, (b + 1) * T) for b in range(B)]
+    else:
+        key = ('varlen', id(cu_seqlens), B * T, HV, slices, FORCE_PIECES, str(device))
+        hit = _split_cache.get(key)
+        if hit is not None and hit[1] is cu_seqlens:
+            return hit[0]
+        cpu = cu_seqlens_cpu if cu_seqlens_cpu is not None else cu_seqlens.cpu()
+        cu = cpu.to(torch.int64).tolist()
+        bounds = [(cu[i], cu[i + 1]) for i in range(len(cu) - 1)]
+    plan = split_plan(bounds, HV, slices, device, B * T)
+    if len(_split_cache) > 64:
+        _split_cache.clear()
+    _split_cache[key] = (plan, cu_seqlens)
+    return plan

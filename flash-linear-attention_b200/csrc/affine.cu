@@ -102,7 +102,71 @@ __global__ void cp_fold_kernel(const b200gdn_fold_args a) {
   for (int c = 0; c < CS / 2; ++c) a.out[((int64_t)hv * K + r) * V + c0 + ch + c] = acc[c];
 }
 
+// Chains of affine maps inside one GPU (a long sequence cut into pieces that are scanned concurrently): for every
+// chain c of the table, x = x0[c] (zeros, or the identity when x0 == NULL and identity != 0); out[first_out] = x; then
+// for t = 0 .. count-2:  x = M[j_t] x + h[j_t],  out[o_t] = x, with
+//   forward:  j_t = first_pre + t,              o_t = first_out + t + 1
+//   reverse:  j_t = first_pre + count - 2 - t,  o_t = first_out + count - 2 - t   (out[first_out + count - 1] = x0 first)
+// and, when `last` is given, last[c] = the chain's final x.  Same thread layout as the fold above.
+__global__ void cp_prefix_kernel(const b200gdn_prefix_args a) {
+  extern __shared__ float xs[];   // [2][K][CS]
+  const int K = a.K, V = a.V, hv = blockIdx.y, c0 = blockIdx.x * CS, chain = blockIdx.z;
+  const int tid = threadIdx.x, r = tid >> 1, ch = (tid & 1) * (CS / 2);
+  const int first_out = a.table[3 * chain], count = a.table[3 * chain + 1], first_pre = a.table[3 * chain + 2];
+  float acc[CS / 2];
+#pragma unroll
+  for (int c = 0; c < CS / 2; ++c) {
+    const int col = c0 + ch + c;
+    acc[c] = a.x0 ? a.x0[(((int64_t)chain * a.HV + hv) * K + r) * V + col] : ((a.identity && r == col) ? 1.f : 0.f);
+    xs[r * CS + ch + c] = acc[c];
+  }
+  auto emit = [&](int piece) {
+    if (a.out == nullptr) return;
+#pragma unroll
+    for (int c = 0; c < CS / 2; ++c) a.out[(((int64_t)piece * a.HV + hv) * K + r) * V + c0 + ch + c] = acc[c];
+  };
+  emit(a.reverse ? first_out + count - 1 : first_out);
+  __syncthreads();
+  int cur = 0;
+  for (int t = 0; t + 1 < count; ++t) {
+    const int j = a.reverse ? first_pre + count - 2 - t : first_pre + t;
+    const float* M = a.M + ((int64_t)j * a.HV + hv) * K * K;
+    const float* x = xs + cur * K * CS;
+#pragma unroll
+    for (int c = 0; c < CS / 2; ++c) acc[c] = a.h ? a.h[(((int64_t)j * a.HV + hv) * K + r) * V + c0 + ch + c] : 0.f;
+    for (int m = 0; m < K; m += 4) {
+      const float4 mv = *reinterpret_cast<const float4*>(&M[r * K + m]);
+      const float mm[4] = {mv.x, mv.y, mv.z, mv.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+#pragma unroll
+        for (int c = 0; c < CS / 2; ++c) acc[c] += mm[e] * x[(m + e) * CS + ch + c];
+    }
+    float* y = xs + (cur ^ 1) * K * CS;
+#pragma unroll
+    for (int c = 0; c < CS / 2; ++c) y[r * CS + ch + c] = acc[c];
+    emit(a.reverse ? first_out + count - 2 - t : first_out + t + 1);
+    __syncthreads();
+    cur ^= 1;
+  }
+  if (a.last != nullptr) {
+#pragma unroll
+    for (int c = 0; c < CS / 2; ++c) a.last[(((int64_t)chain * a.HV + hv) * K + r) * V + c0 + ch + c] = acc[c];
+  }
+}
+
 }  // namespace
+
+int launch_cp_prefix(const b200gdn_prefix_args& a, cudaStream_t st) {
+  const size_t smem = (size_t)2 * a.K * CS * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(cp_prefix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return set_error(B200GDN_ERR_CUDA, "cp_prefix: %s", cudaGetErrorString(e));
+  }
+  dim3 grid(a.V / CS, a.HV, a.n_chains);
+  cp_prefix_kernel<<<grid, 2 * a.K, smem, st>>>(a);
+  return check_launch("cp_prefix");
+}
 
 int launch_cp_fold(const b200gdn_fold_args& a, cudaStream_t st) {
   const size_t smem = (size_t)2 * a.K * CS * sizeof(float);

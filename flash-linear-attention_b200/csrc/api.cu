@@ -188,6 +188,22 @@ int b200gdn_cp_fold(const b200gdn_fold_args* a, void* stream) {
   return launch_cp_fold(*a, static_cast<cudaStream_t>(stream));
 }
 
+int b200gdn_cp_prefix(const b200gdn_prefix_args* a, void* stream) {
+  using namespace gdn;
+  g_launches = 0;
+  if (a == nullptr) return set_error(B200GDN_ERR_BAD_ARGUMENT, "cp_prefix: args is NULL");
+  if (a->struct_bytes != (int32_t)sizeof(b200gdn_prefix_args))
+    return set_error(B200GDN_ERR_BAD_ARGUMENT, "cp_prefix: struct_bytes %d != %zu (ABI mismatch)", a->struct_bytes,
+                     sizeof(b200gdn_prefix_args));
+  if (a->HV <= 0 || a->n_chains <= 0 || a->HV > 65535 || a->n_chains > 65535)
+    return set_error(B200GDN_ERR_BAD_ARGUMENT, "cp_prefix: bad sizes (HV=%d n_chains=%d)", a->HV, a->n_chains);
+  if ((a->K != 64 && a->K != 128 && a->K != 256) || a->V <= 0 || a->V % 32 != 0)
+    return set_error(B200GDN_ERR_UNSUPPORTED, "cp_prefix: K=%d V=%d (K in {64,128,256}, V a multiple of 32)", a->K, a->V);
+  REQUIRE(a->table, "cp_prefix"); REQUIRE(a->M, "cp_prefix");
+  if (a->out == nullptr && a->last == nullptr) return set_error(B200GDN_ERR_BAD_ARGUMENT, "cp_prefix: no output given");
+  return launch_cp_prefix(*a, static_cast<cudaStream_t>(stream));
+}
+
 int64_t b200gdn_saved_bytes(int32_t rows, int32_t H, int32_t HV, int32_t K, int32_t V, int32_t n_chunks) {
   (void)H;
   int64_t r = rows, hv = HV;

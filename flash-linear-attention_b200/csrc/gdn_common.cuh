@@ -86,6 +86,7 @@ int launch_bwd_wy(const b200gdn_chunk_args& a, cudaStream_t st);
 int launch_recurrent(const b200gdn_recurrent_args& a, cudaStream_t st);
 int launch_affine(const b200gdn_affine_args& a, cudaStream_t st);
 int launch_cp_fold(const b200gdn_fold_args& a, cudaStream_t st);
+int launch_cp_prefix(const b200gdn_prefix_args& a, cudaStream_t st);
 int launch_prep(const b200gdn_prep_args& a, cudaStream_t st, bool bwd);
 int launch_conv(const b200gdn_conv_args& a, cudaStream_t st, bool bwd);
 int launch_norm_gate(const b200gdn_norm_gate_args& a, cudaStream_t st, bool bwd);

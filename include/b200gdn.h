@@ -214,6 +214,30 @@ typedef struct b200gdn_fold_args {
 } b200gdn_fold_args;
 int b200gdn_cp_fold(const b200gdn_fold_args* args, void* stream);
 
+/* Prefix chains of affine maps inside one GPU: a long sequence is cut into pieces that are scanned concurrently (the
+ * idea of fla/ops/common/intracard_cp.py:139-180 with the merge of fla/ops/cp/chunk_delta_h.py:254-315).  A pre-scan
+ * gives piece j the pair (M[j], h[j]) with S_end = M[j] S_start + h[j]; this call turns them into the start state of
+ * every piece.  For chain c (one sequence) with table[c] = {first_out, count, first_pre}:
+ *   x = x0[c] (zeros when x0 == NULL; the identity when also `identity` != 0);  out[first_out] = x;
+ *   for t = 0 .. count-2:  x = M[first_pre + t] x + h[first_pre + t];  out[first_out + t + 1] = x.
+ * `reverse` walks the chain from its last piece to its first (the backward pass: out[first_out + count - 1] = x0,
+ * pair first_pre + count - 2 - t, result into out[first_out + count - 2 - t]).  `last[c]`, when given, receives the
+ * chain's final x (with h == NULL, identity and V == K: the product of the chain's matrices).
+ * M [n_pre,HV,K,K], h [n_pre,HV,K,V], x0 / last [n_chains,HV,K,V], out [n_pieces,HV,K,V], all fp32;
+ * K in {64,128,256}, V a multiple of 32. */
+typedef struct b200gdn_prefix_args {
+  int32_t struct_bytes;
+  int32_t HV, K, V;
+  int32_t n_chains, reverse, identity;
+  const int32_t* table;          /* device [n_chains][3] */
+  const float* M;
+  const float* h;                /* or NULL (zeros) */
+  const float* x0;               /* or NULL */
+  float* out;                    /* or NULL */
+  float* last;                   /* or NULL */
+} b200gdn_prefix_args;
+int b200gdn_cp_prefix(const b200gdn_prefix_args* args, void* stream);
+
 /* The three options fla.layers.GatedDeltaNet turns on (fla/layers/gated_deltanet.py:309-325), as one pass before the
  * chunk kernels and one pass after their backward:
  *   L2NORM        y = x rsqrt(sum x^2 + 1e-6) over K for q and k, fp32 math; rstd saved

@@ -607,3 +607,52 @@ def test_forward_stage_by_stage_equals_the_fused_scan(name):
     O.assert_close('o staged', fwd['o'], c['o'], 0.005)
     O.assert_close('o fused', fwd['o'], fused['o'], 0.005)
     O.assert_close('o fused vs staged', c['o'], fused['o'], 0.004)
+
+
+@pytest.mark.parametrize('pieces', [2, 3, 5])
+def test_sequence_split_equals_the_unsplit_scan(pieces):
+    """Long sequences cut into pieces that are scanned concurrently (pre-scan of each piece's affine map, prefix chain,
+    then the regular scan over all pieces): outputs, final state and every gradient against the oracle and against the
+    unsplit run, on ragged packed sequences with grouped value heads, an initial state and a final-state gradient."""
+    from b200gdn import chunk_gated_delta_rule, index
+    dev = 'cuda'
+    cu = [0, 37, 700, 700, 1500, 1563]
+    d = O.make_inputs(1, 1563, 2, 4, 128, 128, seed=29, cu_seqlens=cu)
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=dev)
+
+    def run():
+        leaves = [d[n].to(dev).to(torch.bfloat16).requires_grad_(True) for n in ('q', 'k', 'v')]
+        leaves += [d[n].to(dev).requires_grad_(True) for n in ('g', 'beta', 'h0')]
+        o, ht = chunk_gated_delta_rule(*leaves[:5], initial_state=leaves[5], output_final_state=True, cu_seqlens=cu_t)
+        torch.autograd.backward([o, ht], [d['do'].to(dev).to(torch.bfloat16), d['dht'].to(dev)])
+        return [o.float().cpu(), ht.cpu()] + [x.grad.float().cpu() for x in leaves]
+    plain = run()
+    index.FORCE_PIECES = pieces
+    try:
+        index._split_cache.clear()
+        plan = index.split_plan_for(1, 1563, cu_t, None, torch.device(dev), 4, 2)
+        assert plan is not None and max(plan.pieces_per_seq) == pieces
+        split = run()
+    finally:
+        index.FORCE_PIECES = None
+        index._split_cache.clear()
+    ro, rht, rg = O.naive_with_grads(*(d[n].to(torch.bfloat16).float() for n in ('q', 'k', 'v')), d['g'], d['beta'], 128 ** -0.5,
+                                     d['h0'], d['do'].to(torch.bfloat16).float(), d['dht'], cu_seqlens=cu)
+    want = [ro, rht, rg['dq'], rg['dk'], rg['dv'], rg['dg'], rg['dbeta'], rg['dh0']]
+    names = ('o', 'ht', 'dq', 'dk', 'dv', 'dg', 'dbeta', 'dh0')
+    for n, w_, s_, p_ in zip(names, want, split, plain):
+        O.assert_close(f'{n} split vs oracle', w_.float(), s_, REF_TOL[n])
+        O.assert_close(f'{n} split vs unsplit', p_, s_, 0.004)
+
+
+def test_sequence_split_heuristic_on_one_long_sequence():
+    """One sequence of 32768 tokens with 4 heads: the planner cuts it (the scans would otherwise occupy 8 of 148 SMs), and
+    the result agrees with the token-by-token kernel."""
+    from b200gdn import chunk_gated_delta_rule, fused_recurrent_gated_delta_rule, index
+    q, k, v, g, beta, do = _inputs(1, 32768, 4, 4, 128, 128, seed=31)
+    plan = index.split_plan_for(1, 32768, None, None, q.device, 4, 2)
+    assert plan is not None and plan.n_pieces > 1
+    o, ht = chunk_gated_delta_rule(q, k, v, g, beta, output_final_state=True)
+    o_r, ht_r = fused_recurrent_gated_delta_rule(q, k, v, g, beta=beta, output_final_state=True)
+    O.assert_close('o chunk (split) vs recurrent', o_r.float().cpu(), o.float().cpu(), 0.005)
+    O.assert_close('ht chunk (split) vs recurrent', ht_r.cpu(), ht.cpu(), 0.005)
