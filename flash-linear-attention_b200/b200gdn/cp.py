@@ -193,18 +193,38 @@ def collect_phase_times():
     return {n: sum(a.elapsed_time(b) for a, b in ev) / len(ev) for n, ev in PHASE_TIMES.items()}
 
 
+def _boundary_pair(plan, chain: int, M_pre, h_pre, first_pre: int, K: int, V: int, reverse: bool, stream: int, dev):
+    """(M, h) of a whole local sequence from the pairs of its pieces, which sit at consecutive positions
+    first_pre .. first_pre + pieces - 1 of the pre-scan's outputs: [HV, K, K + V] for the exchange."""
+    from .chunk import prefix_chains
+    HV = M_pre.shape[1]
+    P = plan.pieces_per_seq[chain]
+
+    class One:   # a one-chain table for b200gdn_cp_prefix
+        n_chains = 1
+        chains = torch.tensor([[0, P + 1, first_pre]], dtype=torch.int32, device=dev)
+    h_tot = torch.empty(1, HV, K, V, dtype=torch.float32, device=dev)
+    M_tot = torch.empty(1, HV, K, K, dtype=torch.float32, device=dev)
+    prefix_chains(One, M_pre, h_pre, None, None, K, V, reverse, stream, last=h_tot)
+    prefix_chains(One, M_pre, None, None, None, K, K, reverse, stream, last=M_tot, identity=True)
+    return torch.cat([M_tot[0], h_tot[0]], dim=-1)
+
+
 class ChunkGatedDeltaRuleCPFunction(torch.autograd.Function):
     """Forward and backward of the op on one rank's shard, with the prefix exchange in between the
     intra-chunk stage and the scan (fla/ops/gated_delta_rule/chunk.py:82-93, 183-200).
 
-    Per direction: ONE pre-scan launch gives the (h_ext, M) pair of the rank's boundary sequence (value slices and
-    transition-matrix slices side by side in the grid, as the reference's pre-process kernel does,
-    fla/ops/cp/chunk_delta_h.py:41-315), one all-gather exchanges the pairs, ONE launch folds the pairs of the
-    neighbouring ranks, and the regular (fused) scan runs from the folded state."""
+    Per direction: ONE pre-scan launch gives the (h_ext, M) pairs it needs (value slices and transition-matrix slices
+    side by side in the grid, as the reference's pre-process kernel does, fla/ops/cp/chunk_delta_h.py:41-315), one
+    all-gather exchanges the rank-level pairs, ONE launch folds the pairs of the neighbouring ranks, and the regular
+    (fused) scan runs from the folded state.  A shard with few sequences and heads is also cut into pieces that are
+    scanned concurrently (index.split_plan): the same pre-scan then covers every piece, the rank-level pair is the
+    composition of the boundary sequence's pieces, and a prefix chain gives every piece its start state."""
 
     @staticmethod
     def forward(ctx, q, k, v, g, beta, scale, cp_context):
-        from .chunk import carve, new_chunk_args, _stream
+        from .chunk import carve, new_chunk_args, prefix_chains, _stream
+        from .index import split_plan_for
         in_dtypes = (q.dtype, k.dtype, v.dtype, g.dtype, beta.dtype)
         dev = q.device
         group = cp_context.group
@@ -214,8 +234,9 @@ class ChunkGatedDeltaRuleCPFunction(torch.autograd.Function):
             gf, bf = g.float().contiguous(), beta.float().contiguous()
             B, T, H, K = qb.shape
             HV, V = vb.shape[2], vb.shape[3]
-            tables = tables_for(B, T, cp_context.cu_seqlens, cp_context.cu_seqlens_cpu, dev)
-            chunk_meta, seq_meta, (n_chunks, n_seq) = tables
+            plan = split_plan_for(B, T, cp_context.cu_seqlens, cp_context.cu_seqlens_cpu, dev, HV, V // 64)
+            tables = plan.tables if plan is not None else tables_for(B, T, cp_context.cu_seqlens, cp_context.cu_seqlens_cpu, dev)
+            chunk_meta, seq_meta, (n_chunks, n_seq) = tables      # n_seq counts pieces under a split plan
             rows = B * T
             bf16, f32 = torch.bfloat16, torch.float32
             zero = not tables.covered
@@ -232,24 +253,39 @@ class ChunkGatedDeltaRuleCPFunction(torch.autograd.Function):
             with _Phase('fwd_intra', dev):
                 _lib.call('b200gdn_chunk_fwd', a, st)
 
-            # (M, h_ext) of the last local sequence, zero start state; zeros when nothing continues
+            # pairs (M, h) from a zero start state: of every piece but the last of its sequence (split plan), and of the
+            # last local sequence('s last piece) when it continues on the next rank
+            send = not cp_context.is_last_rank
             with _Phase('fwd_prescan', dev):
-                if cp_context.is_last_rank:
-                    hm = torch.zeros(HV, K, K + V, dtype=f32, device=dev)
-                else:
-                    h_ext, M = carve(dev, False, ((1, HV, K, V), f32), ((1, HV, K, K), f32))
-                    p = new_chunk_args(qb, kb, vb, scale, (chunk_meta, seq_meta[n_seq - 1:n_seq], (n_chunks, 1)))
-                    p.gamma, p.w, p.u, p.ht, p.cp_M = gamma.data_ptr(), w.data_ptr(), u.data_ptr(), h_ext.data_ptr(), M.data_ptr()
+                rows_pre = [plan.pre_fwd] if plan is not None else []
+                if send:
+                    rows_pre.append(seq_meta[n_seq - 1:n_seq])
+                n_pre = sum(int(r.shape[0]) for r in rows_pre)
+                hm = torch.zeros(HV, K, K + V, dtype=f32, device=dev)
+                if n_pre > 0:
+                    pre = rows_pre[0] if len(rows_pre) == 1 else torch.cat(rows_pre, 0)
+                    h_pre, M_pre = carve(dev, False, ((n_pre, HV, K, V), f32), ((n_pre, HV, K, K), f32))
+                    p = new_chunk_args(qb, kb, vb, scale, (chunk_meta, pre, (n_chunks, n_pre)))
+                    p.gamma, p.w, p.u, p.ht, p.cp_M = gamma.data_ptr(), w.data_ptr(), u.data_ptr(), h_pre.data_ptr(), M_pre.data_ptr()
                     p.stage_mask = _lib.FWD_SCAN
                     _lib.call('b200gdn_chunk_fwd', p, st)
-                    hm = torch.cat([M[0], h_ext[0]], dim=-1)
+                    if send and plan is None:
+                        hm = torch.cat([M_pre[0], h_pre[0]], dim=-1)
+                    elif send:   # the last sequence's pieces are the last entries of the pre-scan
+                        last = plan.n_chains - 1
+                        hm = _boundary_pair(plan, last, M_pre, h_pre, n_pre - plan.pieces_per_seq[last], K, V, False, st, dev)
             with _Phase('fwd_exchange', dev):
                 gathered = exchange(hm, group)
             h0 = None
             with _Phase('fwd_fold', dev):
+                n_real = plan.n_chains if plan is not None else n_seq
                 if cp_context.pre_num_ranks > 0:
-                    h0 = torch.zeros(n_seq, HV, K, V, dtype=f32, device=dev)
+                    h0 = torch.zeros(n_real, HV, K, V, dtype=f32, device=dev)
                     fold_on_device(gathered, rank, cp_context.pre_num_ranks, K, True, h0[0])
+                if plan is not None:   # the start state of every piece
+                    h0_v = torch.empty(n_seq, HV, K, V, dtype=f32, device=dev)
+                    prefix_chains(plan, M_pre, h_pre, h0, h0_v, K, V, False, st)
+                    h0 = h0_v
 
             a.h0 = _lib.ptr(h0)
             a.q = qb.data_ptr()
@@ -259,15 +295,15 @@ class ChunkGatedDeltaRuleCPFunction(torch.autograd.Function):
                 _lib.call('b200gdn_chunk_fwd', a, st)
         ctx.save_for_backward(qb, kb, vb, bf, gamma, A, qk, w, h, v_new, chunk_meta, seq_meta)
         ctx.meta = (scale, n_chunks, n_seq, in_dtypes, zero)
-        ctx.cp_context = cp_context
+        ctx.cp_context, ctx.plan = cp_context, plan
         return o.to(q.dtype)
 
     @staticmethod
     def backward(ctx, do):
-        from .chunk import carve, new_chunk_args, _stream
+        from .chunk import carve, new_chunk_args, prefix_chains, _stream
         qb, kb, vb, bf, gamma, A, qk, w, h, v_new, chunk_meta, seq_meta = ctx.saved_tensors
         scale, n_chunks, n_seq, in_dtypes, zero = ctx.meta
-        cp_context = ctx.cp_context
+        cp_context, plan = ctx.cp_context, ctx.plan
         group = cp_context.group
         rank = dist.get_rank(group=group)
         dev = qb.device
@@ -287,26 +323,41 @@ class ChunkGatedDeltaRuleCPFunction(torch.autograd.Function):
             st = _stream(qb)
             tables = (chunk_meta, seq_meta, (n_chunks, n_seq))
 
-            # (M^T, dh_ext) of the first local sequence, zero end gradient; zeros when nothing precedes.  The pre-scan
-            # forms dv_local on chip and stores neither dv2 nor dh.
+            # backward pairs (dM, dh) from a zero end gradient: of the first local sequence('s first piece) when it
+            # continues from the previous rank, and of every piece but the first of its sequence (split plan).  The
+            # pre-scan forms dv_local on chip and stores neither dv2 nor dh.
+            send = not cp_context.is_first_rank
             with _Phase('bwd_prescan', dev):
-                if cp_context.is_first_rank:
-                    dhm = torch.zeros(HV, K, K + V, dtype=f32, device=dev)
-                else:
-                    dh_ext, dM = carve(dev, False, ((1, HV, K, V), f32), ((1, HV, K, K), f32))
-                    p = new_chunk_args(qb, kb, vb, scale, (chunk_meta, seq_meta[0:1], (n_chunks, 1)))
+                rows_pre = [seq_meta[0:1]] if send else []
+                if plan is not None:
+                    rows_pre.append(plan.pre_bwd)
+                n_pre = sum(int(r.shape[0]) for r in rows_pre)
+                dhm = torch.zeros(HV, K, K + V, dtype=f32, device=dev)
+                if n_pre > 0:
+                    pre = rows_pre[0] if len(rows_pre) == 1 else torch.cat(rows_pre, 0)
+                    dh_pre, dM_pre = carve(dev, False, ((n_pre, HV, K, V), f32), ((n_pre, HV, K, K), f32))
+                    p = new_chunk_args(qb, kb, vb, scale, (chunk_meta, pre, (n_chunks, n_pre)))
                     p.gamma, p.w, p.qk, p.d_o = gamma.data_ptr(), w.data_ptr(), qk.data_ptr(), dob.data_ptr()
-                    p.dh0, p.cp_dM = dh_ext.data_ptr(), dM.data_ptr()
+                    p.dh0, p.cp_dM = dh_pre.data_ptr(), dM_pre.data_ptr()
                     p.stage_mask = _lib.BWD_DVLOCAL | _lib.BWD_SCAN
                     _lib.call('b200gdn_chunk_bwd', p, st)
-                    dhm = torch.cat([dM[0], dh_ext[0]], dim=-1)
+                    if send and plan is None:
+                        dhm = torch.cat([dM_pre[0], dh_pre[0]], dim=-1)
+                    elif send:   # the first sequence's pieces are the first entries of the pre-scan
+                        dhm = _boundary_pair(plan, 0, dM_pre, dh_pre, 0, K, V, True, st, dev)
             with _Phase('bwd_exchange', dev):
                 gathered = exchange(dhm, group)
             dht = None
             with _Phase('bwd_fold', dev):
+                n_real = plan.n_chains if plan is not None else n_seq
                 if cp_context.post_num_ranks > 0:
-                    dht = torch.zeros(n_seq, HV, K, V, dtype=f32, device=dev)
-                    fold_on_device(gathered, rank, cp_context.post_num_ranks, K, False, dht[n_seq - 1])
+                    dht = torch.zeros(n_real, HV, K, V, dtype=f32, device=dev)
+                    fold_on_device(gathered, rank, cp_context.post_num_ranks, K, False, dht[n_real - 1])
+                if plan is not None:   # the end gradient of every piece
+                    dht_v = torch.empty(n_seq, HV, K, V, dtype=f32, device=dev)
+                    off = 1 if send else 0   # the plan's own pairs follow the boundary piece in the pre-scan's outputs
+                    prefix_chains(plan, dM_pre[off:], dh_pre[off:], dht, dht_v, K, V, True, st)
+                    dht = dht_v
 
             a = new_chunk_args(qb, kb, vb, scale, tables)
             a.beta, a.gamma, a.A, a.qk, a.w, a.h, a.v_new = (x.data_ptr() for x in (bf, gamma, A, qk, w, h, v_new))

@@ -60,7 +60,7 @@ struct ScanFwdSmem {
   static constexpr size_t o_os = o_vt + u_bytes;            // OUT: 2 x o staging [64][64]
   static constexpr size_t o_gam = o_os + (OUT ? 2 * u_bytes : 0);  // NSTAGE x 64 floats
   static constexpr size_t o_bar = o_gam + NSTAGE * BT * 4;
-  static constexpr size_t bytes = o_bar + (3 * NSTAGE + 7) * 8 + 16 + 1024;  // + alignment slack
+  static constexpr size_t bytes = o_bar + (3 * NSTAGE + 8) * 8 + 16 + 1024;  // + alignment slack
 };
 
 struct ScanFwdMaps {
@@ -82,8 +82,10 @@ __global__ void __launch_bounds__(NEPI + 64 + (OUT ? NOUT * 32 : 0))
   uint64_t* sb_ready = s_ready + 1;     // bf16 snapshot in shared memory
   uint64_t* v_ready = sb_ready + 1;     // V_acc done (MMA 1)
   uint64_t* vt_ready = v_ready + 1;     // v_new / V~ tiles written, decayed S back in TMEM
-  uint64_t* grp_ready = vt_ready + 1;   // OUT: O1 and O2 of a chunk done
-  uint64_t* o_free = grp_ready + 1;     // OUT: [2] the output warps have read the accumulator pair
+  // OUT, one pair of barriers per accumulator pair (chunk parity): a single barrier could complete two phases while a
+  // slow output warp still waits for the first, and a parity wait cannot tell a phase from the one two later
+  uint64_t* grp_ready = vt_ready + 1;   // [2] O1 and O2 of a chunk done
+  uint64_t* o_free = grp_ready + 2;     // [2] the output warps have read the accumulator pair
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_free + 2);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -110,7 +112,8 @@ __global__ void __launch_bounds__(NEPI + 64 + (OUT ? NOUT * 32 : 0))
     tc5::mbar_init(sb_ready, NEPI / 32);
     tc5::mbar_init(v_ready, 1);
     tc5::mbar_init(vt_ready, NEPI / 32);
-    tc5::mbar_init(grp_ready, 1);
+    tc5::mbar_init(&grp_ready[0], 1);
+    tc5::mbar_init(&grp_ready[1], 1);
     tc5::mbar_init(&o_free[0], NOUT);
     tc5::mbar_init(&o_free[1], NOUT);
     tc5::fence_mbar_init();
@@ -206,7 +209,7 @@ __global__ void __launch_bounds__(NEPI + 64 + (OUT ? NOUT * 32 : 0))
         if (OUT) {
           // O2 = P~ v_new, behind the second product: it runs while the epilogue warps convert S
           issue_mma_t<BT / 16>(TM_O2 + 64 * buf, Operand{pq_addr, BT, 0}, Operand{vn_addr0 + buf * (uint32_t)S::u_bytes, BT, 1}, 64, BV, 0);
-          tc5::mma_commit(grp_ready);
+          tc5::mma_commit(&grp_ready[buf]);
         }
         tc5::mma_commit(&empty[s]);   // every product that reads this stage's tiles has been issued before this commit
         if (st_vn && cm.len == BT) {
@@ -361,7 +364,7 @@ __global__ void __launch_bounds__(NEPI + 64 + (OUT ? NOUT * 32 : 0))
     for (int j = 0; j < nc; ++j) {
       const int s = j % NSTAGE, buf = j & 1;
       const ChunkMeta cm = load_chunk_meta(a.chunk_meta, c_first + j);
-      if (!tc5::mbar_wait(grp_ready, j & 1)) { failed = true; break; }
+      if (!tc5::mbar_wait(&grp_ready[buf], (j >> 1) & 1)) { failed = true; break; }
       tc5::fence_after_sync();
       // o = scale (O1 2^gamma_i + O2)
       float o1[2][16], o2[2][16];

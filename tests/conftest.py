@@ -26,3 +26,20 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if 'gpu' in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _no_bounded_wait_expired(request):
+    """After every GPU test: none of the kernels' bounded waits gave up (a silent expiry would leave wrong results that a
+    loose comparison might still accept).  The wait-expiry self-test clears the flag itself."""
+    yield
+    if 'gpu' not in request.keywords:
+        return
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return
+        import b200gdn
+    except Exception:
+        return
+    b200gdn.device_status()

@@ -18,6 +18,10 @@ SCENARIOS = {
     'cp4_complex': (4, 2048, [0, 300, 1500, 1600, 2048], 2, 2),
     'cp4_single': (4, 2048, [0, 2048], 1, 2),
     'cp8_single': (8, 8192, [0, 8192], 1, 1),
+    # the same with every local sequence also cut into pieces that are scanned concurrently (sixth field: pieces)
+    'cp2_cut_split3': (2, 4096, [0, 2700, 4096], 2, 2, 3),
+    'cp2_many_short_gva_split2': (2, 4096, [0, 400, 1000, 1600, 2130, 3100, 4096], 2, 4, 2),
+    'cp4_complex_split2': (4, 8192, [0, 1200, 6000, 6400, 8192], 2, 2, 2),
     # the long-context configuration at full size: one sequence of 524288 tokens, 16 heads (inputs made on the device)
     'cp2_long': (2, 524288, [0, 524288], 16, 16),
     'cp4_long': (4, 524288, [0, 524288], 16, 16),
@@ -29,8 +33,11 @@ def _worker(rank, world, port, name, q):
     import torch.distributed as dist
     from b200gdn import build_cp_context, chunk_gated_delta_rule
     from oracle import gdn_oracle as O
-    _, T, cu, H, HV = SCENARIOS[name]
+    _, T, cu, H, HV = SCENARIOS[name][:5]
     K = V = 128
+    if len(SCENARIOS[name]) > 5:
+        from b200gdn import index
+        index.FORCE_PIECES = SCENARIOS[name][5]
     torch.cuda.set_device(rank)
     dev = torch.device('cuda', rank)
     dist.init_process_group('nccl', init_method=f'tcp://127.0.0.1:{port}', rank=rank, world_size=world, device_id=dev)
@@ -52,11 +59,16 @@ def _worker(rank, world, port, name, q):
                 'do': torch.randn(1, T, HV, V, device=dev, generator=gen).to(torch.bfloat16),
             }
         cu_t = torch.tensor(cu, dtype=torch.long, device=dev)
-        # single-GPU run of the same operator on the whole batch
+        # single-GPU run of the same operator on the whole batch (never cut into pieces in the forced scenarios)
+        if len(SCENARIOS[name]) > 5:
+            index.FORCE_PIECES = 1
         ref_leaves = [full[n].clone().requires_grad_(True) for n in ('q', 'k', 'v', 'g', 'beta')]
         o_ref, _ = chunk_gated_delta_rule(*ref_leaves, cu_seqlens=cu_t)
         o_ref.backward(full['do'])
         # this rank's shard
+        if len(SCENARIOS[name]) > 5:
+            index.FORCE_PIECES = SCENARIOS[name][5]
+            index._split_cache.clear()
         P = T // world
         sl = slice(rank * P, (rank + 1) * P)
         ctx = build_cp_context(cu_t, group=dist.group.WORLD, cu_seqlens_cpu=torch.tensor(cu, dtype=torch.long))
@@ -66,11 +78,16 @@ def _worker(rank, world, port, name, q):
         o.backward(full['do'][:, sl])
         torch.cuda.synchronize()
         def ratio(a, b):   # the oracle's error ratio, evaluated on the device (the long case is 1 G elements)
-            a, b = a.float(), b.float()
+            a, b = a.detach().float(), b.detach().float()
             return float((a - b).square().mean().sqrt() / (a.square().mean().sqrt() + 1e-8))
         errs = {'o': ratio(o_ref[:, sl], o)}
         for nme, a, b in zip(('dq', 'dk', 'dv', 'dg', 'dbeta'), ref_leaves, leaves):
             errs[nme] = ratio(a.grad[:, sl], b.grad)
+        import b200gdn
+        b200gdn.device_status()   # no bounded device wait expired on this rank
+        if errs['o'] > 0.005:     # where along the shard the outputs differ (32 blocks), for the failure message
+            n = P // 32
+            errs['o_blocks'] = [round(ratio(o_ref[:, sl][:, i * n:(i + 1) * n], o[:, i * n:(i + 1) * n]), 4) for i in range(32)]
         q.put((rank, errs))
     except Exception as e:
         import traceback
@@ -98,7 +115,9 @@ def test_context_parallel_matches_single_gpu(name):
         assert not isinstance(errs, str), f'rank {rank}: {errs}'
         # same tolerance as the reference's CP test (assert_close ratio 3e-3 .. 5e-3 against its own single-GPU run)
         for n, e in errs.items():
-            assert e < 0.005, f'{name} rank {rank} {n}: {e}'
+            if n == 'o_blocks':
+                continue
+            assert e < 0.005, f'{name} rank {rank} {n}: {e} {errs}'
 
 
 def test_fold_kernels_match_the_host_fold():
