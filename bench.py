@@ -849,18 +849,18 @@ def workload_modules(args, D):
 
     def conv_step():
         y, _ = causal_conv1d(x, w, bias, activation='silu')
-        y.backward(dy)
+        torch.autograd.grad(y, (x, w, bias), dy)   # no accumulation into .grad: the step is the two kernels, nothing else
     o = torch.randn(B, T, HV, V, device=dev, generator=gen).to(torch.bfloat16).requires_grad_(True)
     gate = torch.randn(B, T, HV, V, device=dev, generator=gen).to(torch.bfloat16).requires_grad_(True)
     nw = torch.ones(V, device=dev, requires_grad=True)
     do = torch.randn(B, T, HV, V, device=dev, generator=gen).to(torch.bfloat16)
 
     def norm_step():
-        rms_norm_gated(o, gate, nw, eps=1e-5).backward(do)
+        torch.autograd.grad(rms_norm_gated(o, gate, nw, eps=1e-5), (o, gate, nw), do)
     ms_conv = timed(conv_step, args.steps, args.warmup, dev, D.barrier) / args.steps
     ms_norm = timed(norm_step, args.steps, args.warmup, dev, D.barrier) / args.steps
     nb = B * T * Dc * 2
-    conv_bytes = 2 * nb + 3 * nb + (B * T // 64) * Dc * (Wc + 1) * 4 * 2   # x -> y ; x, dy -> dx ; parameter partials
+    conv_bytes = 2 * nb + 3 * nb + (B * T // 32) * Dc * (Wc + 1) * 4 * 2   # x -> y ; x, dy -> dx ; parameter partials
     norm_bytes = 3 * nb + 5 * nb                                             # x, g -> y ; x, g, dy -> dx, dg
     if D.rank == 0:
         line = base_line(args, D, 'tokens/s of the short convolution + gated RMS norm around the mixer, fwd+bwd (B4 T4096 H16 D128 bf16)',

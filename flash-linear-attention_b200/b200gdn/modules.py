@@ -82,7 +82,7 @@ class CausalConv1dFunction(torch.autograd.Function):
             dw = torch.empty(D, W, dtype=torch.float32, device=dev)
             db = torch.empty(D, dtype=torch.float32, device=dev) if bf is not None else None
             dh0 = torch.empty(n_seq, D, W, dtype=xc.dtype, device=dev) if h0 is not None else None
-            partials = torch.empty(n_tiles, D, W + 1, dtype=torch.float32, device=dev)
+            partials = torch.empty(2 * n_tiles, D, W + 1, dtype=torch.float32, device=dev)
             a = _lib.ConvArgs()
             a.rows, a.D, a.W, a.n_seq, a.n_tiles = B * T, D, W, n_seq, n_tiles
             a.flags, a.dtype = flags, _DTYPE_CODE[xc.dtype]

@@ -312,7 +312,7 @@ typedef struct b200gdn_conv_args {
   float* dweight;                /* [D, W] or NULL */
   float* dbias;                  /* [D] or NULL */
   void* dinitial_state;          /* [n_seq, D, W] or NULL */
-  float* partials;               /* workspace fp32 [n_tiles, D, W + 1]; required with dweight */
+  float* partials;               /* workspace fp32 [2 n_tiles, D, W + 1]; required with dweight */
 } b200gdn_conv_args;
 int b200gdn_conv_fwd(const b200gdn_conv_args* args, void* stream);
 int b200gdn_conv_bwd(const b200gdn_conv_args* args, void* stream);

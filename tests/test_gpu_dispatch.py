@@ -63,3 +63,77 @@ def test_reference_dispatcher_reaches_the_backend():
     out = subprocess.run([sys.executable, '-c', _PROBE, pkg, REF_INSTALL], capture_output=True, text=True, timeout=900)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert 'dispatch-ok' in out.stdout
+
+
+_LIVE = r'''
+import json, os, sys
+os.environ['FLA_DISABLE_BACKEND_DISPATCH'] = '1'
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[2])
+import torch
+from fla.ops.gated_delta_rule import chunk_gated_delta_rule as ref_op
+from b200gdn import chunk_gated_delta_rule as our_op
+dev = 'cuda'
+nrm = torch.nn.functional.normalize
+
+
+def case(name, T, H, HV, cu, ref_kw):
+    gen = torch.Generator().manual_seed(len(name) + T)
+    N = 1 if cu is None else len(cu) - 1
+    B = 1 if cu is not None else 2
+    d = dict(q=nrm(torch.randn(B, T, H, 128, generator=gen), dim=-1).to(torch.bfloat16),
+             k=nrm(torch.randn(B, T, H, 128, generator=gen), dim=-1).to(torch.bfloat16),
+             v=torch.randn(B, T, HV, 128, generator=gen).to(torch.bfloat16),
+             g=torch.nn.functional.logsigmoid(torch.randn(B, T, HV, generator=gen)),
+             beta=torch.sigmoid(torch.randn(B, T, HV, generator=gen)),
+             h0=torch.randn(N if cu is not None else B, HV, 128, 128, generator=gen) * 0.1,
+             do=torch.randn(B, T, HV, 128, generator=gen).to(torch.bfloat16),
+             dht=torch.randn(N if cu is not None else B, HV, 128, 128, generator=gen) * 0.1)
+    cu_t = None if cu is None else torch.tensor(cu, dtype=torch.int32, device=dev)
+
+    def run(op, **kw):
+        leaves = [d[n].to(dev).requires_grad_(True) for n in ('q', 'k', 'v', 'g', 'beta', 'h0')]
+        o, ht = op(*leaves[:5], initial_state=leaves[5], output_final_state=True, cu_seqlens=cu_t, **kw)
+        torch.autograd.backward([o, ht], [d['do'].to(dev), d['dht'].to(dev)])
+        return [o, ht] + [x.grad for x in leaves]
+    ref, ours = run(ref_op, **ref_kw), run(our_op)
+    names = ('o', 'ht', 'dq', 'dk', 'dv', 'dg', 'dbeta', 'dh0')
+    out = {}
+    for n, r, x in zip(names, ref, ours):
+        r, x = r.float(), x.float()
+        out[n] = float((r - x).square().mean().sqrt() / (r.square().mean().sqrt() + 1e-12))
+    return out
+
+
+res = {
+    'dense_16_heads': case('dense', 2048, 16, 16, None, {}),
+    'ragged_gva': case('ragged', 6000, 8, 16, [0, 100, 1500, 1563, 4400, 4401, 6000], {}),
+    'reference_chunk_size_16': case('cs16', 700, 2, 2, [0, 300, 700], {'chunk_size': 16}),
+    'reference_chunk_size_32': case('cs32', 700, 2, 4, [0, 300, 700], {'chunk_size': 32}),
+}
+print('LIVE ' + json.dumps(res))
+'''
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF_INSTALL, 'fla')), reason='no reference install under baseline/_ref')
+def test_against_the_reference_triton_path_live():
+    """The reference's stock Triton chunk path (other back ends switched off), run on this GPU on the same seeded
+    tensors: 16 heads over 32 chunks with an initial state and a final-state gradient; ragged packed sequences (one of a
+    single token, one of 2900 tokens) with grouped value heads; and the reference run with chunk_size 16 and 32, whose
+    results this library (which always works on 64-token chunks) must reproduce.  Tolerances of the reference's own
+    tests (tests/ops/test_gdn.py:108-200)."""
+    import json
+    pkg = os.path.join(ROOT, 'flash-linear-attention_b200')
+    out = subprocess.run([sys.executable, '-c', _LIVE, pkg, REF_INSTALL], capture_output=True, text=True, timeout=1500)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    line = [ln for ln in out.stdout.splitlines() if ln.startswith('LIVE ')]
+    assert line, out.stdout[-2000:]
+    res = json.loads(line[0][5:])
+    gp = os.path.join(ROOT, 'gpurun_out')
+    if os.path.isdir(gp):
+        with open(os.path.join(gp, 'parity_vs_reference_triton.json'), 'w') as f:
+            json.dump(res, f, indent=1)
+    tol = dict(o=0.005, ht=0.005, dq=0.008, dk=0.008, dv=0.008, dh0=0.008, dg=0.02, dbeta=0.02)
+    for cname, errs in res.items():
+        for n, e in errs.items():
+            assert e <= tol[n], f'{cname}: {n} err-ratio {e} > {tol[n]}'
