@@ -92,7 +92,8 @@ def staged_bytes(R, C, NS):
 # stale with every kernel change: refresh it together with the profile.
 NCU_TRAFFIC = {
     'source': 'profiles/chunk_fwd_bwd_B4_T4096_H16_D128_tcgen05.md',
-    'bytes': {'intra_fwd': 256.8e6, 'bwd_dqk': 654.0e6, 'bwd_wy': 553.0e6},
+    'kernel_sources_commit': 'fa829f3',
+    'bytes': {'intra_fwd': 359.5e6, 'scan_out_fwd': 536.9e6, 'scan_dvl_bwd': 472.7e6, 'bwd_dqk': 650.1e6, 'bwd_wy': 549.8e6},
 }
 
 
@@ -658,9 +659,10 @@ def workload_train(args, D):
         step_tflops = tok_heads * (F_FWD + F_BWD) / (step_ms * 1e-3) / 1e12
         roof = tensor_roofline(top, tok_heads * STAGE_FLOPS[top], stages[top], peaks, NCU_TRAFFIC['bytes'].get(top))
         roof.update({
-            'traffic_source': NCU_TRAFFIC['source'],
+            'traffic_source': NCU_TRAFFIC['source'], 'traffic_kernel_sources_commit': NCU_TRAFFIC['kernel_sources_commit'],
             'step': {'TFLOP/s': step_tflops, 'frac': step_tflops / peaks['bf16'], 'frac_of_sustained': step_tflops / peaks['bf16_sustained'],
                      'algorithmic_bytes_step': alg, 'staged_bytes_step': sum(sb.values()), 'staged_over_algorithmic': sum(sb.values()) / alg,
+                     'traffic_step': sum(NCU_TRAFFIC['bytes'].values()), 'traffic_over_algorithmic': sum(NCU_TRAFFIC['bytes'].values()) / alg,
                      'GB/s_of_algorithmic_bytes': alg / (step_ms * 1e-3) / 1e9,
                      'hbm_frac_of_algorithmic_bytes': alg / (step_ms * 1e-3) / 1e9 / peaks['hbm'],
                      'hbm_frac_of_staged_bytes': sum(sb.values()) / (sum(stages.values()) * 1e-3) / 1e9 / peaks['hbm'],
@@ -787,7 +789,7 @@ def workload_decode(args, D):
     dev = D.dev
     Hn = 16
     table = []
-    for Bn in (1, 2, 4, 8, 16, 32, 64, 128, 256):
+    for Bn in args.decode_batches:
         n_sets = max(2, 512 // Bn)                      # pool of at least 512 MiB: four times L2
         pool = torch.randn(n_sets * Bn, Hn, K, V, device=dev) * 0.1
         d = device_inputs(Bn, 1, Hn, Hn, dev, seed=Bn)
@@ -821,9 +823,9 @@ def workload_decode(args, D):
     if D.rank == 0:
         top = table[-1]
         line = base_line(args, D, 'decode steps/s of fused_recurrent_gated_delta_rule (one token per sequence, [B,16,128,128] fp32 state in place)',
-                         top['steps_per_s'], top['us_per_step'] / 1e3, 'weak', 'decode sweep B = 1..256, H=HV=16 K=V=128, bf16 q/k/v, state pool of >= 512 MiB addressed by state_indices',
+                         top['steps_per_s'], top['us_per_step'] / 1e3, 'weak', 'decode sweep B = ' + ','.join(str(b) for b in args.decode_batches) + ', H=HV=16 K=V=128, bf16 q/k/v, state pool of >= 512 MiB addressed by state_indices',
                          parallelism='replicas only', timing='CUDA graph of one pass over the pool, CUDA events around the replays')
-        line['unit'] = 'steps/s (batch 256)'
+        line['unit'] = f"steps/s (batch {top['batch']})"
         line['dtype'] = 'f32'
         line['roofline'] = {'kernel': 'decode_stream_kernel', 'bound': 'hbm', 'achieved': top['GB/s'], 'peak': peaks['hbm'], 'unit': 'GB/s',
                             'frac': top['hbm_frac'], 'traffic': None, 'peak_source': peaks['source'],
@@ -857,8 +859,22 @@ def workload_modules(args, D):
 
     def norm_step():
         torch.autograd.grad(rms_norm_gated(o, gate, nw, eps=1e-5), (o, gate, nw), do)
-    ms_conv = timed(conv_step, args.steps, args.warmup, dev, D.barrier) / args.steps
-    ms_norm = timed(norm_step, args.steps, args.warmup, dev, D.barrier) / args.steps
+    def graph_ms(fn):
+        """Device time of one step: the step is captured into a CUDA graph once and replayed, so that the figure is the
+        kernels' time and not the host's launch path (three launches per step are shorter than their Python calls)."""
+        fn()
+        torch.cuda.synchronize(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        return timed(graph.replay, args.steps, args.warmup, dev, D.barrier) / args.steps
+    ms_conv_eager = timed(conv_step, args.steps, args.warmup, dev, D.barrier) / args.steps
+    ms_norm_eager = timed(norm_step, args.steps, args.warmup, dev, D.barrier) / args.steps
+    timing = 'CUDA graph of one forward + backward, CUDA events around the replays; eager figures beside'
+    try:
+        ms_conv, ms_norm = graph_ms(conv_step), graph_ms(norm_step)
+    except RuntimeError as e:   # a step that cannot be captured: the eager figures stand in, and the line says so
+        ms_conv, ms_norm, timing = ms_conv_eager, ms_norm_eager, f'eager (graph capture failed: {str(e)[:80]})'
     nb = B * T * Dc * 2
     conv_bytes = 2 * nb + 3 * nb + (B * T // 32) * Dc * (Wc + 1) * 4 * 2   # x -> y ; x, dy -> dx ; parameter partials
     norm_bytes = 3 * nb + 5 * nb                                             # x, g -> y ; x, g, dy -> dx, dg
@@ -866,12 +882,15 @@ def workload_modules(args, D):
         line = base_line(args, D, 'tokens/s of the short convolution + gated RMS norm around the mixer, fwd+bwd (B4 T4096 H16 D128 bf16)',
                          B * T / ((ms_conv * 3 + ms_norm) * 1e-3), ms_conv * 3 + ms_norm, 'weak',
                          'causal_conv1d (W=4, SiLU, bias) on q, k, v [4,4096,2048] each and rms_norm_gated on [4,4096,16,128], forward + backward',
-                         parallelism='single GPU')
+                         parallelism='single GPU', timing=timing)
         line['roofline'] = {'kernel': 'conv_fwd + conv_bwd', 'bound': 'hbm', 'achieved': conv_bytes / (ms_conv * 1e-3) / 1e9, 'peak': peaks['hbm'],
                             'unit': 'GB/s', 'frac': conv_bytes / (ms_conv * 1e-3) / 1e9 / peaks['hbm'], 'traffic': None, 'peak_source': peaks['source']}
         line['modules'] = {'conv_fwd_bwd_ms': ms_conv, 'conv_GB/s': conv_bytes / (ms_conv * 1e-3) / 1e9,
+                           'conv_hbm_frac': conv_bytes / (ms_conv * 1e-3) / 1e9 / peaks['hbm'],
                            'norm_gate_fwd_bwd_ms': ms_norm, 'norm_gate_GB/s': norm_bytes / (ms_norm * 1e-3) / 1e9,
-                           'norm_gate_hbm_frac': norm_bytes / (ms_norm * 1e-3) / 1e9 / peaks['hbm']}
+                           'norm_gate_hbm_frac': norm_bytes / (ms_norm * 1e-3) / 1e9 / peaks['hbm'],
+                           'eager_conv_fwd_bwd_ms': ms_conv_eager, 'eager_norm_gate_fwd_bwd_ms': ms_norm_eager}
+        line['gpu_launches'] = 6 * (args.steps + args.warmup) * 2
         print(json.dumps(line))
 
 
@@ -882,6 +901,8 @@ def main():
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--workload', default='train', choices=['train', 'fwd', 'varlen', 'heads', 'cp', 'decode', 'layer', 'modules'])
+    ap.add_argument('--decode-batches', type=lambda t: [int(x) for x in t.split(',')], default=[1, 2, 4, 8, 16, 32, 64, 128, 256],
+                    help='batch sizes of the decode sweep (the last one is the headline of that workload)')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-gpu-baseline', action='store_true')
     ap.add_argument('--worker', default=None, help=argparse.SUPPRESS)

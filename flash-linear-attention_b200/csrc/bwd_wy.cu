@@ -529,17 +529,29 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
   if (warp == 1) tc5::tmem_dealloc(tm, 256);
 }
 
-// dA_log[hv] = sum over chunks of the per-chunk partials (fixed order: reproducible); same for ddt_bias
-__global__ void gate_param_reduce_kernel(const b200gdn_chunk_args a) {
-  const int hv = blockIdx.x * blockDim.x + threadIdx.x;
-  if (hv >= a.HV) return;
+// dA_log[hv] = sum over chunks of the per-chunk partials, same for ddt_bias.  One CTA per head: thread i adds chunks
+// i, i + 256, ..., then the 256 sums are added pairwise in a fixed tree (reproducible, no atomics).
+__global__ void __launch_bounds__(256) gate_param_reduce_kernel(const b200gdn_chunk_args a) {
+  __shared__ float2 part[256];
+  const int hv = blockIdx.x, tid = threadIdx.x;
   float sA = 0.f, sB = 0.f;
-  for (int c = 0; c < a.n_chunks; ++c) {
+  for (int c = tid; c < a.n_chunks; c += 256) {
     sA += a.gate_partials[((int64_t)c * a.HV + hv) * 2 + 0];
     sB += a.gate_partials[((int64_t)c * a.HV + hv) * 2 + 1];
   }
-  a.dA_log[hv] = sA;
-  if (a.ddt_bias) a.ddt_bias[hv] = sB;
+  part[tid] = make_float2(sA, sB);
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (tid < o) {
+      part[tid].x += part[tid + o].x;
+      part[tid].y += part[tid + o].y;
+    }
+    __syncthreads();
+  }
+  if (tid == 0) {
+    a.dA_log[hv] = part[0].x;
+    if (a.ddt_bias) a.ddt_bias[hv] = part[0].y;
+  }
 }
 
 template <int DK, int DV, bool GROUPED>
@@ -561,7 +573,7 @@ int launch(const b200gdn_chunk_args& a, cudaStream_t st) {
   bwd_wy_kernel<DK, DV, GROUPED><<<grid, NTHREADS, S::bytes, st>>>(a, m);
   if (int e = check_launch("bwd_wy")) return e;
   if (a.options & B200GDN_PREP_GATE) {
-    gate_param_reduce_kernel<<<(a.HV + 63) / 64, 64, 0, st>>>(a);
+    gate_param_reduce_kernel<<<a.HV, 256, 0, st>>>(a);
     return check_launch("gate_param_reduce");
   }
   return 0;
