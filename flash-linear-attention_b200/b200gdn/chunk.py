@@ -162,6 +162,26 @@ def carve(dev, zero, *specs):
     return out
 
 
+class Slab:
+    """One device allocation cut into pieces that are only ever handed to the kernels as addresses: ``nbytes`` per piece
+    (0 = no such piece, address 0), every piece on a 256-byte boundary.  Unlike ``carve`` it builds no tensor view per
+    piece (three torch calls each), which is most of what an allocation-heavy step costs on the host."""
+    __slots__ = ('buf', 'offs')
+
+    def __init__(self, dev, zero, nbytes):
+        offs, total = [], 0
+        for n in nbytes:
+            offs.append(total if n > 0 else -1)
+            total += (int(n) + 255) // 256 * 256
+        self.offs = offs
+        self.buf = (torch.zeros if zero else torch.empty)(max(total, 256), dtype=torch.uint8, device=dev)
+
+    @staticmethod
+    def addresses(buf, offs):
+        base = buf.data_ptr()
+        return [base + o if o >= 0 else 0 for o in offs]
+
+
 def prefix_chains(plan, M, h, x0, out, K, V, reverse: bool, stream: int, last=None, identity: bool = False) -> None:
     """b200gdn_cp_prefix over the chains of a split plan: the start state (reverse: the end gradient) of every piece."""
     a = _lib.PrefixArgs()
@@ -203,18 +223,17 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             o = (torch.zeros if zero else torch.empty)(B, T, HV, V, dtype=bf16, device=dev)
             ht = torch.empty(n_seq, HV, K, V, dtype=f32, device=dev) if output_final_state else None
             # h and v_new are only read by the backward pass: without one they are not even written
-            gamma, A, qk, w, u, v_new, h = carve(
-                dev, zero, ((n_chunks, HV, 64), f32), ((rows, HV, 64), bf16), ((rows, HV, 64), bf16), ((rows, HV, K), bf16),
-                ((rows, HV, V), bf16), ((rows, HV, V) if need_grad else (0,), bf16),
-                ((n_chunks, HV, K, V) if need_grad else (0,), bf16))
-            if not need_grad:
-                v_new = h = None
+            # gamma, A, qk, w, u, v_new, h: known to the host only as addresses
+            slab = Slab(dev, zero, (n_chunks * HV * 64 * 4, rows * HV * 64 * 2, rows * HV * 64 * 2, rows * HV * K * 2,
+                                    rows * HV * V * 2, rows * HV * V * 2 if need_grad else 0,
+                                    n_chunks * HV * K * V * 2 if need_grad else 0))
+            p_gamma, p_A, p_qk, p_w, p_u, p_vnew, p_h = Slab.addresses(slab.buf, slab.offs)
             a.g, a.beta, a.h0 = gf.data_ptr(), bf.data_ptr(), _lib.ptr(h0)
             A_log_f = A_log.detach().float().contiguous() if (options & _lib.PREP_GATE) else None
             bias_f = dt_bias.detach().float().contiguous() if (options & _lib.PREP_GATE) and dt_bias is not None else None
             a.options, a.A_log, a.dt_bias = options, _lib.ptr(A_log_f), _lib.ptr(bias_f)
             a.o, a.ht = o.data_ptr(), _lib.ptr(ht)
-            a.gamma, a.A, a.qk, a.w, a.u, a.h, a.v_new = (_lib.ptr(x) for x in (gamma, A, qk, w, u, h, v_new))
+            a.gamma, a.A, a.qk, a.w, a.u, a.h, a.v_new = p_gamma, p_A, p_qk, p_w, p_u, p_h, p_vnew
             st = _stream(qb)
             if plan is None:
                 _lib.call('b200gdn_chunk_fwd', a, st)
@@ -225,7 +244,7 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
                 h_pre, M_pre, h0_v = carve(dev, False, ((plan.n_pre, HV, K, V), f32), ((plan.n_pre, HV, K, K), f32),
                                            ((n_seq, HV, K, V), f32))
                 p = new_chunk_args(qb, kb, vb, scale, (tables[0], plan.pre_fwd, (n_chunks, plan.n_pre)))
-                p.gamma, p.w, p.u, p.ht, p.cp_M = gamma.data_ptr(), w.data_ptr(), u.data_ptr(), h_pre.data_ptr(), M_pre.data_ptr()
+                p.gamma, p.w, p.u, p.ht, p.cp_M = p_gamma, p_w, p_u, h_pre.data_ptr(), M_pre.data_ptr()
                 p.stage_mask = _lib.FWD_SCAN
                 _lib.call('b200gdn_chunk_fwd', p, st)
                 prefix_chains(plan, M_pre, h_pre, h0, h0_v, K, V, False, st)
@@ -235,8 +254,9 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
                 if ht is not None:
                     ht = ht.index_select(0, plan.last_piece)
         if need_grad:
-            ctx.save_for_backward(qb, kb, vb, bf, gamma, A, qk, w, h, v_new, tables[0], tables[1],
+            ctx.save_for_backward(qb, kb, vb, bf, slab.buf, tables[0], tables[1],
                                   gf if (options & _lib.PREP_GATE) else None, A_log_f, bias_f)
+            ctx.slab_offs = slab.offs
         ctx.meta = (scale, n_chunks, n_seq, initial_state is not None, in_dtypes, options,
                     None if A_log is None else A_log.dtype, None if dt_bias is None else dt_bias.dtype, zero)
         ctx.plan = plan
@@ -244,7 +264,8 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, do, dht):
-        qb, kb, vb, bf, gamma, A, qk, w, h, v_new, chunk_meta, seq_meta, gf, A_log_f, bias_f = ctx.saved_tensors
+        qb, kb, vb, bf, saved, chunk_meta, seq_meta, gf, A_log_f, bias_f = ctx.saved_tensors
+        p_gamma, p_A, p_qk, p_w, _, p_vnew, p_h = Slab.addresses(saved, ctx.slab_offs)
         scale, n_chunks, n_seq, has_h0, in_dtypes, options, A_dtype, bias_dtype, zero = ctx.meta
         dev = qb.device
         dA_log = ddt_bias = None
@@ -258,33 +279,28 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             bf16, f32 = torch.bfloat16, torch.float32
             grouped = HV > H
             gate = bool(options & _lib.PREP_GATE)
-            # results first (they outlive the call), then the workspace
-            dq, dk, dv, dg, dbeta, dh0, dh, dv2, dG, dk_part, dq_acc, gate_partials, dA_log, ddt_bias = carve(
-                dev, zero,
-                ((B, T, H, K), bf16), ((B, T, H, K), bf16), ((B, T, HV, V), bf16), ((B, T, HV), f32), ((B, T, HV), f32),
-                ((n_seq, HV, K, V) if has_h0 else (0,), f32),
-                ((n_chunks, HV, K, V), bf16), ((rows, HV, V), bf16), ((rows, HV), f32),
-                ((rows, H, K) if grouped else (0,), f32), ((rows, H, K) if grouped else (0,), f32),
-                ((n_chunks, HV, 2) if gate else (0,), f32), ((HV,) if gate else (0,), f32),
-                ((HV,) if gate and bias_f is not None else (0,), f32))
-            if not has_h0:
-                dh0 = None
-            if not grouped:
-                dk_part = dq_acc = None
-            if not gate:
-                gate_partials = dA_log = None
-            if not (gate and bias_f is not None):
-                ddt_bias = None
-            a.beta, a.gamma, a.A, a.qk, a.w, a.h, a.v_new = (x.data_ptr() for x in (bf, gamma, A, qk, w, h, v_new))
+            # the results are tensors of their own (they outlive the call); the workspace is one allocation known to the
+            # host only as addresses
+            new = torch.zeros if zero else torch.empty
+            dq, dk = new(B, T, H, K, dtype=bf16, device=dev), new(B, T, H, K, dtype=bf16, device=dev)
+            dv = new(B, T, HV, V, dtype=bf16, device=dev)
+            dg, dbeta = new(B, T, HV, dtype=f32, device=dev), new(B, T, HV, dtype=f32, device=dev)
+            dh0 = torch.empty(n_seq, HV, K, V, dtype=f32, device=dev) if has_h0 else None
+            dA_log = torch.empty(HV, dtype=f32, device=dev) if gate else None
+            ddt_bias = torch.empty(HV, dtype=f32, device=dev) if gate and bias_f is not None else None
+            ws = Slab(dev, zero, (n_chunks * HV * K * V * 2, rows * HV * V * 2, rows * HV * 4,
+                                  rows * H * K * 4 if grouped else 0, rows * H * K * 4 if grouped else 0,
+                                  n_chunks * HV * 2 * 4 if gate else 0))
+            p_dh, p_dv2, p_dG, p_dk_part, p_dq_acc, p_gate_partials = Slab.addresses(ws.buf, ws.offs)
+            a.beta, a.gamma, a.A, a.qk, a.w, a.h, a.v_new = bf.data_ptr(), p_gamma, p_A, p_qk, p_w, p_h, p_vnew
             a.d_o, a.dht = dob.data_ptr(), _lib.ptr(dhtf)
             a.dq, a.dk, a.dv, a.dg, a.dbeta, a.dh0 = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dg.data_ptr(), \
                 dbeta.data_ptr(), _lib.ptr(dh0)
-            a.dh, a.dv2, a.dk_part, a.dG, a.dq_acc = dh.data_ptr(), dv2.data_ptr(), \
-                _lib.ptr(dk_part), dG.data_ptr(), _lib.ptr(dq_acc)
+            a.dh, a.dv2, a.dk_part, a.dG, a.dq_acc = p_dh, p_dv2, p_dk_part, p_dG, p_dq_acc
             a.options = options
             if gate:
                 a.g, a.A_log, a.dt_bias = gf.data_ptr(), A_log_f.data_ptr(), _lib.ptr(bias_f)
-                a.gate_partials, a.dA_log, a.ddt_bias = gate_partials.data_ptr(), dA_log.data_ptr(), _lib.ptr(ddt_bias)
+                a.gate_partials, a.dA_log, a.ddt_bias = p_gate_partials, dA_log.data_ptr(), _lib.ptr(ddt_bias)
             st = _stream(qb)
             plan = ctx.plan
             if plan is None:
@@ -295,7 +311,7 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
                 dh_pre, dM_pre, dht_v = carve(dev, False, ((plan.n_pre, HV, K, V), f32), ((plan.n_pre, HV, K, K), f32),
                                               ((n_seq, HV, K, V), f32))
                 p = new_chunk_args(qb, kb, vb, scale, (chunk_meta, plan.pre_bwd, (n_chunks, plan.n_pre)))
-                p.gamma, p.w, p.qk, p.d_o = gamma.data_ptr(), w.data_ptr(), qk.data_ptr(), dob.data_ptr()
+                p.gamma, p.w, p.qk, p.d_o = p_gamma, p_w, p_qk, dob.data_ptr()
                 p.dh0, p.cp_dM = dh_pre.data_ptr(), dM_pre.data_ptr()
                 p.stage_mask = _lib.BWD_DVLOCAL | _lib.BWD_SCAN
                 _lib.call('b200gdn_chunk_bwd', p, st)
