@@ -95,11 +95,14 @@ def test_public_api_against_reference_fixture(name):
     O.assert_close('dg', gold['dg'], g.grad.cpu(), 0.02)
 
 
-def test_options_equal_preprocessing():
-    """In-kernel options == the op on pre-processed inputs (tests/ops/test_gdn.py:281-448, 881-1190)."""
+@pytest.mark.parametrize('HV', [4, 2])
+def test_options_equal_preprocessing(HV):
+    """In-kernel options == the op on pre-processed inputs (tests/ops/test_gdn.py:281-448, 881-1190); grouped value
+    heads (HV = 4 over H = 2) and one value head per q/k head: the L2 norm's backward is applied where dq and dk are
+    completed, which the two cases do in different code paths."""
     from b200gdn import chunk_gated_delta_rule
     dev = 'cuda'
-    B, T, H, HV, K, V = 2, 150, 2, 4, 128, 128
+    B, T, H, K, V = 2, 150, 2, 128, 128
     gen = torch.Generator().manual_seed(9)
     q = torch.randn(B, T, H, K, generator=gen).to(dev).to(torch.bfloat16)
     k = torch.randn(B, T, H, K, generator=gen).to(dev).to(torch.bfloat16)
@@ -643,6 +646,39 @@ def test_sequence_split_equals_the_unsplit_scan(pieces):
     for n, w_, s_, p_ in zip(names, want, split, plain):
         O.assert_close(f'{n} split vs oracle', w_.float(), s_, REF_TOL[n])
         O.assert_close(f'{n} split vs unsplit', p_, s_, 0.004)
+
+
+@pytest.mark.parametrize('pieces', [None, 3])
+def test_state_v_first_layout(pieces):
+    """states stored [N,HV,V,K] (the reference's state_v_first, tests/ops/test_gdn.py:385-461): the scans read h0 / dht
+    and write ht / dh0 in that layout themselves; the split path transposes at its boundary.  Bit-identical to the run
+    on transposed states."""
+    from b200gdn import chunk_gated_delta_rule, index
+    dev = 'cuda'
+    cu = [0, 37, 700, 700, 1500, 1563]
+    d = O.make_inputs(1, 1563, 2, 4, 128, 128, seed=33, cu_seqlens=cu)
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=dev)
+
+    def run(v_first):
+        leaves = [d[n].to(dev).to(torch.bfloat16).requires_grad_(True) for n in ('q', 'k', 'v')]
+        leaves += [d[n].to(dev).requires_grad_(True) for n in ('g', 'beta')]
+        h0 = d['h0'].to(dev)
+        h0 = (h0.transpose(-1, -2).contiguous() if v_first else h0).requires_grad_(True)
+        dht = d['dht'].to(dev)
+        o, ht = chunk_gated_delta_rule(*leaves, initial_state=h0, output_final_state=True, cu_seqlens=cu_t,
+                                       state_v_first=v_first)
+        torch.autograd.backward([o, ht], [d['do'].to(dev).to(torch.bfloat16), dht.transpose(-1, -2).contiguous() if v_first else dht])
+        outs = [o, ht.transpose(-1, -2) if v_first else ht] + [x.grad for x in leaves]
+        return [x.float().cpu() for x in outs + [h0.grad.transpose(-1, -2) if v_first else h0.grad]]
+    index.FORCE_PIECES = pieces
+    try:
+        index._split_cache.clear()
+        a, b = run(False), run(True)
+    finally:
+        index.FORCE_PIECES = None
+        index._split_cache.clear()
+    for i, (x, y) in enumerate(zip(a, b)):
+        assert torch.equal(x, y), f'state_v_first differs in result {i}'
 
 
 def test_sequence_split_heuristic_on_one_long_sequence():
