@@ -34,7 +34,7 @@ class ChunkArgs(C.Structure):
         ('dq', _p), ('dk', _p), ('dv', _p), ('dg', _p), ('dbeta', _p), ('dh0', _p),
         ('dh', _p), ('dv2', _p), ('dw', _p), ('dk_part', _p), ('dG', _p), ('dq_acc', _p),
         ('options', C.c_uint32), ('A_log', _p), ('dt_bias', _p), ('gate_partials', _p), ('dA_log', _p), ('ddt_bias', _p),
-        ('cp_M', _p), ('cp_dM', _p), ('qk', _p),
+        ('cp_M', _p), ('cp_dM', _p), ('qk', _p), ('rstd_q', _p), ('rstd_k', _p),
     ]
 
 
@@ -49,6 +49,7 @@ class RecurrentArgs(C.Structure):
 
 
 PREP_L2NORM, PREP_GATE, PREP_BETA_SIGMOID, PREP_NEG_EIGVAL = 1, 2, 4, 8
+STATE_V_FIRST = 16   # chunk passes: h0, ht, dht, dh0 stored [N,HV,V,K]
 PREP_PART_ROWS = 128
 
 

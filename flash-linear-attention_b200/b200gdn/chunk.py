@@ -199,19 +199,45 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, cu_seqlens_cpu,
                 A_log=None, dt_bias=None, options=0, out_dtype=None):
-        # options: _lib.PREP_GATE / PREP_BETA_SIGMOID / PREP_NEG_EIGVAL bits; g / beta are then the raw pre-activations
+        # options: _lib.PREP_L2NORM (q, k are normalised here, and the backward kernels apply the norm's backward),
+        # STATE_V_FIRST (states stored [V,K]) and the PREP_GATE / PREP_BETA_SIGMOID / PREP_NEG_EIGVAL bits; g / beta are then the raw pre-activations
         # and the kernels apply (and differentiate) the activations themselves
         in_dtypes = (q.dtype, k.dtype, v.dtype, g.dtype, beta.dtype)
         out_dtype = out_dtype or q.dtype
         dev = q.device
         with torch.cuda.device(dev):
-            qb, kb, vb = (x.to(torch.bfloat16).contiguous() for x in (q, k, v))
+            vb = v.to(torch.bfloat16).contiguous()
+            rstd_q = rstd_k = None
+            if options & _lib.PREP_L2NORM:
+                # q, k L2-normalised to bf16 in one pass (fla/modules/l2norm.py:84-144); the reciprocal norms go to the
+                # backward kernels, which finish dq and dk with the norm's backward themselves
+                if q.dtype not in _DTYPE_CODE or k.dtype != q.dtype:
+                    raise _lib.B200GDNError(f'q/k dtypes {q.dtype}/{k.dtype} are not supported by the L2-norm option')
+                q, k = q.contiguous(), k.contiguous()
+                pa = _lib.PrepArgs()
+                pa.rows, pa.H, pa.K, pa.HV = q.shape[0] * q.shape[1], q.shape[2], q.shape[3], g.shape[-1]
+                pa.flags, pa.qk_dtype = _lib.PREP_L2NORM, _DTYPE_CODE[q.dtype]
+                qb, kb = torch.empty(q.shape, dtype=torch.bfloat16, device=dev), torch.empty(q.shape, dtype=torch.bfloat16, device=dev)
+                rstd_q = torch.empty(q.shape[:-1], dtype=torch.float32, device=dev)
+                rstd_k = torch.empty(q.shape[:-1], dtype=torch.float32, device=dev)
+                pa.q, pa.k, pa.qn, pa.kn = q.data_ptr(), k.data_ptr(), qb.data_ptr(), kb.data_ptr()
+                pa.rstd_q, pa.rstd_k = rstd_q.data_ptr(), rstd_k.data_ptr()
+                _lib.call('b200gdn_prep_fwd', pa, _stream(q))
+                options &= ~_lib.PREP_L2NORM
+            else:
+                qb, kb = q.to(torch.bfloat16).contiguous(), k.to(torch.bfloat16).contiguous()
             gf, bf = g.float().contiguous(), beta.float().contiguous()
             h0 = None if initial_state is None else initial_state.float().contiguous()
             B, T, H, K = qb.shape
             HV, V = vb.shape[2], vb.shape[3]
             # few sequences and heads: long sequences are cut into pieces that are scanned concurrently
             plan = split_plan_for(B, T, cu_seqlens, cu_seqlens_cpu, dev, HV, V // 64)
+            # states stored [V,K]: the scans read and write that layout themselves; only the split path, which composes
+            # states as [K,V] matrices, transposes at its boundary
+            transpose_states = bool(options & _lib.STATE_V_FIRST) and plan is not None
+            if transpose_states:
+                options &= ~_lib.STATE_V_FIRST
+                h0 = None if h0 is None else h0.transpose(-1, -2).contiguous()
             tables = plan.tables if plan is not None else tables_for(B, T, cu_seqlens, cu_seqlens_cpu, dev)
             n_chunks, n_seq = tables[2]          # n_seq counts pieces under a split plan
             n_real = plan.n_chains if plan is not None else n_seq
@@ -221,7 +247,8 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             need_grad = any(ctx.needs_input_grad[:5]) or ctx.needs_input_grad[6]
             zero = not tables.covered
             o = (torch.zeros if zero else torch.empty)(B, T, HV, V, dtype=bf16, device=dev)
-            ht = torch.empty(n_seq, HV, K, V, dtype=f32, device=dev) if output_final_state else None
+            st_shape = (n_seq, HV, V, K) if options & _lib.STATE_V_FIRST else (n_seq, HV, K, V)
+            ht = torch.empty(st_shape, dtype=f32, device=dev) if output_final_state else None
             # h and v_new are only read by the backward pass: without one they are not even written
             # gamma, A, qk, w, u, v_new, h: known to the host only as addresses
             slab = Slab(dev, zero, (n_chunks * HV * 64 * 4, rows * HV * 64 * 2, rows * HV * 64 * 2, rows * HV * K * 2,
@@ -255,16 +282,19 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
                     ht = ht.index_select(0, plan.last_piece)
         if need_grad:
             ctx.save_for_backward(qb, kb, vb, bf, slab.buf, tables[0], tables[1],
-                                  gf if (options & _lib.PREP_GATE) else None, A_log_f, bias_f)
+                                  gf if (options & _lib.PREP_GATE) else None, A_log_f, bias_f, rstd_q, rstd_k)
             ctx.slab_offs = slab.offs
         ctx.meta = (scale, n_chunks, n_seq, initial_state is not None, in_dtypes, options,
                     None if A_log is None else A_log.dtype, None if dt_bias is None else dt_bias.dtype, zero)
         ctx.plan = plan
+        ctx.transpose_states = transpose_states
+        if transpose_states and ht is not None:
+            ht = ht.transpose(-1, -2).contiguous()
         return o.to(out_dtype), ht
 
     @staticmethod
     def backward(ctx, do, dht):
-        qb, kb, vb, bf, saved, chunk_meta, seq_meta, gf, A_log_f, bias_f = ctx.saved_tensors
+        qb, kb, vb, bf, saved, chunk_meta, seq_meta, gf, A_log_f, bias_f, rstd_q, rstd_k = ctx.saved_tensors
         p_gamma, p_A, p_qk, p_w, _, p_vnew, p_h = Slab.addresses(saved, ctx.slab_offs)
         scale, n_chunks, n_seq, has_h0, in_dtypes, options, A_dtype, bias_dtype, zero = ctx.meta
         dev = qb.device
@@ -275,6 +305,8 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             rows = B * T
             dob = do.to(torch.bfloat16).contiguous()
             dhtf = None if dht is None else dht.float().contiguous()
+            if ctx.transpose_states and dhtf is not None:
+                dhtf = dhtf.transpose(-1, -2).contiguous()
             a = new_chunk_args(qb, kb, vb, scale, (chunk_meta, seq_meta, (n_chunks, n_seq)))
             bf16, f32 = torch.bfloat16, torch.float32
             grouped = HV > H
@@ -285,7 +317,8 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             dq, dk = new(B, T, H, K, dtype=bf16, device=dev), new(B, T, H, K, dtype=bf16, device=dev)
             dv = new(B, T, HV, V, dtype=bf16, device=dev)
             dg, dbeta = new(B, T, HV, dtype=f32, device=dev), new(B, T, HV, dtype=f32, device=dev)
-            dh0 = torch.empty(n_seq, HV, K, V, dtype=f32, device=dev) if has_h0 else None
+            st_shape = (n_seq, HV, V, K) if options & _lib.STATE_V_FIRST else (n_seq, HV, K, V)
+            dh0 = torch.empty(st_shape, dtype=f32, device=dev) if has_h0 else None
             dA_log = torch.empty(HV, dtype=f32, device=dev) if gate else None
             ddt_bias = torch.empty(HV, dtype=f32, device=dev) if gate and bias_f is not None else None
             ws = Slab(dev, zero, (n_chunks * HV * K * V * 2, rows * HV * V * 2, rows * HV * 4,
@@ -294,6 +327,7 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             p_dh, p_dv2, p_dG, p_dk_part, p_dq_acc, p_gate_partials = Slab.addresses(ws.buf, ws.offs)
             a.beta, a.gamma, a.A, a.qk, a.w, a.h, a.v_new = bf.data_ptr(), p_gamma, p_A, p_qk, p_w, p_h, p_vnew
             a.d_o, a.dht = dob.data_ptr(), _lib.ptr(dhtf)
+            a.rstd_q, a.rstd_k = _lib.ptr(rstd_q), _lib.ptr(rstd_k)   # given: dq, dk come out w.r.t. the un-normalised q, k
             a.dq, a.dk, a.dv, a.dg, a.dbeta, a.dh0 = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dg.data_ptr(), \
                 dbeta.data_ptr(), _lib.ptr(dh0)
             a.dh, a.dv2, a.dk_part, a.dG, a.dq_acc = p_dh, p_dv2, p_dk_part, p_dG, p_dq_acc
@@ -320,6 +354,8 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
                 _lib.call('b200gdn_chunk_bwd', a, st)
                 if dh0 is not None:
                     dh0 = dh0.index_select(0, plan.first_piece)
+            if ctx.transpose_states and dh0 is not None:
+                dh0 = dh0.transpose(-1, -2).contiguous()
         qd, kd, vd, gd, bd = in_dtypes
         if dA_log is not None:
             dA_log = dA_log.to(A_dtype)
@@ -426,26 +462,24 @@ def chunk_gated_delta_rule(
     if use_gate_in_kernel and A_log.numel() != v.shape[2]:
         raise ValueError(f"A_log must have HV={v.shape[2]} elements, got {A_log.numel()}.")
     use_cp = cp_context is not None and getattr(cp_context, 'group', None) is not None
-    # The gate and beta activations are fused into the first forward and the last backward kernel; the L2 norm (and,
-    # under context parallelism, all three) runs as a pass of its own before / after the chunk kernels.
-    fused = 0 if use_cp else flags & (_lib.PREP_GATE | _lib.PREP_BETA_SIGMOID | _lib.PREP_NEG_EIGVAL)
+    # The gate and beta activations are fused into the first forward and the last backward kernel; the L2 norm is one
+    # pass before the forward kernels and its backward is fused into the kernels that complete dq and dk.  Under
+    # context parallelism all three run as passes of their own before / after the chunk kernels.
+    fused = 0 if use_cp else flags & (_lib.PREP_L2NORM | _lib.PREP_GATE | _lib.PREP_BETA_SIGMOID | _lib.PREP_NEG_EIGVAL)
     pre = flags & ~fused
     if pre & (_lib.PREP_L2NORM | _lib.PREP_GATE | _lib.PREP_BETA_SIGMOID):
         q, k, g, beta = LayerOptionsFunction.apply(q, k, g, beta, A_log if pre & _lib.PREP_GATE else None,
                                                    dt_bias if pre & _lib.PREP_GATE else None, pre)
-    if state_v_first and initial_state is not None:
-        initial_state = initial_state.transpose(-1, -2)
-
     if cp_context is not None and getattr(cp_context, 'group', None) is not None:
         from .cp import chunk_gated_delta_rule_cp
-        o = chunk_gated_delta_rule_cp(q, k, v, g, beta, scale, cp_context)
+        o = chunk_gated_delta_rule_cp(q, k, v, g, beta, scale, cp_context)   # no states cross this interface
         return o.to(out_dtype), None
 
+    # states stored [V,K] (state_v_first): read and written in that layout by the scans themselves
     o, final_state = ChunkGatedDeltaRuleFunction.apply(
         q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, cu_seqlens_cpu,
-        A_log if fused & _lib.PREP_GATE else None, dt_bias if fused & _lib.PREP_GATE else None, fused, out_dtype)
-    if final_state is not None and state_v_first:
-        final_state = final_state.transpose(-1, -2).contiguous()
+        A_log if fused & _lib.PREP_GATE else None, dt_bias if fused & _lib.PREP_GATE else None,
+        fused | (_lib.STATE_V_FIRST if state_v_first else 0), out_dtype)
     return o, final_state
 
 

@@ -60,7 +60,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
   float* rqs = gs + BT;          // [2][64] row-dot partials <dq, q> of the two column halves
   float* rks = rqs + 2 * BT;     // [2][64] <dk, k>
   float* red = rks + 2 * BT;     // [0..7] <h,dh> per warp, [8..15] sum of <dk_state, k> per warp
-  uint64_t* bar = reinterpret_cast<uint64_t*>(red + 16);
+  float* rq2s = red + 16;        // [2][64] <dq, q> of the group's summed dq (fused L2-norm backward, grouped heads only)
+  uint64_t* bar = reinterpret_cast<uint64_t*>(rq2s + 2 * BT);
   uint64_t* bar_a = bar + 1;   // do, v_new, gamma of one head
   uint64_t* bar_b = bar + 2;   // one h / dh panel pair
   uint64_t* bar_c = bar + 3;   // q, k (once)
@@ -246,12 +247,16 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
     if (failed) break;
 
     // ---- epilogue 2: dq (this warp's half of the columns)
+    // fused L2-norm backward: the finished dq stays in registers until the row dots <dq,q> are complete, so that
+    // (dq - q <dq,q>) rstd is formed from the fp32 values and rounded once
+    const bool l2_q = last && a.rstd_q != nullptr;
+    float racc[KB][16];
     {
-      float racc[KB][16];
 #pragma unroll
       for (int b = 0; b < KB; ++b) acc_ld32q(TM_DQ, q, ck + b * 32, racc[b]);
       tc5::tmem_ld_wait();
       float rq_lo = 0.f, rq_hi = 0.f;
+      float rq2_lo = 0.f, rq2_hi = 0.f;   // grouped heads: the same dots for the sum over the group
 #pragma unroll
       for (int b = 0; b < KB; ++b) {
         float (&r)[16] = racc[b];
@@ -278,9 +283,23 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
               if (!last) *pp = make_float2(r[4 * i + 2], r[4 * i + 3]);
             }
           }
+          if (GROUPED) {
+            rq2_lo += r[4 * i] * qa.x + r[4 * i + 1] * qa.y;
+            rq2_hi += r[4 * i + 2] * qb.x + r[4 * i + 3] * qb.y;
+          }
           fs.set(i, r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
         }
-        if (last) fs.store(Hp, BT, q * 16, ck + b * 32, lane);
+        if (last && !l2_q) fs.store(Hp, BT, q * 16, ck + b * 32, lane);
+      }
+      if (GROUPED && l2_q) {
+        rq2_lo += __shfl_xor_sync(0xffffffffu, rq2_lo, 1);
+        rq2_lo += __shfl_xor_sync(0xffffffffu, rq2_lo, 2);
+        rq2_hi += __shfl_xor_sync(0xffffffffu, rq2_hi, 1);
+        rq2_hi += __shfl_xor_sync(0xffffffffu, rq2_hi, 2);
+        if (t == 0) {
+          rq2s[hc * BT + r_lo] = rq2_lo;
+          rq2s[hc * BT + r_hi] = rq2_hi;
+        }
       }
       rq_lo += __shfl_xor_sync(0xffffffffu, rq_lo, 1);
       rq_lo += __shfl_xor_sync(0xffffffffu, rq_lo, 2);
@@ -300,6 +319,30 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_dqk_kernel(const b200gdn_chun
       tc5::fence_after_sync();
       issue_mma_t<4>(TM_DKI, opPm, opQ, 64, DK, 0);
       ph.commit();
+    }
+    if (l2_q) {
+      // q as passed is the L2-normalised tensor: dq w.r.t. the un-normalised one is (dq - q <dq,q>) rstd.  The row
+      // dots are complete now (both column halves); every warp stages its block of the tile from its registers.
+      const float* dots = GROUPED ? rq2s : rqs;
+      const float dot_lo = dots[r_lo] + dots[BT + r_lo], dot_hi = dots[r_hi] + dots[BT + r_hi];
+      const float rs_lo = r_lo < cm.len ? a.rstd_q[(row0 + r_lo) * a.H + hq] : 0.f;
+      const float rs_hi = r_hi < cm.len ? a.rstd_q[(row0 + r_hi) * a.H + hq] : 0.f;
+#pragma unroll
+      for (int b = 0; b < KB; ++b) {
+        FragLoad fq;
+        fq.load(Qs, BT, q * 16, ck + b * 32, lane);
+        const float (&r)[16] = racc[b];
+        FragStore fs;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 qa = fq.lo2(i), qb = fq.hi2(i);
+          fs.set(i, (r[4 * i] - qa.x * dot_lo) * rs_lo, (r[4 * i + 1] - qa.y * dot_lo) * rs_lo,
+                 (r[4 * i + 2] - qb.x * dot_hi) * rs_hi, (r[4 * i + 3] - qb.y * dot_hi) * rs_hi);
+        }
+        fs.store(Hp, BT, q * 16, ck + b * 32, lane);
+      }
+      tc5::fence_async_smem();
+      __syncthreads();
     }
     if (last) {
       if (cm.len == BT) {

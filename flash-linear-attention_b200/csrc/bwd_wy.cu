@@ -475,14 +475,18 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
     }
 
     // ---- epilogue 5: dk = accumulator + part from the dq/dk kernel (group-accumulated in fp32)
+    const bool l2_k = last && a.rstd_k != nullptr;   // fused L2-norm backward: needs <dk, k> of the finished rows
     {
       float r[KB][16];
 #pragma unroll
       for (int b = 0; b < KB; ++b) acc_ld32q(TM_BIG, q, hc * (DK / 2) + b * 32, r[b]);
       tc5::tmem_ld_wait();
+      float rk_lo = 0.f, rk_hi = 0.f;
 #pragma unroll
       for (int b = 0; b < KB; ++b) {
         FragStore fs;
+        FragLoad fk;
+        if (l2_k) fk.load(Ks, BT, q * 16, hc * (DK / 2) + b * 32, lane);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int n8 = b * 4 + i, col = n8 * 8 + 2 * t;
@@ -501,14 +505,63 @@ __global__ void __launch_bounds__(NTHREADS, 2) bwd_wy_kernel(const b200gdn_chunk
             if (r_hi < cm.len) *reinterpret_cast<float2*>(dkbuf + r_hi * dkstride + col) = make_float2(d2, d3);
           } else {
             fs.set(i, d0, d1, d2, d3);
+            if (l2_k) {
+              const float2 ka = fk.lo2(i), kb = fk.hi2(i);
+              rk_lo += d0 * ka.x + d1 * ka.y;
+              rk_hi += d2 * kb.x + d3 * kb.y;
+            }
           }
         }
-        if (last) fs.store(dWs, BT, q * 16, hc * (DK / 2) + b * 32, lane);
+        if (last && !l2_k) fs.store(dWs, BT, q * 16, hc * (DK / 2) + b * 32, lane);
+      }
+      if (l2_k) {   // r_mk (row sums of M . KK) was consumed before phase 5 ended: its place takes the row dots
+        rk_lo = sum_over_t(rk_lo);
+        rk_hi = sum_over_t(rk_hi);
+        if (t == 0) {
+          r_mk[hc * BT + r_lo] = rk_lo;
+          r_mk[hc * BT + r_hi] = rk_hi;
+        }
       }
     }
     tc5::fence_async_smem();
     tc5::fence_before_sync();
     __syncthreads();
+    if (l2_k) {
+      // k as passed is the L2-normalised tensor: dk w.r.t. the un-normalised one is (dk - k <dk,k>) rstd.  Both column
+      // halves of the dots are there now; every warp forms its block again from the fp32 accumulator (still in
+      // tensor memory) and the part it holds in registers, so that the result is rounded once
+      const float dot_lo = r_mk[r_lo] + r_mk[BT + r_lo], dot_hi = r_mk[r_hi] + r_mk[BT + r_hi];
+      const float rs_lo = r_lo < cm.len ? a.rstd_k[(row0 + r_lo) * a.H + hq] : 0.f;
+      const float rs_hi = r_hi < cm.len ? a.rstd_k[(row0 + r_hi) * a.H + hq] : 0.f;
+      float r[KB][16];
+#pragma unroll
+      for (int b = 0; b < KB; ++b) acc_ld32q(TM_BIG, q, hc * (DK / 2) + b * 32, r[b]);
+      tc5::tmem_ld_wait();
+#pragma unroll
+      for (int b = 0; b < KB; ++b) {
+        FragLoad fk;
+        fk.load(Ks, BT, q * 16, hc * (DK / 2) + b * 32, lane);
+        FragStore fs;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int n8 = b * 4 + i;
+          float2 p_lo, p_hi;
+          if (!GROUPED) {
+            p_lo = unpack_bf16(part16[GROUPED ? 0 : n8][0]);
+            p_hi = unpack_bf16(part16[GROUPED ? 0 : n8][1]);
+          } else {
+            p_lo = part32[GROUPED ? n8 : 0][0];
+            p_hi = part32[GROUPED ? n8 : 0][1];
+          }
+          const float2 ka = fk.lo2(i), kb = fk.hi2(i);
+          fs.set(i, (r[b][4 * i] + p_lo.x - ka.x * dot_lo) * rs_lo, (r[b][4 * i + 1] + p_lo.y - ka.y * dot_lo) * rs_lo,
+                 (r[b][4 * i + 2] + p_hi.x - kb.x * dot_hi) * rs_hi, (r[b][4 * i + 3] + p_hi.y - kb.y * dot_hi) * rs_hi);
+        }
+        fs.store(dWs, BT, q * 16, hc * (DK / 2) + b * 32, lane);
+      }
+      tc5::fence_async_smem();
+      __syncthreads();
+    }
     if (last) {
       if (cm.len == BT) {
         if (tid == 32) {

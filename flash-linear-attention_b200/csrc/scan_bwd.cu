@@ -83,6 +83,7 @@ __global__ void __launch_bounds__(NEPI + 64)
   const bool store_d2 = a.dv2 != nullptr && (dvl || has_dl);
   const bool st_dh = !m_mode && a.dh != nullptr;
   float* const dh0_out = m_mode ? a.cp_dM : a.dh0;
+  const bool vfirst = !m_mode && (a.options & B200GDN_STATE_V_FIRST);   // dht and dh0 stored [V][K]
   constexpr uint32_t TMEM_COLS = DVL ? 256 : 128;   // DVL: 192 used; the allocation is a power of two
 
   if (warp == 0) tc5::tmem_alloc(tmem_slot, TMEM_COLS);
@@ -218,7 +219,7 @@ __global__ void __launch_bounds__(NEPI + 64)
           for (int e = 0; e < 4; ++e) {
             const int r = srow0 + 16 * hf + g + ((e >> 1) << 3);
             const int col = v0 + 32 * hc + 8 * i + 2 * t + (e & 1);
-            Sr[hf][4 * i + e] = dht ? dht[(int64_t)r * DV + col] : ((m_mode && r == col) ? 1.f : 0.f);
+            Sr[hf][4 * i + e] = dht ? (vfirst ? dht[(int64_t)col * DK + r] : dht[(int64_t)r * DV + col]) : ((m_mode && r == col) ? 1.f : 0.f);
           }
     }
 
@@ -360,8 +361,15 @@ __global__ void __launch_bounds__(NEPI + 64)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int r = srow0 + 16 * hf + g, col = v0 + 32 * hc + 8 * i + 2 * t;
-          *reinterpret_cast<float2*>(&d0[(int64_t)r * DV + col]) = make_float2(Sr[hf][4 * i], Sr[hf][4 * i + 1]);
-          *reinterpret_cast<float2*>(&d0[(int64_t)(r + 8) * DV + col]) = make_float2(Sr[hf][4 * i + 2], Sr[hf][4 * i + 3]);
+          if (vfirst) {   // [V][K]: once per sequence, so the strided scalar stores do not matter
+            d0[(int64_t)col * DK + r] = Sr[hf][4 * i];
+            d0[(int64_t)(col + 1) * DK + r] = Sr[hf][4 * i + 1];
+            d0[(int64_t)col * DK + r + 8] = Sr[hf][4 * i + 2];
+            d0[(int64_t)(col + 1) * DK + r + 8] = Sr[hf][4 * i + 3];
+          } else {
+            *reinterpret_cast<float2*>(&d0[(int64_t)r * DV + col]) = make_float2(Sr[hf][4 * i], Sr[hf][4 * i + 1]);
+            *reinterpret_cast<float2*>(&d0[(int64_t)(r + 8) * DV + col]) = make_float2(Sr[hf][4 * i + 2], Sr[hf][4 * i + 3]);
+          }
         }
     }
   }

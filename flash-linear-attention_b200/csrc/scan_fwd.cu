@@ -98,6 +98,7 @@ __global__ void __launch_bounds__(NEPI + 64 + (OUT ? NOUT * 32 : 0))
   const bool has_u = !m_mode && a.u != nullptr;
   const bool st_h = !m_mode && a.h != nullptr, st_vn = !m_mode && a.v_new != nullptr;
   float* const ht_out = m_mode ? a.cp_M : a.ht;
+  const bool vfirst = !m_mode && (a.options & B200GDN_STATE_V_FIRST);   // h0 and ht stored [V][K]
   constexpr uint32_t TMEM_COLS = OUT ? 512 : 128;   // 384 used; the allocation is a power of two
 
   if (warp == 0) tc5::tmem_alloc(tmem_slot, TMEM_COLS);
@@ -241,7 +242,7 @@ __global__ void __launch_bounds__(NEPI + 64 + (OUT ? NOUT * 32 : 0))
           for (int e = 0; e < 4; ++e) {
             const int r = srow0 + 16 * hf + g + ((e >> 1) << 3);
             const int col = v0 + 32 * hc + 8 * i + 2 * t + (e & 1);
-            Sr[hf][4 * i + e] = h0 ? h0[(int64_t)r * DV + col] : ((m_mode && r == col) ? 1.f : 0.f);
+            Sr[hf][4 * i + e] = h0 ? (vfirst ? h0[(int64_t)col * DK + r] : h0[(int64_t)r * DV + col]) : ((m_mode && r == col) ? 1.f : 0.f);
           }
     }
 
@@ -350,8 +351,15 @@ __global__ void __launch_bounds__(NEPI + 64 + (OUT ? NOUT * 32 : 0))
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int r = srow0 + 16 * hf + g, col = v0 + 32 * hc + 8 * i + 2 * t;
-          *reinterpret_cast<float2*>(&ht[(int64_t)r * DV + col]) = make_float2(Sr[hf][4 * i], Sr[hf][4 * i + 1]);
-          *reinterpret_cast<float2*>(&ht[(int64_t)(r + 8) * DV + col]) = make_float2(Sr[hf][4 * i + 2], Sr[hf][4 * i + 3]);
+          if (vfirst) {   // [V][K]: once per sequence, so the strided scalar stores do not matter
+            ht[(int64_t)col * DK + r] = Sr[hf][4 * i];
+            ht[(int64_t)(col + 1) * DK + r] = Sr[hf][4 * i + 1];
+            ht[(int64_t)col * DK + r + 8] = Sr[hf][4 * i + 2];
+            ht[(int64_t)(col + 1) * DK + r + 8] = Sr[hf][4 * i + 3];
+          } else {
+            *reinterpret_cast<float2*>(&ht[(int64_t)r * DV + col]) = make_float2(Sr[hf][4 * i], Sr[hf][4 * i + 1]);
+            *reinterpret_cast<float2*>(&ht[(int64_t)(r + 8) * DV + col]) = make_float2(Sr[hf][4 * i + 2], Sr[hf][4 * i + 3]);
+          }
         }
     }
   } else if (OUT) {

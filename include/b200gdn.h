@@ -60,6 +60,7 @@ typedef enum b200gdn_status {
 #define B200GDN_PREP_GATE 2u
 #define B200GDN_PREP_BETA_SIGMOID 4u
 #define B200GDN_PREP_NEG_EIGVAL 8u
+#define B200GDN_STATE_V_FIRST 16u /* chunk passes: h0, ht, dht and dh0 are stored [N,HV,V,K] (the reference's state_v_first) */
 typedef struct b200gdn_chunk_args {
   int32_t struct_bytes;          /* = sizeof(b200gdn_chunk_args), checked */
   int32_t rows, H, HV, K, V;
@@ -124,6 +125,12 @@ typedef struct b200gdn_chunk_args {
   /* written by the forward pass (intra stage, needs q), read by the fused scan stages of both passes:
    * bf16 [rows,HV,64], row i of a chunk holds <q_i,k_j> 2^(gamma_i - gamma_j) for j <= i, zero for j > i */
   void* qk;
+  /* Backward only.  q / k as passed are the L2-normalised tensors b200gdn_prep_fwd produced
+   * (fla/modules/l2norm.py:84-144); with their reciprocal norms given here (fp32 [rows,H]) the backward pass returns
+   * dq / dk w.r.t. the un-normalised tensors, dx = (dy - y <dy,y>) rstd, applied where dq and dk are completed
+   * (replaces l2norm_bwd, fla/modules/l2norm.py:200-251).  NULL: dq / dk are gradients w.r.t. q / k as passed. */
+  const float* rstd_q;
+  const float* rstd_k;
 } b200gdn_chunk_args;
 
 /* Replaces chunk_gated_delta_rule_fwd (fla/ops/gated_delta_rule/chunk.py:33-123):

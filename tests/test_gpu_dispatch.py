@@ -104,7 +104,38 @@ def case(name, T, H, HV, cu, ref_kw):
     return out
 
 
+def case_layer(T, H, HV):
+    """the options fla.layers.GatedDeltaNet turns on (fla/layers/gated_deltanet.py:309-325), on both sides"""
+    gen = torch.Generator().manual_seed(77)
+    B = 2
+    d = dict(q=torch.randn(B, T, H, 128, generator=gen).to(torch.bfloat16),
+             k=torch.randn(B, T, H, 128, generator=gen).to(torch.bfloat16),
+             v=torch.randn(B, T, HV, 128, generator=gen).to(torch.bfloat16),
+             g=torch.randn(B, T, HV, generator=gen), beta=torch.randn(B, T, HV, generator=gen),
+             h0=torch.randn(B, HV, 128, 128, generator=gen) * 0.1,      # [V,K]
+             A_log=torch.randn(HV, generator=gen) * 0.3, dt_bias=torch.randn(HV, generator=gen) * 0.3,
+             do=torch.randn(B, T, HV, 128, generator=gen).to(torch.bfloat16),
+             dht=torch.randn(B, HV, 128, 128, generator=gen) * 0.1)
+
+    def run(op):
+        leaves = [d[n].to(dev).requires_grad_(True) for n in ('q', 'k', 'v', 'g', 'beta', 'h0', 'A_log', 'dt_bias')]
+        o, ht = op(*leaves[:5], initial_state=leaves[5], output_final_state=True, use_qk_l2norm_in_kernel=True,
+                   use_gate_in_kernel=True, A_log=leaves[6], dt_bias=leaves[7], use_beta_sigmoid_in_kernel=True,
+                   allow_neg_eigval=True, state_v_first=True)
+        torch.autograd.backward([o, ht], [d['do'].to(dev), d['dht'].to(dev)])
+        return [o, ht] + [x.grad for x in leaves]
+    ref, ours = run(ref_op), run(our_op)
+    names = ('o', 'ht', 'dq', 'dk', 'dv', 'dg', 'dbeta', 'dh0', 'dA_log', 'ddt_bias')
+    out = {}
+    for n, r, x in zip(names, ref, ours):
+        r, x = r.float(), x.float()
+        out[n] = float((r - x).square().mean().sqrt() / (r.square().mean().sqrt() + 1e-12))
+    return out
+
+
 res = {
+    'layer_options': case_layer(1500, 4, 4),
+    'layer_options_gva': case_layer(700, 2, 4),
     'dense_16_heads': case('dense', 2048, 16, 16, None, {}),
     'ragged_gva': case('ragged', 6000, 8, 16, [0, 100, 1500, 1563, 4400, 4401, 6000], {}),
     'reference_chunk_size_16': case('cs16', 700, 2, 2, [0, 300, 700], {'chunk_size': 16}),
@@ -120,8 +151,9 @@ def test_against_the_reference_triton_path_live():
     """The reference's stock Triton chunk path (other back ends switched off), run on this GPU on the same seeded
     tensors: 16 heads over 32 chunks with an initial state and a final-state gradient; ragged packed sequences (one of a
     single token, one of 2900 tokens) with grouped value heads; and the reference run with chunk_size 16 and 32, whose
-    results this library (which always works on 64-token chunks) must reproduce.  Tolerances of the reference's own
-    tests (tests/ops/test_gdn.py:108-200)."""
+    results this library (which always works on 64-token chunks) must reproduce; and the layer's in-kernel options
+    (q/k L2 norm, gate, 2 sigmoid(beta), V-first states) on both sides, with and without grouped value heads.
+    Tolerances of the reference's own tests (tests/ops/test_gdn.py:108-200, 225-448)."""
     import json
     pkg = os.path.join(ROOT, 'flash-linear-attention_b200')
     out = subprocess.run([sys.executable, '-c', _LIVE, pkg, REF_INSTALL], capture_output=True, text=True, timeout=1500)
@@ -133,7 +165,7 @@ def test_against_the_reference_triton_path_live():
     if os.path.isdir(gp):
         with open(os.path.join(gp, 'parity_vs_reference_triton.json'), 'w') as f:
             json.dump(res, f, indent=1)
-    tol = dict(o=0.005, ht=0.005, dq=0.008, dk=0.008, dv=0.008, dh0=0.008, dg=0.02, dbeta=0.02)
+    tol = dict(o=0.005, ht=0.005, dq=0.008, dk=0.008, dv=0.008, dh0=0.008, dg=0.02, dbeta=0.02, dA_log=0.02, ddt_bias=0.02)
     for cname, errs in res.items():
         for n, e in errs.items():
             assert e <= tol[n], f'{cname}: {n} err-ratio {e} > {tol[n]}'
