@@ -250,11 +250,13 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             st_shape = (n_seq, HV, V, K) if options & _lib.STATE_V_FIRST else (n_seq, HV, K, V)
             ht = torch.empty(st_shape, dtype=f32, device=dev) if output_final_state else None
             # h and v_new are only read by the backward pass: without one they are not even written
-            # gamma, A, qk, w, u, v_new, h: known to the host only as addresses
+            # gamma, A, qk, w, v_new, h: known to the host only as addresses, kept for the backward pass as one tensor.
+            # u is read by the forward scan only: an allocation of its own, returned to the pool when this pass ends
             slab = Slab(dev, zero, (n_chunks * HV * 64 * 4, rows * HV * 64 * 2, rows * HV * 64 * 2, rows * HV * K * 2,
-                                    rows * HV * V * 2, rows * HV * V * 2 if need_grad else 0,
-                                    n_chunks * HV * K * V * 2 if need_grad else 0))
-            p_gamma, p_A, p_qk, p_w, p_u, p_vnew, p_h = Slab.addresses(slab.buf, slab.offs)
+                                    rows * HV * V * 2 if need_grad else 0, n_chunks * HV * K * V * 2 if need_grad else 0))
+            p_gamma, p_A, p_qk, p_w, p_vnew, p_h = Slab.addresses(slab.buf, slab.offs)
+            u_buf = (torch.zeros if zero else torch.empty)(rows * HV * V, dtype=bf16, device=dev)
+            p_u = u_buf.data_ptr()
             a.g, a.beta, a.h0 = gf.data_ptr(), bf.data_ptr(), _lib.ptr(h0)
             A_log_f = A_log.detach().float().contiguous() if (options & _lib.PREP_GATE) else None
             bias_f = dt_bias.detach().float().contiguous() if (options & _lib.PREP_GATE) and dt_bias is not None else None
@@ -295,7 +297,7 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do, dht):
         qb, kb, vb, bf, saved, chunk_meta, seq_meta, gf, A_log_f, bias_f, rstd_q, rstd_k = ctx.saved_tensors
-        p_gamma, p_A, p_qk, p_w, _, p_vnew, p_h = Slab.addresses(saved, ctx.slab_offs)
+        p_gamma, p_A, p_qk, p_w, p_vnew, p_h = Slab.addresses(saved, ctx.slab_offs)
         scale, n_chunks, n_seq, has_h0, in_dtypes, options, A_dtype, bias_dtype, zero = ctx.meta
         dev = qb.device
         dA_log = ddt_bias = None
