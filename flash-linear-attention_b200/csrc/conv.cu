@@ -9,7 +9,7 @@
 // Pure HBM streaming: a thread owns four consecutive channels (one 8-byte access per token for bf16) and walks 32
 // consecutive tokens of one sequence (half a tile of the mixer's chunk table) with the W-1 previous inputs in
 // registers, so x is read once (plus W-1 rows of overlap per share) and y written once.  The rows reach the thread
-// through a private ring of asynchronous 16-byte copies in shared memory (sixteen tokens, twelve of them in flight
+// through a private ring of asynchronous 8- or 16-byte copies in shared memory (sixteen tokens, twelve of them in flight
 // while four are consumed): the DRAM latency is paid once per share, not once per round of loads, and the registers
 // hold no look-ahead.  The backward pass recomputes the pre-activation, forms dx with a register ring over the W taps
 // (the W-1 tokens after the share are re-evaluated for their contribution to its dx), writes the gradient of the
