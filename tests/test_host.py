@@ -200,3 +200,24 @@ def test_install_and_uninstall_against_the_reference_registry():
                          capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stdout + out.stderr
     assert 'install-ok 0.5.2' in out.stdout
+
+
+def test_slab_hands_out_aligned_addresses_and_null_for_absent_pieces():
+    """The step's workspace is one allocation known to the host only as addresses: every piece on a 256-byte boundary,
+    pieces of zero bytes get the null address, pieces do not overlap, and the addresses can be rebuilt from the saved
+    tensor and offsets (what the backward pass does)."""
+    import torch
+    from b200gdn.chunk import Slab
+    sizes = (1000, 0, 256, 77, 0, 4096)
+    slab = Slab(torch.device('cpu'), True, sizes)
+    addr = Slab.addresses(slab.buf, slab.offs)
+    base = slab.buf.data_ptr()
+    assert [a == 0 for a in addr] == [n == 0 for n in sizes]
+    live = [(a - base, n) for a, n in zip(addr, sizes) if n]
+    assert all(off % 256 == 0 for off, _ in live)
+    for (o0, n0), (o1, _) in zip(live, live[1:]):
+        assert o0 + n0 <= o1
+    assert live[-1][0] + live[-1][1] <= slab.buf.numel()
+    assert Slab.addresses(slab.buf, list(slab.offs)) == addr
+    assert int(slab.buf.sum()) == 0                      # zero=True fills the allocation
+    assert Slab(torch.device('cpu'), False, (0, 0)).buf.numel() >= 256   # never an empty allocation
